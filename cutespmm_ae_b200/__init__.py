@@ -1,0 +1,220 @@
+"""cutespmm_ae_b200 -- Python binding of libcutespmm, the B200 (sm_100a) sparse x dense product.
+
+Everything here is a thin ctypes layer over the C ABI declared in include/cutespmm.h; the classes
+mirror the reference project's operator objects for this path:
+
+    reference (aFatCa/cuTeSpMM_AE)                    here
+    ------------------------------------------------  ---------------------------------
+    MTX_READER(path)               IO.cu:10           MtxReader(path)
+    HRPB(M, K, rowPtr, cols, vals) data.cu:80         Plan(M, K, row_ptr, cols, vals)
+    SPMM_TC(M, K, N, blockedRowPtr).run(...)          Plan.spmm(B, C) / Plan.spmm_host(B, C)
+                                   spmm.cu:276,823
+
+There is no CPU implementation behind these calls: if the shared library is missing the import
+fails, and executing a plan without a CUDA device returns an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+from . import _build
+
+__all__ = ["CuteSpmmError", "Plan", "MtxReader", "partition_rows", "lib", "PATH_AUTO", "PATH_ROWS", "PATH_BRICK"]
+
+PATH_AUTO, PATH_ROWS, PATH_BRICK = 0, 1, 2
+
+
+class CuteSpmmError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"libcutespmm: {message} (status {status})")
+        self.status = status
+
+
+class Options(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("path", C.c_uint32), ("split_nnz", C.c_uint32),
+                ("tile_nnz", C.c_uint32), ("brick_density", C.c_float), ("reserved", C.c_uint32 * 3)]
+
+
+class PlanInfo(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "M", "K", "nnz", "num_panels", "num_blocks", "num_tiles", "num_long_rows", "num_chunks",
+        "brick_panels", "num_bricks", "device_bytes", "scratch_bytes_per_col")]
+
+
+def _load() -> C.CDLL:
+    path = _build.LIB
+    if not path.exists():
+        # building needs nvcc only, not a GPU
+        _build.build()
+    lib = C.CDLL(str(path))
+    u64p, u32p, f32p, vp = C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.POINTER(C.c_float), C.c_void_p
+    sig = {
+        "cutespmm_status_string": (C.c_char_p, [C.c_int]),
+        "cutespmm_last_error": (C.c_char_p, []),
+        "cutespmm_version": (C.c_int, []),
+        "cutespmm_plan_create": (C.c_int, [C.POINTER(vp), C.c_uint64, C.c_uint64, vp, vp, vp, C.POINTER(Options)]),
+        "cutespmm_plan_create_u32": (C.c_int, [C.POINTER(vp), C.c_uint32, C.c_uint32, vp, vp, vp, C.POINTER(Options)]),
+        "cutespmm_plan_build_host": (C.c_int, [C.POINTER(vp), C.c_uint64, C.c_uint64, vp, vp, vp, C.POINTER(Options)]),
+        "cutespmm_plan_destroy": (C.c_int, [vp]),
+        "cutespmm_plan_info": (C.c_int, [vp, C.POINTER(PlanInfo)]),
+        "cutespmm_plan_blocked_row_ptr": (C.c_int, [vp, vp]),
+        "cutespmm_plan_active_cols": (C.c_int, [vp, vp]),
+        "cutespmm_plan_decode_csr": (C.c_int, [vp, vp, vp, vp]),
+        "cutespmm_spmm": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, vp]),
+        "cutespmm_spmm_host": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, vp, f32p]),
+        "cutespmm_spmm_launch_count": (C.c_int, [vp, C.c_uint32]),
+        "cutespmm_plan_device_status": (C.c_int, [vp, u32p]),
+        "cutespmm_partition_rows": (C.c_int, [C.c_uint64, vp, C.c_uint32, C.c_uint32, C.c_uint32, vp]),
+        "cutespmm_mtx_open": (C.c_int, [C.POINTER(vp), C.c_char_p, C.c_int]),
+        "cutespmm_mtx_dims": (C.c_int, [vp, u32p, u32p, u32p]),
+        "cutespmm_mtx_arrays": (C.c_int, [vp, C.POINTER(u32p), C.POINTER(u32p), C.POINTER(f32p)]),
+        "cutespmm_mtx_close": (C.c_int, [vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        msg = lib.cutespmm_last_error().decode() or lib.cutespmm_status_string(status).decode()
+        raise CuteSpmmError(status, msg)
+
+
+def _np(a, dtype) -> np.ndarray:
+    """Host array view of a numpy array or CPU torch tensor, converted to `dtype`, contiguous."""
+    if hasattr(a, "detach"):
+        a = a.detach().cpu().numpy()
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+class Plan:
+    """Device-resident, preprocessed A.  Counterpart of HRPB (data.cu:54-340) plus the work list
+    of SPMM_TC (spmm.cu:691-822).  `host_only=True` builds the plan without touching CUDA."""
+
+    def __init__(self, M: int, K: int, row_ptr, cols, vals, *, path: int = PATH_AUTO, split_nnz: int = 0,
+                 tile_nnz: int = 0, brick_density: float = 0.0, host_only: bool = False):
+        self._h = C.c_void_p()
+        rp, cc, vv = _np(row_ptr, np.uint64), _np(cols, np.uint32), _np(vals, np.float32)
+        if rp.shape[0] != M + 1:
+            raise ValueError("row_ptr must have M+1 entries")
+        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density)
+        fn = lib.cutespmm_plan_build_host if host_only else lib.cutespmm_plan_create
+        _check(fn(C.byref(self._h), M, K, rp.ctypes.data, cc.ctypes.data, vv.ctypes.data, C.byref(opts)))
+        self.M, self.K, self.nnz = M, K, int(rp[-1])
+
+    @classmethod
+    def from_csr(cls, A, **kw) -> "Plan":
+        """From a generators.CsrMatrix (or anything with M, K, row_ptr, cols, vals)."""
+        return cls(A.M, A.K, A.row_ptr, A.cols, A.vals, **kw)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self._h.value:
+            lib.cutespmm_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
+    def info(self) -> dict:
+        i = PlanInfo()
+        _check(lib.cutespmm_plan_info(self._h, C.byref(i)))
+        return {n: int(getattr(i, n)) for n, _ in PlanInfo._fields_}
+
+    def blocked_row_ptr(self) -> np.ndarray:
+        out = np.empty(self.info()["num_panels"] + 1, dtype=np.uint32)
+        _check(lib.cutespmm_plan_blocked_row_ptr(self._h, out.ctypes.data))
+        return out
+
+    def active_cols(self) -> np.ndarray:
+        out = np.empty(self.info()["num_blocks"] * 16, dtype=np.uint32)
+        _check(lib.cutespmm_plan_active_cols(self._h, out.ctypes.data))
+        return out
+
+    def decode_csr(self):
+        rp = np.empty(self.M + 1, dtype=np.uint64)
+        cc = np.empty(self.nnz, dtype=np.uint32)
+        vv = np.empty(self.nnz, dtype=np.float32)
+        _check(lib.cutespmm_plan_decode_csr(self._h, rp.ctypes.data, cc.ctypes.data, vv.ctypes.data))
+        n = int(rp[-1])
+        return rp, cc[:n], vv[:n]
+
+    def launch_count(self, N: int) -> int:
+        return lib.cutespmm_spmm_launch_count(self._h, N)
+
+    def device_status(self) -> int:
+        s = C.c_uint32()
+        _check(lib.cutespmm_plan_device_status(self._h, C.byref(s)))
+        return s.value
+
+    def spmm(self, B, Cout=None, stream=None):
+        """C = A @ B with B, C CUDA fp32 torch tensors (row-major, last stride 1).  Runs on
+        `stream` (a torch.cuda.Stream) or on torch's current stream."""
+        import torch
+
+        if not B.is_cuda or B.dtype != torch.float32 or B.dim() != 2 or B.stride(1) != 1:
+            raise ValueError("B must be a 2-D CUDA fp32 tensor with unit column stride")
+        if B.shape[0] != self.K:
+            raise ValueError(f"B has {B.shape[0]} rows, A has {self.K} columns")
+        N = B.shape[1]
+        if Cout is None:
+            Cout = torch.empty((self.M, N), dtype=torch.float32, device=B.device)
+        if not Cout.is_cuda or Cout.dtype != torch.float32 or Cout.shape != (self.M, N) or Cout.stride(1) != 1:
+            raise ValueError("C must be an M x N CUDA fp32 tensor with unit column stride")
+        st = (stream or torch.cuda.current_stream(B.device)).cuda_stream
+        _check(lib.cutespmm_spmm(self._h, B.data_ptr(), B.stride(0) if B.shape[0] > 1 else max(N, 1), Cout.data_ptr(),
+                                 Cout.stride(0) if self.M > 1 else max(N, 1), N, st))
+        return Cout
+
+    def spmm_host(self, B, Cout=None, stream=None):
+        """Host buffers in, host buffers out (numpy arrays or CPU torch tensors; pin them for full
+        copy bandwidth).  Returns (C, kernel_ms)."""
+        import torch
+
+        tb = B if hasattr(B, "data_ptr") else torch.from_numpy(np.ascontiguousarray(B, dtype=np.float32))
+        if tb.is_cuda or tb.dtype != torch.float32 or tb.dim() != 2 or tb.stride(1) != 1 or tb.shape[0] != self.K:
+            raise ValueError("B must be a K x N CPU fp32 tensor with unit column stride")
+        N = tb.shape[1]
+        if Cout is None:
+            Cout = torch.empty((self.M, N), dtype=torch.float32)
+        tc = Cout if hasattr(Cout, "data_ptr") else torch.from_numpy(Cout)
+        ms = C.c_float(0.0)
+        st = stream.cuda_stream if stream is not None else None
+        _check(lib.cutespmm_spmm_host(self._h, tb.data_ptr(), tb.stride(0) if self.K > 1 else max(N, 1), tc.data_ptr(),
+                                      tc.stride(0) if self.M > 1 else max(N, 1), N, st, C.byref(ms)))
+        return Cout, ms.value
+
+
+def partition_rows(row_ptr, nparts: int, align_rows: int = 16, row_cost: int = 4) -> np.ndarray:
+    """nnz-balanced contiguous row ranges, boundaries multiples of `align_rows`; returns nparts+1 bounds."""
+    rp = _np(row_ptr, np.uint64)
+    out = np.empty(nparts + 1, dtype=np.uint64)
+    _check(lib.cutespmm_partition_rows(rp.shape[0] - 1, rp.ctypes.data, nparts, align_rows, row_cost, out.ctypes.data))
+    return out
+
+
+class MtxReader:
+    """MatrixMarket loader with the fields MTX_READER exposes (IO.cu:4-9): M, K, nnz, rowPtr, cols, vals."""
+
+    def __init__(self, path: str | Path, pattern_only: bool = True):
+        h = C.c_void_p()
+        st = lib.cutespmm_mtx_open(C.byref(h), str(path).encode(), 1 if pattern_only else 0)
+        if st != 0:
+            raise CuteSpmmError(st, f"cannot read MatrixMarket file {path}")
+        try:
+            M, K, nnz = C.c_uint32(), C.c_uint32(), C.c_uint32()
+            _check(lib.cutespmm_mtx_dims(h, C.byref(M), C.byref(K), C.byref(nnz)))
+            rp, cc, vv = C.POINTER(C.c_uint32)(), C.POINTER(C.c_uint32)(), C.POINTER(C.c_float)()
+            _check(lib.cutespmm_mtx_arrays(h, C.byref(rp), C.byref(cc), C.byref(vv)))
+            self.M, self.K, self.nnz = M.value, K.value, nnz.value
+            self.rowPtr = np.ctypeslib.as_array(rp, shape=(self.M + 1,)).copy()
+            self.cols = np.ctypeslib.as_array(cc, shape=(max(self.nnz, 1),))[: self.nnz].copy()
+            self.vals = np.ctypeslib.as_array(vv, shape=(max(self.nnz, 1),))[: self.nnz].copy()
+        finally:
+            lib.cutespmm_mtx_close(h)

@@ -1,0 +1,361 @@
+// The extern "C" surface declared in include/cutespmm.h: plan life cycle, execution, sharding.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "device_plan.hpp"
+#include "plan.hpp"
+
+using namespace cutespmm;
+
+namespace {
+thread_local std::string g_last_error;
+
+int fail(int status, const std::string &msg)
+{
+    g_last_error = msg;
+    return status;
+}
+int fail_cuda(cudaError_t e, const char *what)
+{
+    g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return e == cudaErrorMemoryAllocation ? CUTESPMM_ENOMEM : CUTESPMM_ECUDA;
+}
+
+template <class T> cudaError_t upload(const std::vector<T> &h, void **d, uint64_t &bytes)
+{
+    *d = nullptr;
+    if (h.empty()) return cudaSuccess;
+    cudaError_t e = cudaMalloc(d, h.size() * sizeof(T));
+    if (e != cudaSuccess) return e;
+    bytes += h.size() * sizeof(T);
+    return cudaMemcpy(*d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice);
+}
+}  // namespace
+
+struct cutespmm_plan {
+    HostPlan host;
+    bool on_device = false;
+    int device = -1;
+    int sm_count = 0;
+    uint64_t device_bytes = 0;
+    // device arrays
+    void *d_row_ptr = nullptr, *d_pairs = nullptr, *d_tiles = nullptr, *d_chunks = nullptr, *d_long_rows = nullptr;
+    void *d_items = nullptr, *d_bcols = nullptr, *d_bmaps = nullptr, *d_bvals = nullptr;
+    float *d_scratch = nullptr;
+    uint32_t *d_status = nullptr;
+    uint32_t num_row_chunks = 0;
+    // staging for the host-buffer call
+    float *d_B = nullptr, *d_C = nullptr;
+    uint64_t staged_B = 0, staged_C = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+
+    ~cutespmm_plan()
+    {
+        if (!on_device) return;
+        int cur = -1;
+        cudaGetDevice(&cur);
+        if (cur != device) cudaSetDevice(device);
+        for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_items, d_bcols, d_bmaps, d_bvals,
+                        (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
+            if (p) cudaFree(p);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+        if (cur != device && cur >= 0) cudaSetDevice(cur);
+    }
+};
+
+extern "C" {
+
+const char *cutespmm_status_string(int status)
+{
+    switch (status) {
+        case CUTESPMM_OK: return "success";
+        case CUTESPMM_EINVAL: return "invalid argument";
+        case CUTESPMM_ENOMEM: return "out of memory";
+        case CUTESPMM_ECUDA: return "CUDA error";
+        case CUTESPMM_EUNSUPPORTED: return "unsupported";
+        case CUTESPMM_EIO: return "I/O error";
+        case CUTESPMM_ETIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+const char *cutespmm_last_error(void) { return g_last_error.c_str(); }
+int cutespmm_version(void) { return 100; }
+
+static int build_common(cutespmm_plan_t **out, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
+                        const float *vals, const cutespmm_options_t *opts)
+{
+    if (!out) return fail(CUTESPMM_EINVAL, "plan is NULL");
+    *out = nullptr;
+    cutespmm_plan *p = new (std::nothrow) cutespmm_plan();
+    if (!p) return fail(CUTESPMM_ENOMEM, "host allocation failed");
+    std::string err;
+    int st;
+    try {
+        st = build_host_plan(p->host, M, K, rowPtr, cols, vals, opts, err);
+    } catch (const std::bad_alloc &) {
+        st = CUTESPMM_ENOMEM;
+        err = "host allocation failed while building the plan";
+    }
+    if (st != CUTESPMM_OK) {
+        delete p;
+        return fail(st, err);
+    }
+    *out = p;
+    return CUTESPMM_OK;
+}
+
+int cutespmm_plan_build_host(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint64_t *rowPtr,
+                             const uint32_t *cols, const float *vals, const cutespmm_options_t *opts)
+{
+    return build_common(plan, M, K, rowPtr, cols, vals, opts);
+}
+
+int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
+                         const float *vals, const cutespmm_options_t *opts)
+{
+    // fail before the (possibly long) host build when there is no usable device
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice (libcutespmm needs a CUDA device; there is no CPU path)");
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetDeviceProperties");
+    if (prop.major < 10)
+        return fail(CUTESPMM_EUNSUPPORTED, "this library is built for sm_100a (B200) only; found compute capability " +
+                                               std::to_string(prop.major) + "." + std::to_string(prop.minor));
+    int st = build_common(plan, M, K, rowPtr, cols, vals, opts);
+    if (st != CUTESPMM_OK) return st;
+    cutespmm_plan *p = *plan;
+    HostPlan &h = p->host;
+    p->device = dev;
+    p->sm_count = prop.multiProcessorCount;
+    p->on_device = true;
+    p->num_row_chunks = 0;
+    for (const Chunk &c : h.chunks)
+        if (c.j1 > c.j0) ++p->num_row_chunks;  // row chunks come first; brick-piece slots carry no nonzeros
+    uint64_t &by = p->device_bytes;
+#define UP(vec, ptr)                                                   \
+    if ((e = upload(vec, &ptr, by)) != cudaSuccess) {                  \
+        delete p;                                                      \
+        *plan = nullptr;                                               \
+        return fail_cuda(e, "uploading " #vec);                        \
+    }
+    UP(h.row_ptr, p->d_row_ptr)
+    UP(h.pairs, p->d_pairs)
+    UP(h.tile_rows, p->d_tiles)
+    UP(h.chunks, p->d_chunks)
+    UP(h.long_rows, p->d_long_rows)
+    UP(h.panel_items, p->d_items)
+    UP(h.brick_cols, p->d_bcols)
+    UP(h.brick_maps, p->d_bmaps)
+    UP(h.brick_vals, p->d_bvals)
+#undef UP
+    const uint64_t scratch = (uint64_t)h.chunks.size() * kScratchCols * sizeof(float);
+    if (scratch) {
+        if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) { delete p; *plan = nullptr; return fail_cuda(e, "scratch"); }
+        by += scratch;
+    }
+    if ((e = cudaMalloc(&p->d_status, 256)) != cudaSuccess || (e = cudaMemset(p->d_status, 0, 256)) != cudaSuccess) {
+        delete p; *plan = nullptr; return fail_cuda(e, "status word");
+    }
+    by += 256;
+    return CUTESPMM_OK;
+}
+
+int cutespmm_plan_create_u32(cutespmm_plan_t **plan, uint32_t M, uint32_t K, const uint32_t *rowPtr,
+                             const uint32_t *cols, const float *vals, const cutespmm_options_t *opts)
+{
+    if (!rowPtr) return fail(CUTESPMM_EINVAL, "rowPtr is NULL");
+    std::vector<uint64_t> rp((size_t)M + 1);
+    for (size_t i = 0; i <= M; ++i) rp[i] = rowPtr[i];
+    return cutespmm_plan_create(plan, M, K, rp.data(), cols, vals, opts);
+}
+
+int cutespmm_plan_destroy(cutespmm_plan_t *plan)
+{
+    delete plan;
+    return CUTESPMM_OK;
+}
+
+int cutespmm_plan_info(const cutespmm_plan_t *p, cutespmm_plan_info_t *info)
+{
+    if (!p || !info) return fail(CUTESPMM_EINVAL, "null argument");
+    const HostPlan &h = p->host;
+    std::memset(info, 0, sizeof(*info));
+    info->M = h.M; info->K = h.K; info->nnz = h.nnz;
+    info->num_panels = h.num_panels();
+    info->num_blocks = h.blocked_row_ptr.empty() ? 0 : h.blocked_row_ptr.back();
+    info->num_tiles = h.tile_rows.size() / 2;
+    info->num_long_rows = h.long_rows.size();
+    info->num_chunks = h.chunks.size();
+    info->brick_panels = h.brick_panels;
+    info->num_bricks = h.num_bricks;
+    info->device_bytes = p->device_bytes;
+    info->scratch_bytes_per_col = h.chunks.size() * sizeof(float);
+    return CUTESPMM_OK;
+}
+
+int cutespmm_plan_blocked_row_ptr(const cutespmm_plan_t *p, uint32_t *out)
+{
+    if (!p || !out) return fail(CUTESPMM_EINVAL, "null argument");
+    std::memcpy(out, p->host.blocked_row_ptr.data(), p->host.blocked_row_ptr.size() * sizeof(uint32_t));
+    return CUTESPMM_OK;
+}
+int cutespmm_plan_active_cols(const cutespmm_plan_t *p, uint32_t *out)
+{
+    if (!p || !out) return fail(CUTESPMM_EINVAL, "null argument");
+    std::memcpy(out, p->host.active_cols.data(), p->host.active_cols.size() * sizeof(uint32_t));
+    return CUTESPMM_OK;
+}
+int cutespmm_plan_decode_csr(const cutespmm_plan_t *p, uint64_t *rowPtr, uint32_t *cols, float *vals)
+{
+    if (!p || !rowPtr || (p->host.nnz && (!cols || !vals))) return fail(CUTESPMM_EINVAL, "null argument");
+    decode_host_plan(p->host, rowPtr, cols, vals);
+    return CUTESPMM_OK;
+}
+
+static RowsArgs rows_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
+{
+    RowsArgs a{};
+    a.row_ptr = static_cast<const uint32_t *>(p->d_row_ptr);
+    a.pairs = p->d_pairs;
+    a.tiles = p->d_tiles;
+    a.chunks = p->d_chunks;
+    a.long_rows = p->d_long_rows;
+    a.num_tiles = (uint32_t)(p->host.tile_rows.size() / 2);
+    a.num_chunks = p->num_row_chunks;
+    a.num_long_rows = (uint32_t)p->host.long_rows.size();
+    a.split_nnz = p->host.opts.split_nnz;
+    a.B = B; a.C = C; a.scratch = p->d_scratch;
+    a.ldb = ldb; a.ldc = ldc; a.ld_scratch = kScratchCols;
+    a.N = N;
+    return a;
+}
+static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
+{
+    BrickArgs a{};
+    a.items = p->d_items;
+    a.cols = static_cast<const uint32_t *>(p->d_bcols);
+    a.maps = static_cast<const uint32_t *>(p->d_bmaps);
+    a.vals = static_cast<const float *>(p->d_bvals);
+    a.num_items = (uint32_t)p->host.panel_items.size();
+    a.M = (uint32_t)p->host.M;
+    a.B = B; a.C = C; a.scratch = p->d_scratch;
+    a.ldb = ldb; a.ldc = ldc; a.ld_scratch = kScratchCols;
+    a.N = N;
+    a.status = p->d_status;
+    return a;
+}
+
+int cutespmm_spmm_launch_count(const cutespmm_plan_t *p, uint32_t N)
+{
+    if (!p || N == 0) return 0;
+    const uint32_t windows = (N + kScratchCols - 1) / kScratchCols;
+    int per = 0;
+    if (!p->host.tile_rows.empty() || p->num_row_chunks) per += 1;
+    if (!p->host.panel_items.empty()) per += 1;
+    if (!p->host.long_rows.empty()) per += 1;
+    return per * (int)windows;
+}
+
+int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N,
+                  void *stream)
+{
+    if (!p) return fail(CUTESPMM_EINVAL, "plan is NULL");
+    if (!p->on_device) return fail(CUTESPMM_EUNSUPPORTED, "host-only plan: build it with cutespmm_plan_create on a CUDA device to execute it");
+    if (N == 0) return CUTESPMM_OK;
+    if (!C && p->host.M) return fail(CUTESPMM_EINVAL, "C is NULL");
+    if (!B && p->host.nnz) return fail(CUTESPMM_EINVAL, "B is NULL");
+    if (ldb < N || ldc < N) return fail(CUTESPMM_EINVAL, "leading dimension smaller than N");
+    if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 3) return fail(CUTESPMM_EINVAL, "B and C must be 4-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (p->host.M == 0) return CUTESPMM_OK;
+    for (uint32_t n0 = 0; n0 < N; n0 += kScratchCols) {
+        const uint32_t nw = N - n0 < kScratchCols ? N - n0 : kScratchCols;
+        cudaError_t e;
+        if (!p->host.panel_items.empty()) {
+            BrickArgs ba = brick_args(p, B + n0, ldb, C + n0, ldc, nw);
+            if (!brick_supports(nw, ldb, ldc, ba.B, ba.C))
+                return fail(CUTESPMM_EUNSUPPORTED, "the tensor-core path needs 16-byte aligned B and C, leading dimensions that are multiples of 4 and N a multiple of 32; build the plan with CUTESPMM_PATH_ROWS for other shapes");
+            if ((e = launch_brick(ba, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "brick kernel launch");
+        }
+        RowsArgs ra = rows_args(p, B + n0, ldb, C + n0, ldc, nw);
+        if ((e = launch_rows(ra, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "row kernel launch");
+        if ((e = launch_fixup(ra, s)) != cudaSuccess) return fail_cuda(e, "fix-up kernel launch");
+    }
+    return CUTESPMM_OK;
+}
+
+int cutespmm_spmm_host(cutespmm_plan_t *p, const float *B_host, uint64_t ldb, float *C_host, uint64_t ldc, uint32_t N,
+                       void *stream, float *kernel_ms)
+{
+    if (!p) return fail(CUTESPMM_EINVAL, "plan is NULL");
+    if (!p->on_device) return fail(CUTESPMM_EUNSUPPORTED, "host-only plan cannot execute");
+    if (N == 0) return CUTESPMM_OK;
+    if (!B_host || !C_host) return fail(CUTESPMM_EINVAL, "null host buffer");
+    if (ldb < N || ldc < N) return fail(CUTESPMM_EINVAL, "leading dimension smaller than N");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    const uint64_t ldd = (N + 3) / 4 * 4;  // device leading dimension: rows start 16-byte aligned
+    const uint64_t needB = p->host.K * ldd * sizeof(float), needC = p->host.M * ldd * sizeof(float);
+    if (needB > p->staged_B) {
+        if (p->d_B) cudaFree(p->d_B);
+        p->d_B = nullptr; p->staged_B = 0;
+        if ((e = cudaMalloc(&p->d_B, needB)) != cudaSuccess) return fail_cuda(e, "staging buffer for B");
+        p->staged_B = needB;
+    }
+    if (needC > p->staged_C) {
+        if (p->d_C) cudaFree(p->d_C);
+        p->d_C = nullptr; p->staged_C = 0;
+        if ((e = cudaMalloc(&p->d_C, needC)) != cudaSuccess) return fail_cuda(e, "staging buffer for C");
+        p->staged_C = needC;
+    }
+    if (!p->ev0) {
+        if ((e = cudaEventCreate(&p->ev0)) != cudaSuccess || (e = cudaEventCreate(&p->ev1)) != cudaSuccess)
+            return fail_cuda(e, "cudaEventCreate");
+    }
+    if (p->host.K &&
+        (e = cudaMemcpy2DAsync(p->d_B, ldd * sizeof(float), B_host, ldb * sizeof(float), (size_t)N * sizeof(float),
+                               p->host.K, cudaMemcpyHostToDevice, s)) != cudaSuccess)
+        return fail_cuda(e, "copy of B to the device");
+    cudaEventRecord(p->ev0, s);
+    int st = cutespmm_spmm(p, p->d_B, ldd, p->d_C, ldd, N, s);
+    if (st != CUTESPMM_OK) return st;
+    cudaEventRecord(p->ev1, s);
+    if (p->host.M &&
+        (e = cudaMemcpy2DAsync(C_host, ldc * sizeof(float), p->d_C, ldd * sizeof(float), (size_t)N * sizeof(float),
+                               p->host.M, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+        return fail_cuda(e, "copy of C to the host");
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return fail_cuda(e, "SpMM execution");
+    if (kernel_ms) cudaEventElapsedTime(kernel_ms, p->ev0, p->ev1);
+    uint32_t dev_status = 0;
+    cutespmm_plan_device_status(p, &dev_status);
+    if (dev_status) return fail(CUTESPMM_ETIMEOUT, "a device-side wait ran out (status " + std::to_string(dev_status) + ")");
+    return CUTESPMM_OK;
+}
+
+int cutespmm_plan_device_status(const cutespmm_plan_t *p, uint32_t *status)
+{
+    if (!p || !status) return fail(CUTESPMM_EINVAL, "null argument");
+    *status = 0;
+    if (!p->on_device) return CUTESPMM_OK;
+    cudaError_t e = cudaMemcpy(status, p->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(e, "reading the status word");
+    return CUTESPMM_OK;
+}
+
+int cutespmm_partition_rows(uint64_t M, const uint64_t *rowPtr, uint32_t nparts, uint32_t align_rows, uint32_t row_cost,
+                            uint64_t *bounds)
+{
+    std::string err;
+    int st = partition_rows(M, rowPtr, nparts, align_rows, row_cost, bounds, err);
+    return st == CUTESPMM_OK ? st : fail(st, err);
+}
+
+}  // extern "C"

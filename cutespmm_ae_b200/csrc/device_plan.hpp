@@ -1,0 +1,47 @@
+// Kernel argument blocks and launcher prototypes shared by the C ABI and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace cutespmm {
+
+// Arguments of the row-gather kernel and of the fix-up kernel that follows it.
+struct RowsArgs {
+    const uint32_t *row_ptr;   // M+1 offsets into pairs
+    const void *pairs;         // nnz x {col, fp32 bits}
+    const void *tiles;         // num_tiles x {row_begin, row_end}
+    const void *chunks;        // num_chunks x {row, j0, j1, slot}
+    const void *long_rows;     // num_long_rows x {row, slot0, slot1, -}
+    uint32_t num_tiles, num_chunks, num_long_rows, split_nnz;
+    const float *B;            // K x N window, leading dimension ldb
+    float *C;                  // M x N window, leading dimension ldc
+    float *scratch;            // partial sums, leading dimension ld_scratch
+    uint64_t ldb, ldc, ld_scratch;
+    uint32_t N;
+};
+
+cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s);
+cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
+int rows_kernel_count(const RowsArgs &a);
+
+// Arguments of the tensor-core brick kernel.
+struct BrickArgs {
+    const void *items;           // num_items x PanelItem
+    const uint32_t *cols;        // active columns per item
+    const uint32_t *maps;        // 4 words per brick
+    const float *vals;           // packed values
+    uint32_t num_items;
+    uint32_t M;
+    const float *B;
+    float *C;
+    float *scratch;
+    uint64_t ldb, ldc, ld_scratch;
+    uint32_t N;
+    uint32_t *status;            // device status word (0 = fine)
+};
+
+cudaError_t launch_brick(const BrickArgs &a, int sm_count, cudaStream_t s);
+bool brick_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const void *C);
+
+}  // namespace cutespmm

@@ -1,0 +1,274 @@
+// Host preprocessing: CSR -> device-ready arrays and nnz-balanced work lists.
+//
+// Takes the place of HRPB::DATASTRUCT (reference data.cu:94-335) and of SPMM_TC::partition
+// (reference spmm.cu:691-822).  Differences that matter to a caller:
+//   * memory is proportional to the input (the reference allocates (M/16)*(K/16)+1 offsets,
+//     data.cu:91, and three K*64-word scratch arrays, data.cu:95-98);
+//   * correct for any number of OpenMP threads (the reference indexes per-thread scratch by the
+//     thread id it asked for, data.cu:105-113);
+//   * rows need not be sorted; every nonzero is kept;
+//   * the work list is balanced by nonzeros and does not depend on a per-GPU occupancy table
+//     (spmm.cu:290-690 has no entry for a 148-SM part).
+#include "plan.hpp"
+
+#include <algorithm>
+#include <cstring>
+#include <numeric>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace cutespmm {
+
+void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols);  // brick_build.cpp
+
+static void fill_default_options(cutespmm_options_t &o, const cutespmm_options_t *in)
+{
+    std::memset(&o, 0, sizeof(o));
+    if (in) {
+        const size_t n = std::min<size_t>(in->struct_size ? in->struct_size : sizeof(o), sizeof(o));
+        std::memcpy(&o, in, n);
+    }
+    o.struct_size = sizeof(o);
+    if (o.split_nnz == 0) o.split_nnz = kDefaultSplitNnz;
+    if (o.tile_nnz == 0) o.tile_nnz = kDefaultTileCost;
+    if (o.brick_density <= 0.0f) o.brick_density = 0.125f;
+}
+
+// Distinct columns of every 16-row panel, ascending: the HRPB view (data.cu:116-149 counts them,
+// data.cu:188-209 sorts them).  Fills blocked_row_ptr / active_cols and returns the per-panel counts.
+static std::vector<uint32_t> analyze_panels(HostPlan &p)
+{
+    const uint64_t P = p.num_panels();
+    std::vector<uint32_t> ncols(P, 0);
+    // pass 1: count distinct columns per panel
+    std::vector<uint64_t> col_off(P + 1, 0);
+#pragma omp parallel
+    {
+        std::vector<uint32_t> buf;
+#pragma omp for schedule(dynamic, 256)
+        for (int64_t q = 0; q < (int64_t)P; ++q) {
+            const uint64_t r0 = (uint64_t)q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
+            const uint32_t j0 = p.row_ptr[r0], j1 = p.row_ptr[r1];
+            buf.resize(j1 - j0);
+            for (uint32_t j = j0; j < j1; ++j) buf[j - j0] = p.pairs[j].col;
+            std::sort(buf.begin(), buf.end());
+            ncols[q] = (uint32_t)(std::unique(buf.begin(), buf.end()) - buf.begin());
+        }
+    }
+    p.blocked_row_ptr.assign(P + 1, 0);
+    for (uint64_t q = 0; q < P; ++q) {
+        const uint32_t nb = (ncols[q] + kBlockCols - 1) / kBlockCols;
+        p.blocked_row_ptr[q + 1] = p.blocked_row_ptr[q] + nb;
+        col_off[q + 1] = col_off[q] + (uint64_t)nb * kBlockCols;
+    }
+    p.active_cols.assign(col_off[P], 0u);
+    // pass 2: write them
+#pragma omp parallel
+    {
+        std::vector<uint32_t> buf;
+#pragma omp for schedule(dynamic, 256)
+        for (int64_t q = 0; q < (int64_t)P; ++q) {
+            const uint64_t r0 = (uint64_t)q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
+            const uint32_t j0 = p.row_ptr[r0], j1 = p.row_ptr[r1];
+            buf.resize(j1 - j0);
+            for (uint32_t j = j0; j < j1; ++j) buf[j - j0] = p.pairs[j].col;
+            std::sort(buf.begin(), buf.end());
+            const size_t n = std::unique(buf.begin(), buf.end()) - buf.begin();
+            std::copy(buf.begin(), buf.begin() + n, p.active_cols.begin() + col_off[q]);
+        }
+    }
+    return ncols;
+}
+
+// Cuts the rows that the row kernel executes into tiles of about equal cost.  A tile is a run of
+// consecutive rows inside one stretch of row-kernel panels; long rows cost nothing here (their
+// nonzeros are executed as chunks).
+static void build_tiles(HostPlan &p)
+{
+    const uint64_t P = p.num_panels();
+    const uint32_t split = p.opts.split_nnz;
+    const uint64_t target = p.opts.tile_nnz;
+    p.tile_rows.clear();
+    p.chunks.clear();
+    p.long_rows.clear();
+    uint64_t q = 0;
+    while (q < P) {
+        if (p.row_path[q]) { ++q; continue; }
+        uint64_t q1 = q;
+        while (q1 < P && !p.row_path[q1]) ++q1;
+        const uint64_t r_end = std::min<uint64_t>(p.M, q1 * kPanelRows);
+        uint64_t r = q * kPanelRows;
+        uint64_t begin = r, cost = 0;
+        for (; r < r_end; ++r) {
+            const uint32_t len = p.row_ptr[r + 1] - p.row_ptr[r];
+            if (len > split) {
+                LongRow lr{(uint32_t)r, (uint32_t)p.chunks.size(), 0, 0};
+                for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; j += split)
+                    p.chunks.push_back(Chunk{(uint32_t)r, j, std::min<uint32_t>(j + split, p.row_ptr[r + 1]),
+                                             (uint32_t)p.chunks.size()});
+                lr.slot1 = (uint32_t)p.chunks.size();
+                p.long_rows.push_back(lr);
+                cost += kRowCost;
+            } else {
+                cost += len + kRowCost;
+            }
+            if (cost >= target || r + 1 - begin >= kMaxTileRows) {
+                p.tile_rows.push_back((uint32_t)begin);
+                p.tile_rows.push_back((uint32_t)(r + 1));
+                begin = r + 1;
+                cost = 0;
+            }
+        }
+        if (begin < r_end) {
+            p.tile_rows.push_back((uint32_t)begin);
+            p.tile_rows.push_back((uint32_t)r_end);
+        }
+        q = q1;
+    }
+}
+
+int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
+                    const float *vals, const cutespmm_options_t *opts, std::string &err)
+{
+    if (!rowPtr) { err = "rowPtr is NULL"; return CUTESPMM_EINVAL; }
+    if (M >= (1ull << 32) - kPanelRows || K >= (1ull << 32)) { err = "M and K must be below 2^32"; return CUTESPMM_EUNSUPPORTED; }
+    if (rowPtr[0] != 0) { err = "rowPtr[0] must be 0"; return CUTESPMM_EINVAL; }
+    const uint64_t nnz = rowPtr[M];
+    if (nnz >= (1ull << 32)) { err = "more than 2^32-1 nonzeros in one plan: shard the rows"; return CUTESPMM_EUNSUPPORTED; }
+    if (nnz && (!cols || !vals)) { err = "cols/vals is NULL"; return CUTESPMM_EINVAL; }
+    if (opts && opts->path > CUTESPMM_PATH_BRICK) { err = "unknown path"; return CUTESPMM_EINVAL; }
+    fill_default_options(p.opts, opts);
+    p.M = M; p.K = K; p.nnz = nnz;
+
+    // validation + 32-bit row pointers
+    int bad = 0;
+    p.row_ptr.resize(M + 1);
+#pragma omp parallel for schedule(static) reduction(| : bad)
+    for (int64_t r = 0; r <= (int64_t)M; ++r) {
+        if (r < (int64_t)M && rowPtr[r + 1] < rowPtr[r]) bad |= 1;
+        if (rowPtr[r] > nnz) bad |= 1;
+        p.row_ptr[r] = (uint32_t)rowPtr[r];
+    }
+    if (bad & 1) { err = "rowPtr is not non-decreasing"; return CUTESPMM_EINVAL; }
+
+    // pairs, sorted by column inside each row (stable: equal columns keep input order)
+    p.pairs.resize(nnz);
+#pragma omp parallel for schedule(dynamic, 1024) reduction(| : bad)
+    for (int64_t r = 0; r < (int64_t)M; ++r) {
+        const uint64_t j0 = rowPtr[r], j1 = rowPtr[r + 1];
+        bool sorted = true;
+        for (uint64_t j = j0; j < j1; ++j) {
+            uint32_t vb;
+            std::memcpy(&vb, &vals[j], 4);
+            p.pairs[j] = Pair{cols[j], vb};
+            if (cols[j] >= K) bad |= 2;
+            if (j > j0 && cols[j] < cols[j - 1]) sorted = false;
+        }
+        if (!sorted)
+            std::stable_sort(p.pairs.begin() + j0, p.pairs.begin() + j1,
+                             [](const Pair &a, const Pair &b) { return a.col < b.col; });
+    }
+    if (bad & 2) { err = "column index out of range (>= K)"; return CUTESPMM_EINVAL; }
+
+    const std::vector<uint32_t> panel_ncols = analyze_panels(p);
+
+    // path per panel
+    const uint64_t P = p.num_panels();
+    p.row_path.assign(P, 0);
+    if (p.opts.path != CUTESPMM_PATH_ROWS) {
+#pragma omp parallel for schedule(static)
+        for (int64_t q = 0; q < (int64_t)P; ++q) {
+            const uint64_t r0 = (uint64_t)q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
+            const uint32_t n = p.row_ptr[r1] - p.row_ptr[r0];
+            if (n == 0) continue;  // empty panels: the row kernel writes their zeros
+            if (p.opts.path == CUTESPMM_PATH_BRICK) { p.row_path[q] = 1; continue; }
+            // AUTO: fill of the panel's 16 x (8*ceil(ncols/8)) dense image
+            const uint32_t padded = (panel_ncols[q] + kBrickCols - 1) / kBrickCols * kBrickCols;
+            const float fill = (float)n / (float)(kPanelRows * padded);
+            bool long_row = false;
+            for (uint64_t r = r0; r < r1; ++r) long_row |= (p.row_ptr[r + 1] - p.row_ptr[r]) > p.opts.split_nnz;
+            p.row_path[q] = (fill >= p.opts.brick_density && !long_row) ? 1 : 0;
+        }
+    }
+    build_tiles(p);
+    build_brick_part(p, panel_ncols);
+    return CUTESPMM_OK;
+}
+
+void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float *vals)
+{
+    // The pairs array holds every nonzero (both kernels' rows); the brick arrays are a second
+    // encoding of the brick panels.  Decode each part from the encoding its kernel reads.
+    const uint64_t P = p.num_panels();
+    std::vector<std::vector<std::pair<uint32_t, float>>> rows(p.M);
+    for (uint64_t q = 0; q < P; ++q) {
+        if (p.row_path[q]) continue;
+        const uint64_t r0 = q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
+        for (uint64_t r = r0; r < r1; ++r)
+            for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; ++j) {
+                float v;
+                std::memcpy(&v, &p.pairs[j].val_bits, 4);
+                rows[r].push_back({p.pairs[j].col, v});
+            }
+    }
+    for (const PanelItem &it : p.panel_items) {
+        const uint32_t nbricks = it.num_cols / kBrickCols;
+        uint32_t voff = it.val_begin;
+        for (uint32_t b = 0; b < nbricks; ++b) {
+            const uint32_t *map = &p.brick_maps[(size_t)(it.map_begin + b) * 4];
+            uint32_t cnt = 0;
+            for (uint32_t bit = 0; bit < 128; ++bit) {
+                if (!((map[bit >> 5] >> (bit & 31)) & 1u)) continue;
+                const uint32_t r = bit / kBrickCols, c = bit % kBrickCols;
+                rows[(size_t)it.panel * kPanelRows + r].push_back(
+                    {p.brick_cols[it.col_begin + b * kBrickCols + c], p.brick_vals[voff + cnt]});
+                ++cnt;
+            }
+            voff += (cnt + 3) / 4 * 4;
+        }
+    }
+    uint64_t off = 0;
+    for (uint64_t r = 0; r < p.M; ++r) {
+        rowPtr[r] = off;
+        std::stable_sort(rows[r].begin(), rows[r].end(),
+                         [](const auto &a, const auto &b) { return a.first < b.first; });
+        for (auto &e : rows[r]) {
+            cols[off] = e.first;
+            vals[off] = e.second;
+            ++off;
+        }
+    }
+    rowPtr[p.M] = off;
+}
+
+int partition_rows(uint64_t M, const uint64_t *rowPtr, uint32_t nparts, uint32_t align_rows, uint32_t row_cost,
+                   uint64_t *bounds, std::string &err)
+{
+    if (!rowPtr || !bounds || nparts == 0) { err = "bad argument"; return CUTESPMM_EINVAL; }
+    if (align_rows == 0) align_rows = 1;
+    const uint64_t total = (rowPtr[M] - rowPtr[0]) + (uint64_t)row_cost * M;
+    bounds[0] = 0;
+    uint64_t r = 0;
+    for (uint32_t k = 1; k < nparts; ++k) {
+        // smallest aligned r with cost(rows [0, r)) >= k/nparts of the total
+        const long double want = (long double)total * k / nparts;
+        uint64_t lo = r, hi = M;
+        while (lo < hi) {
+            const uint64_t mid = lo + (hi - lo) / 2;
+            const long double c = (long double)(rowPtr[mid] - rowPtr[0]) + (long double)row_cost * mid;
+            if (c < want) lo = mid + 1; else hi = mid;
+        }
+        // round to the nearer multiple of align_rows, staying monotone and inside [0, M]
+        uint64_t down = lo / align_rows * align_rows, up = std::min<uint64_t>(M, down + align_rows);
+        auto cost_at = [&](uint64_t x) { return (long double)(rowPtr[x] - rowPtr[0]) + (long double)row_cost * x; };
+        uint64_t pick = (want - cost_at(down) <= cost_at(up) - want) ? down : up;
+        if (pick < r) pick = r;
+        bounds[k] = r = pick;
+    }
+    bounds[nparts] = M;
+    return CUTESPMM_OK;
+}
+
+}  // namespace cutespmm

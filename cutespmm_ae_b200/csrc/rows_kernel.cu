@@ -1,0 +1,224 @@
+// CUDA-core row-gather kernel: the path for rows whose 16x8 bricks are too empty to pay for a
+// tensor-core contraction (power-law graphs, uniform random matrices), and the executor of long
+// rows cut into chunks.
+//
+// In the reference every row panel goes through the brick kernel (kernel.cu:119-288), zero-filled
+// bricks included; its tile splitter (inc/splitter.hpp:34-124) that would send light tiles to CUDA
+// cores is never called.  Here a warp owns one row at a time: the lanes span the columns of B
+// (one float4 each at N = 128, so a row of B is one coalesced 512-byte request), the row's
+// (column, value) pairs are fetched 32 at a time with one coalesced 8-byte load per lane and handed
+// round with shuffles, and the products are accumulated in fp32 registers in storage order.  The
+// eight warps of a block take interleaved rows of one scheduling tile, so rows that share columns
+// (stencils, block structure) meet in L1.  C rows are written once with streaming stores; nothing
+// is read-modify-written and no atomics are used: a long row is cut into chunks whose partial sums
+// go to a scratch matrix and are added, in order, by a second small kernel.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "device_plan.hpp"
+
+namespace cutespmm {
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr unsigned kFull = 0xffffffffu;
+
+template <int VEC> struct Vec;
+template <> struct Vec<4> { using T = float4; };
+template <> struct Vec<2> { using T = float2; };
+template <> struct Vec<1> { using T = float; };
+
+__device__ __forceinline__ float4 ldg_b(const float4 *p) { return __ldg(p); }
+__device__ __forceinline__ float2 ldg_b(const float2 *p) { return __ldg(p); }
+__device__ __forceinline__ float ldg_b(const float *p) { return __ldg(p); }
+
+__device__ __forceinline__ void fma_vec(float4 &a, float v, const float4 &b)
+{
+    a.x = fmaf(v, b.x, a.x); a.y = fmaf(v, b.y, a.y); a.z = fmaf(v, b.z, a.z); a.w = fmaf(v, b.w, a.w);
+}
+__device__ __forceinline__ void fma_vec(float2 &a, float v, const float2 &b)
+{
+    a.x = fmaf(v, b.x, a.x); a.y = fmaf(v, b.y, a.y);
+}
+__device__ __forceinline__ void fma_vec(float &a, float v, const float &b) { a = fmaf(v, b, a); }
+
+__device__ __forceinline__ void zero_vec(float4 &a) { a = make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ void zero_vec(float2 &a) { a = make_float2(0.f, 0.f); }
+__device__ __forceinline__ void zero_vec(float &a) { a = 0.f; }
+
+__device__ __forceinline__ void store_stream(float4 *p, const float4 &v) { __stcs(p, v); }
+__device__ __forceinline__ void store_stream(float2 *p, const float2 &v) { __stcs(p, v); }
+__device__ __forceinline__ void store_stream(float *p, const float &v) { __stcs(p, v); }
+
+// acc[ch] += sum over nonzeros [j0, j1) of val * B[col][lane's columns].  `bl` points at this lane's
+// first column of row 0 of B; ok[ch] says whether the lane's ch-th column group exists (ragged N).
+template <int VEC, int CH, bool FULL>
+__device__ __forceinline__ void accumulate(typename Vec<VEC>::T (&acc)[CH], const uint2 *__restrict__ pairs,
+                                           uint32_t j0, uint32_t j1, const float *__restrict__ bl, uint64_t ldb,
+                                           const bool (&ok)[CH], int lane)
+{
+    using V = typename Vec<VEC>::T;
+    constexpr int U = (CH == 1) ? 4 : 2;  // nonzeros in flight per step
+    for (uint32_t j = j0; j < j1; j += 32) {
+        const uint32_t n = min(32u, j1 - j);
+        uint2 pr = make_uint2(0u, 0u);
+        if ((uint32_t)lane < n) pr = __ldcs(pairs + j + lane);
+        uint32_t k = 0;
+        for (; k + U <= n; k += U) {
+            float v[U];
+            V b[U][CH];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t c = __shfl_sync(kFull, pr.x, k + u);
+                v[u] = __uint_as_float(__shfl_sync(kFull, pr.y, k + u));
+                const float *row = bl + (uint64_t)c * ldb;
+#pragma unroll
+                for (int ch = 0; ch < CH; ++ch) {
+                    if (FULL || ok[ch]) b[u][ch] = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
+                    else zero_vec(b[u][ch]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int ch = 0; ch < CH; ++ch) fma_vec(acc[ch], v[u], b[u][ch]);
+        }
+        for (; k < n; ++k) {
+            const uint32_t c = __shfl_sync(kFull, pr.x, k);
+            const float v = __uint_as_float(__shfl_sync(kFull, pr.y, k));
+            const float *row = bl + (uint64_t)c * ldb;
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) {
+                if (FULL || ok[ch]) {
+                    const V b = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
+                    fma_vec(acc[ch], v, b);
+                }
+            }
+        }
+    }
+}
+
+template <int VEC, int CH, bool FULL>
+__global__ void __launch_bounds__(kWarps * 32) spmm_rows_kernel(RowsArgs a)
+{
+    using V = typename Vec<VEC>::T;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t col0 = blockIdx.y * (32 * VEC * CH) + lane * VEC;  // this lane's first column
+    bool ok[CH];
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) ok[ch] = FULL || (col0 + ch * 32 * VEC < a.N);
+    const float *bl = a.B + col0;
+    const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
+
+    // chunks of long rows first: they are the largest single work items
+    {
+        const uint32_t gw = blockIdx.x * kWarps + warp, nw = gridDim.x * kWarps;
+        for (uint32_t c = gw; c < a.num_chunks; c += nw) {
+            const uint4 ck = __ldg(reinterpret_cast<const uint4 *>(a.chunks) + c);  // row, j0, j1, slot
+            V acc[CH];
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
+            accumulate<VEC, CH, FULL>(acc, pairs, ck.y, ck.z, bl, a.ldb, ok, lane);
+            float *out = a.scratch + (uint64_t)ck.w * a.ld_scratch + col0;
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch)
+                if (FULL || ok[ch]) *reinterpret_cast<V *>(out + ch * 32 * VEC) = acc[ch];
+        }
+    }
+
+    for (uint32_t t = blockIdx.x; t < a.num_tiles; t += gridDim.x) {
+        const uint2 tr = __ldg(reinterpret_cast<const uint2 *>(a.tiles) + t);  // rows [x, y)
+        for (uint32_t r = tr.x + warp; r < tr.y; r += kWarps) {
+            const uint32_t j0 = __ldg(a.row_ptr + r), j1 = __ldg(a.row_ptr + r + 1);
+            if (j1 - j0 > a.split_nnz) continue;  // long row: done as chunks, written by the fix-up kernel
+            V acc[CH];
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
+            accumulate<VEC, CH, FULL>(acc, pairs, j0, j1, bl, a.ldb, ok, lane);
+            float *out = a.C + (uint64_t)r * a.ldc + col0;
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch)
+                if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(out + ch * 32 * VEC), acc[ch]);
+        }
+    }
+}
+
+// C[row] = scratch[slot0] + scratch[slot0+1] + ... (in slot order: deterministic).
+__global__ void __launch_bounds__(128) spmm_fixup_kernel(const uint4 *__restrict__ long_rows, uint32_t num_long_rows,
+                                                         const float *__restrict__ scratch, uint64_t ld_scratch,
+                                                         float *__restrict__ C, uint64_t ldc, uint32_t N)
+{
+    for (uint32_t i = blockIdx.x; i < num_long_rows; i += gridDim.x) {
+        const uint4 lr = __ldg(long_rows + i);  // row, slot0, slot1
+        for (uint32_t n = threadIdx.x; n < N; n += blockDim.x) {
+            float s = 0.f;
+            for (uint32_t k = lr.y; k < lr.z; ++k) s += scratch[(uint64_t)k * ld_scratch + n];
+            __stcs(C + (uint64_t)lr.x * ldc + n, s);
+        }
+    }
+}
+
+template <int VEC, int CH, bool FULL>
+cudaError_t launch_rows_t(const RowsArgs &a, uint32_t slabs, int sm_count, cudaStream_t s)
+{
+    static int blocks_per_sm = 0;  // same for every device of one model; queried once
+    if (blocks_per_sm == 0) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, spmm_rows_kernel<VEC, CH, FULL>, kWarps * 32, 0);
+        if (e != cudaSuccess) return e;
+        blocks_per_sm = n > 0 ? n : 1;
+    }
+    const uint64_t want = (uint64_t)sm_count * blocks_per_sm;
+    uint64_t work = a.num_tiles > (a.num_chunks + kWarps - 1) / kWarps ? a.num_tiles : (a.num_chunks + kWarps - 1) / kWarps;
+    uint32_t gx = (uint32_t)(work < want ? work : want);
+    if (slabs > 1) gx = (gx + slabs - 1) / slabs;  // keep the whole grid about one resident wave
+    if (gx == 0) gx = 1;
+    spmm_rows_kernel<VEC, CH, FULL><<<dim3(gx, slabs), kWarps * 32, 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int rows_kernel_count(const RowsArgs &a) { return (a.num_tiles || a.num_chunks) ? 1 : 0; }
+
+// Picks the widest vector the pointers, leading dimensions and N allow.
+cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s)
+{
+    if (a.num_tiles == 0 && a.num_chunks == 0) return cudaSuccess;
+    const uintptr_t pb = reinterpret_cast<uintptr_t>(a.B), pc = reinterpret_cast<uintptr_t>(a.C),
+                    ps = reinterpret_cast<uintptr_t>(a.scratch);
+    const bool v4 = !((pb | pc | ps) & 15) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 3);
+    const bool v2 = !((pb | pc | ps) & 7) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 1);
+    const uint32_t N = a.N;
+#define CUTESPMM_GO(VEC, CH)                                                                   \
+    do {                                                                                       \
+        const uint32_t w = 32 * VEC * CH, slabs = (N + w - 1) / w;                             \
+        return (N % w == 0) ? launch_rows_t<VEC, CH, true>(a, slabs, sm_count, s)              \
+                            : launch_rows_t<VEC, CH, false>(a, slabs, sm_count, s);            \
+    } while (0)
+    if (v4 && N > 64) {
+        if (N >= 256) CUTESPMM_GO(4, 2);
+        CUTESPMM_GO(4, 1);
+    }
+    if (v2 && N > 32) {
+        if (N >= 128) CUTESPMM_GO(2, 2);
+        CUTESPMM_GO(2, 1);
+    }
+    if (N >= 64) CUTESPMM_GO(1, 2);
+    CUTESPMM_GO(1, 1);
+#undef CUTESPMM_GO
+}
+
+cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s)
+{
+    if (a.num_long_rows == 0) return cudaSuccess;
+    const uint32_t g = a.num_long_rows < 4096 ? a.num_long_rows : 4096;
+    spmm_fixup_kernel<<<g, 128, 0, s>>>(reinterpret_cast<const uint4 *>(a.long_rows), a.num_long_rows, a.scratch,
+                                        a.ld_scratch, a.C, a.ldc, a.N);
+    return cudaGetLastError();
+}
+
+}  // namespace cutespmm

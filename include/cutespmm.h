@@ -1,0 +1,161 @@
+/*
+ * libcutespmm -- C ABI of the B200 (sm_100a) sparse x dense product
+ *
+ *        C[M x N] = A_sparse[M x K] * B_dense[K x N]
+ *
+ * fp32 storage, fp32 accumulation.  Row-major B and C with leading dimensions.
+ * This is the boundary a host program binds instead of the reference project's
+ * header-included classes; every entry point names the reference interface it
+ * replaces (file:line inside aFatCa/cuTeSpMM_AE).
+ *
+ * Conventions
+ *   - every function returns a cutespmm_status_t (0 = success, negative = error)
+ *     and never exits or aborts the process (the reference's chkerr, inc.h:61-69,
+ *     calls exit(-1));  cutespmm_last_error() gives the message of the calling
+ *     thread's last failure;
+ *   - host arrays are borrowed for the duration of the call only;
+ *   - device pointers refer to the CUDA device that was current when the plan
+ *     was created; all GPU work is ordered on the stream the caller passes
+ *     (a cudaStream_t cast to void*, NULL = the legacy default stream the
+ *     reference uses, spmm.cu:171-174);
+ *   - cutespmm_spmm performs no allocation: the scratch it needs belongs to
+ *     the plan.
+ */
+#ifndef CUTESPMM_H
+#define CUTESPMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    CUTESPMM_OK = 0,
+    CUTESPMM_EINVAL = -1,       /* bad argument: null pointer, index out of range, misaligned buffer */
+    CUTESPMM_ENOMEM = -2,       /* host or device allocation failed */
+    CUTESPMM_ECUDA = -3,        /* a CUDA runtime call or kernel launch failed (no device, ...) */
+    CUTESPMM_EUNSUPPORTED = -4, /* valid request outside what this build handles */
+    CUTESPMM_EIO = -5,          /* file could not be read or parsed */
+    CUTESPMM_ETIMEOUT = -6      /* a bounded device-side wait ran out (reported through the plan's status word) */
+} cutespmm_status_t;
+
+/* Which kernel family executes a plan. */
+typedef enum {
+    CUTESPMM_PATH_AUTO = 0,  /* per-panel choice by brick density */
+    CUTESPMM_PATH_ROWS = 1,  /* CUDA-core row-gather kernel for every row */
+    CUTESPMM_PATH_BRICK = 2  /* tensor-core brick kernel for every panel */
+} cutespmm_path_t;
+
+typedef struct {
+    uint32_t struct_size; /* sizeof(cutespmm_options_t), for forward compatibility */
+    uint32_t path;        /* cutespmm_path_t */
+    uint32_t split_nnz;   /* rows longer than this are cut into chunks of this many nonzeros (0 = default 1024) */
+    uint32_t tile_nnz;    /* nonzeros a thread block takes per scheduling tile (0 = default) */
+    float brick_density;  /* AUTO: panels whose 16x8 bricks are at least this full go to the brick kernel (0 = default) */
+    uint32_t reserved[3];
+} cutespmm_options_t;
+
+typedef struct {
+    uint64_t M, K, nnz;
+    uint64_t num_panels;      /* 16-row panels, ceil(M/16)                  (HRPB::numRowPanels, data.cu:60,87) */
+    uint64_t num_blocks;      /* 16-column blocks of active columns          (blockedRowPtr[numRowPanels], data.cu:145) */
+    uint64_t num_tiles;       /* scheduling tiles of the row kernel */
+    uint64_t num_long_rows;   /* rows cut into chunks */
+    uint64_t num_chunks;      /* chunks of long rows = rows of the partial-sum scratch */
+    uint64_t brick_panels;    /* panels executed by the tensor-core kernel */
+    uint64_t num_bricks;      /* non-empty 16x8 bricks in those panels */
+    uint64_t device_bytes;    /* device memory the plan owns */
+    uint64_t scratch_bytes_per_col; /* scratch bytes per column of B (times N gives the partial-sum scratch) */
+} cutespmm_plan_info_t;
+
+typedef struct cutespmm_plan cutespmm_plan_t;
+
+const char *cutespmm_status_string(int status);
+const char *cutespmm_last_error(void);
+/* major*10000 + minor*100 + patch */
+int cutespmm_version(void);
+
+/* ---- preprocessing -------------------------------------------------------------------------
+ * Replaces HRPB::HRPB / HRPB::DATASTRUCT (data.cu:80-335) and SPMM_TC::partition
+ * (spmm.cu:691-822): builds the device-resident form of A and the nnz-balanced work list and
+ * uploads both to the current CUDA device.  rowPtr has M+1 entries; cols/vals have rowPtr[M].
+ * Column indices may be in any order inside a row (the reference silently loses nonzeros when
+ * they are not ascending); duplicates are kept as separate terms.  Indices >= K, a decreasing
+ * rowPtr, or rowPtr[M] >= 2^32 are rejected (EINVAL / EUNSUPPORTED).  opts may be NULL. */
+int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint64_t *rowPtr,
+                         const uint32_t *cols, const float *vals, const cutespmm_options_t *opts);
+
+/* Same, with the 32-bit row pointers MTX_READER produces (IO.cu:7,32) and HRPB takes (data.cu:80). */
+int cutespmm_plan_create_u32(cutespmm_plan_t **plan, uint32_t M, uint32_t K, const uint32_t *rowPtr,
+                             const uint32_t *cols, const float *vals, const cutespmm_options_t *opts);
+
+/* Host-only build of the same plan: no CUDA call is made and the plan cannot execute.  For
+ * inspecting the work list and the packed format on a machine without a GPU. */
+int cutespmm_plan_build_host(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint64_t *rowPtr,
+                             const uint32_t *cols, const float *vals, const cutespmm_options_t *opts);
+
+int cutespmm_plan_destroy(cutespmm_plan_t *plan);
+int cutespmm_plan_info(const cutespmm_plan_t *plan, cutespmm_plan_info_t *info);
+
+/* HRPB::blockedRowPtr (data.cu:65,145,176-185): prefix sum over 16-row panels of
+ * ceil(distinct columns in the panel / 16).  out has num_panels+1 entries. */
+int cutespmm_plan_blocked_row_ptr(const cutespmm_plan_t *plan, uint32_t *out);
+/* HRPB::activeCols (data.cu:70,204-209): per panel its distinct columns ascending, zero-padded
+ * to a multiple of 16.  out has num_blocks*16 entries. */
+int cutespmm_plan_active_cols(const cutespmm_plan_t *plan, uint32_t *out);
+
+/* Decodes the plan's packed form of A back to CSR (columns ascending inside a row, duplicates
+ * merged in the brick part) -- the format round-trip check.  rowPtr: M+1, cols/vals: nnz. */
+int cutespmm_plan_decode_csr(const cutespmm_plan_t *plan, uint64_t *rowPtr, uint32_t *cols, float *vals);
+
+/* ---- execution -----------------------------------------------------------------------------
+ * Replaces SPMM_TC::run (spmm.cu:823-839) and the kernel SpMM<NUM_WARPS,ILP_LEVEL>
+ * (kernel.cu:119-288).  B: K x N device, row-major, leading dimension ldb >= N; C: M x N device,
+ * ldc >= N.  Every row of C is written (rows without nonzeros become 0), so C needs no memset
+ * (the reference relies on run.cu:43,49).  Any N >= 1. */
+int cutespmm_spmm(const cutespmm_plan_t *plan, const float *B_dev, uint64_t ldb, float *C_dev,
+                  uint64_t ldc, uint32_t N, void *stream);
+
+/* Host-buffer call in the style of the reference driver loop (run.cu:38-53) and of its
+ * float GPU_xxx(host pointers..., m, k, n, ...) wrappers (spmm.cu:860): copies B to the device,
+ * runs the product, copies C back, all on `stream`, and waits for it.  The device staging buffers
+ * belong to the plan and are (re)allocated only when N grows.  kernel_ms (may be NULL) receives
+ * the device time of the product alone. */
+int cutespmm_spmm_host(cutespmm_plan_t *plan, const float *B_host, uint64_t ldb, float *C_host,
+                       uint64_t ldc, uint32_t N, void *stream, float *kernel_ms);
+
+/* Number of kernels one cutespmm_spmm call launches for this plan and N. */
+int cutespmm_spmm_launch_count(const cutespmm_plan_t *plan, uint32_t N);
+
+/* Status word the kernels of this plan write on a failed bounded wait (0 = none).  Synchronises
+ * nothing: call after the stream has been synchronised. */
+int cutespmm_plan_device_status(const cutespmm_plan_t *plan, uint32_t *status);
+
+/* ---- sharding ------------------------------------------------------------------------------
+ * No counterpart in the reference (single GPU).  Cuts rows [0, M) into `nparts` contiguous
+ * ranges of about equal cost (nonzeros + row_cost per row), every boundary a multiple of
+ * `align_rows` (16 keeps row panels whole).  bounds has nparts+1 entries, bounds[0] = 0,
+ * bounds[nparts] = M.  Each rank then builds a plan over its own rows and C stays row-sharded. */
+int cutespmm_partition_rows(uint64_t M, const uint64_t *rowPtr, uint32_t nparts, uint32_t align_rows,
+                            uint32_t row_cost, uint64_t *bounds);
+
+/* ---- MatrixMarket loader -------------------------------------------------------------------
+ * Replaces MTX_READER (IO.cu:1-88).  pattern_only != 0 reproduces the reference exactly: every
+ * value is 1.0 (IO.cu:68,81), M and K are padded up to multiples of 16 (IO.cu:30-31), a
+ * "symmetric" header mirrors off-diagonal entries (IO.cu:16,42,77), entries keep file order
+ * inside a row.  pattern_only == 0 keeps the file's values (SparseCoo behaviour,
+ * inc/SparseCoo.hpp:91-157; 1.0 where the file has none). */
+typedef struct cutespmm_mtx cutespmm_mtx_t;
+int cutespmm_mtx_open(cutespmm_mtx_t **mtx, const char *path, int pattern_only);
+int cutespmm_mtx_dims(const cutespmm_mtx_t *mtx, uint32_t *M, uint32_t *K, uint32_t *nnz);
+/* Borrowed views valid until cutespmm_mtx_close (the fields MTX_READER exposes, IO.cu:4-9). */
+int cutespmm_mtx_arrays(const cutespmm_mtx_t *mtx, const uint32_t **rowPtr, const uint32_t **cols,
+                        const float **vals);
+int cutespmm_mtx_close(cutespmm_mtx_t *mtx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUTESPMM_H */

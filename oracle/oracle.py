@@ -1,0 +1,156 @@
+"""ctypes access to the CPU oracle (oracle/spmm_oracle.c) and, when it has been built, to the
+reference project's own host routines (oracle/_ref/libcutespmm_ref.so, see oracle/Makefile).
+
+TEST INFRASTRUCTURE ONLY: the checker, never the thing measured or shipped.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "liboracle.so"
+REF_PATH = HERE / "_ref" / "libcutespmm_ref.so"
+
+__all__ = ["build", "spmm_coo", "spmm_csr", "spmm_csr_rows", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
+
+
+def build(ref_root: str | None = "/root/reference") -> None:
+    """Compiles liboracle.so (gcc) and, if the reference tree is present, oracle/_ref."""
+    subprocess.run(["make", "-s", "-C", str(HERE)], check=True)
+    if ref_root and (Path(ref_root) / "data.cu").exists():
+        subprocess.run(["make", "-s", "-C", str(HERE), "ref", f"REF={ref_root}"], check=True)
+
+
+_lib = None
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            build(ref_root=None)
+        _lib = C.CDLL(str(LIB_PATH))
+        vp = C.c_void_p
+        _lib.oracle_spmm_coo.argtypes = [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64]
+        _lib.oracle_spmm_coo.restype = None
+        _lib.oracle_spmm_csr.argtypes = [vp, vp, vp, vp, vp, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64]
+        _lib.oracle_spmm_csr.restype = None
+        _lib.oracle_spmm_csr_rows.argtypes = [vp, vp, vp, vp, vp, vp, C.c_uint64, C.c_uint32, C.c_uint64]
+        _lib.oracle_spmm_csr_rows.restype = None
+        _lib.oracle_max_rel_err.argtypes = [vp, vp, C.c_uint32, C.c_uint32]
+        _lib.oracle_max_rel_err.restype = C.c_float
+        _lib.oracle_rel_fro.argtypes = [vp, vp, C.c_uint64]
+        _lib.oracle_rel_fro.restype = C.c_double
+    return _lib
+
+
+def _a(x, dt):
+    if hasattr(x, "detach"):
+        x = x.detach().cpu().numpy()
+    return np.ascontiguousarray(x, dtype=dt)
+
+
+def spmm_coo(rows, cols, vals, B, M: int, K: int) -> np.ndarray:
+    """inc.h:71-83 restated: in-order accumulation over a COO list."""
+    rows, cols, vals, B = _a(rows, np.uint32), _a(cols, np.uint32), _a(vals, np.float32), _a(B, np.float32)
+    N = B.shape[1]
+    out = np.empty((M, N), dtype=np.float32)
+    _load().oracle_spmm_coo(rows.ctypes.data, cols.ctypes.data, vals.ctypes.data, B.ctypes.data, out.ctypes.data, M, K, N, rows.size)
+    return out
+
+
+def spmm_csr(row_ptr, cols, vals, B, M: int, K: int) -> np.ndarray:
+    """Row-parallel form of the same arithmetic (bit-identical on row-sorted input)."""
+    rp, cols, vals, B = _a(row_ptr, np.uint64), _a(cols, np.uint32), _a(vals, np.float32), _a(B, np.float32)
+    N = B.shape[1]
+    out = np.empty((M, N), dtype=np.float32)
+    _load().oracle_spmm_csr(rp.ctypes.data, cols.ctypes.data, vals.ctypes.data, B.ctypes.data, out.ctypes.data, M, K, N, N, N)
+    return out
+
+
+def spmm_csr_rows(row_ptr, cols, vals, B, which) -> np.ndarray:
+    """Rows `which` of the product only."""
+    rp, cols, vals, B = _a(row_ptr, np.uint64), _a(cols, np.uint32), _a(vals, np.float32), _a(B, np.float32)
+    which = _a(which, np.uint64)
+    N = B.shape[1]
+    out = np.empty((which.size, N), dtype=np.float32)
+    _load().oracle_spmm_csr_rows(rp.ctypes.data, cols.ctypes.data, vals.ctypes.data, B.ctypes.data, out.ctypes.data,
+                                 which.ctypes.data, which.size, N, N)
+    return out
+
+
+def max_rel_err(C_ref, C_test) -> float:
+    """inc.h:84-110 restated."""
+    a, b = _a(C_ref, np.float32), _a(C_test, np.float32)
+    return float(_load().oracle_max_rel_err(a.ctypes.data, b.ctypes.data, a.shape[0], a.shape[1]))
+
+
+def rel_fro(C_ref, C_test) -> float:
+    a, b = _a(C_ref, np.float32), _a(C_test, np.float32)
+    assert a.shape == b.shape
+    return float(_load().oracle_rel_fro(a.ctypes.data, b.ctypes.data, a.size))
+
+
+def ref_available() -> bool:
+    return REF_PATH.exists()
+
+
+class Ref:
+    """The reference project's own host routines (compiled from its sources into oracle/_ref)."""
+
+    def __init__(self):
+        self.lib = C.CDLL(str(REF_PATH))
+        vp = C.c_void_p
+        L = self.lib
+        L.ref_spmm_coo.argtypes = [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint]
+        L.ref_spmm_coo.restype = None
+        L.ref_check_gemm_correctness_coo.argtypes = [vp, vp, C.c_uint32, C.c_uint32]
+        L.ref_check_gemm_correctness_coo.restype = C.c_float
+        L.ref_mtx_open.argtypes = [C.c_char_p]
+        L.ref_mtx_open.restype = vp
+        for f in ("ref_mtx_M", "ref_mtx_K", "ref_mtx_nnz", "ref_hrpb_num_panels", "ref_hrpb_num_blocks"):
+            getattr(L, f).argtypes = [vp]
+            getattr(L, f).restype = C.c_uint
+        L.ref_mtx_copy.argtypes = [vp, vp, vp, vp]
+        L.ref_mtx_copy.restype = None
+        L.ref_hrpb_build.argtypes = [C.c_uint, C.c_uint, vp, vp, vp]
+        L.ref_hrpb_build.restype = vp
+        L.ref_hrpb_copy.argtypes = [vp, vp, vp]
+        L.ref_hrpb_copy.restype = None
+        L.ref_hrpb_stream_words.argtypes = [vp]
+        L.ref_hrpb_stream_words.restype = C.c_ulonglong
+
+    def spmm_coo(self, rows, cols, vals, B, M, K):
+        rows, cols, vals, B = _a(rows, np.uint32), _a(cols, np.uint32), _a(vals, np.float32), _a(B, np.float32)
+        N = B.shape[1]
+        out = np.empty((M, N), dtype=np.float32)
+        self.lib.ref_spmm_coo(rows.ctypes.data, cols.ctypes.data, vals.ctypes.data, B.ctypes.data, out.ctypes.data, M, K, N, rows.size)
+        return out
+
+    def max_rel_err(self, C_ref, C_test):
+        a, b = _a(C_ref, np.float32), _a(C_test, np.float32)
+        return float(self.lib.ref_check_gemm_correctness_coo(a.ctypes.data, b.ctypes.data, a.shape[0], a.shape[1]))
+
+    def mtx_read(self, path):
+        h = self.lib.ref_mtx_open(str(path).encode())
+        M, K, nnz = self.lib.ref_mtx_M(h), self.lib.ref_mtx_K(h), self.lib.ref_mtx_nnz(h)
+        rp = np.empty(M + 1, np.uint32)
+        cols = np.empty(max(nnz, 1), np.uint32)
+        vals = np.empty(max(nnz, 1), np.float32)
+        self.lib.ref_mtx_copy(h, rp.ctypes.data, cols.ctypes.data, vals.ctypes.data)
+        return M, K, nnz, rp, cols[:nnz], vals[:nnz]
+
+    def hrpb(self, M, K, row_ptr, cols, vals):
+        """blockedRowPtr, activeCols and packed-stream size of the reference's preprocessing.
+        Needs ascending unique columns per row and M, K multiples of 16 (data.cu:80-93)."""
+        rp, cols, vals = _a(row_ptr, np.uint32), _a(cols, np.uint32), _a(vals, np.float32)
+        h = self.lib.ref_hrpb_build(M, K, rp.ctypes.data, cols.ctypes.data, vals.ctypes.data)
+        P, nb = self.lib.ref_hrpb_num_panels(h), self.lib.ref_hrpb_num_blocks(h)
+        brp = np.empty(P + 1, np.uint32)
+        ac = np.empty(max(nb * 16, 1), np.uint32)
+        self.lib.ref_hrpb_copy(h, brp.ctypes.data, ac.ctypes.data)
+        return brp, ac[: nb * 16], int(self.lib.ref_hrpb_stream_words(h))

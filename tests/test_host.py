@@ -1,0 +1,144 @@
+"""Host-side logic of libcutespmm that needs no GPU: the library loads and exports its header's
+symbols, the plan builder's views agree with the reference's preprocessing (golden vectors), the
+packed format round-trips, bad input is rejected with an error code, the loader matches MTX_READER."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cutespmm_ae_b200 as cs
+from cutespmm_ae_b200 import generators as g
+from conftest import GOLDEN, GOLDEN_CASES, ROOT, load_golden
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "cutespmm.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    names = set(re.findall(r"\b(cutespmm_[a-z0-9_]+)\s*\(", header))
+    assert len(names) >= 18
+    lib = ctypes.CDLL(str(cs._build.LIB))
+    missing = [n for n in sorted(names) if not hasattr(lib, n)]
+    assert not missing, missing
+    assert cs.lib.cutespmm_version() >= 100
+
+
+def test_status_strings():
+    assert cs.lib.cutespmm_status_string(0) == b"success"
+    assert b"invalid" in cs.lib.cutespmm_status_string(-1)
+
+
+@pytest.mark.parametrize("name", [c for c in GOLDEN_CASES if c != "uniform_256_unsorted"])
+def test_panel_views_match_reference_preprocessing(name):
+    gd = load_golden(name)
+    p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"], host_only=True)
+    assert np.array_equal(p.blocked_row_ptr(), gd["blocked_row_ptr"])
+    assert np.array_equal(p.active_cols(), gd["active_cols"])
+    info = p.info()
+    assert info["num_panels"] == int(gd["M"]) // 16
+    assert info["nnz"] == gd["cols"].size
+
+
+@pytest.mark.parametrize("path", [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO])
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_packed_format_round_trip(name, path):
+    gd = load_golden(name)
+    M, K = int(gd["M"]), int(gd["K"])
+    p = cs.Plan(M, K, gd["row_ptr"], gd["cols"], gd["vals"], host_only=True, path=path, split_nnz=16)
+    rp, cols, vals = p.decode_csr()
+    # expected: the input with every row sorted by column
+    exp_c, exp_v = gd["cols"].copy(), gd["vals"].copy()
+    for r in range(M):
+        j0, j1 = int(gd["row_ptr"][r]), int(gd["row_ptr"][r + 1])
+        o = np.argsort(exp_c[j0:j1], kind="stable")
+        exp_c[j0:j1], exp_v[j0:j1] = exp_c[j0:j1][o], exp_v[j0:j1][o]
+    assert np.array_equal(rp, gd["row_ptr"].astype(np.uint64))
+    assert np.array_equal(cols, exp_c)
+    assert np.array_equal(vals.view(np.uint32), exp_v.view(np.uint32))
+
+
+def test_round_trip_partial_last_panel_and_empty():
+    A = g.uniform_random(37, 50, 3, seed=3)  # M not a multiple of 16
+    for path in (cs.PATH_ROWS, cs.PATH_BRICK):
+        p = cs.Plan.from_csr(A, host_only=True, path=path)
+        rp, cols, vals = p.decode_csr()
+        assert np.array_equal(cols, A.cols.numpy().astype(np.uint32))
+        assert p.info()["num_panels"] == 3
+    empty = cs.Plan(32, 32, np.zeros(33, np.uint64), np.zeros(0, np.uint32), np.zeros(0, np.float32), host_only=True)
+    assert empty.info()["nnz"] == 0 and empty.info()["num_blocks"] == 0
+    zero_rows = cs.Plan(0, 8, np.zeros(1, np.uint64), np.zeros(0, np.uint32), np.zeros(0, np.float32), host_only=True)
+    assert zero_rows.info()["num_panels"] == 0
+
+
+def test_long_rows_become_chunks():
+    gd = load_golden("rmat_s8")
+    p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"], host_only=True, path=cs.PATH_ROWS,
+                split_nnz=8)
+    lens = np.diff(gd["row_ptr"].astype(np.int64))
+    info = p.info()
+    assert info["num_long_rows"] == int((lens > 8).sum())
+    assert info["num_chunks"] == int(np.ceil(lens[lens > 8] / 8).sum())
+
+
+def test_bad_input_is_rejected_not_fatal():
+    rp = np.array([0, 2, 1], np.uint64)
+    with pytest.raises(cs.CuteSpmmError) as e:
+        cs.Plan(2, 4, rp, np.zeros(2, np.uint32), np.zeros(2, np.float32), host_only=True)
+    assert e.value.status == -1
+    with pytest.raises(cs.CuteSpmmError) as e:  # column index >= K
+        cs.Plan(1, 4, np.array([0, 1], np.uint64), np.array([4], np.uint32), np.ones(1, np.float32), host_only=True)
+    assert e.value.status == -1 and "column" in str(e.value)
+    with pytest.raises(cs.CuteSpmmError):  # rowPtr[0] != 0
+        cs.Plan(1, 4, np.array([1, 1], np.uint64), np.zeros(1, np.uint32), np.ones(1, np.float32), host_only=True)
+    h = ctypes.c_void_p()
+    assert cs.lib.cutespmm_plan_build_host(ctypes.byref(h), 1, 1, None, None, None, None) == -1
+    assert cs.lib.cutespmm_plan_info(None, None) == -1
+
+
+def test_host_only_plan_refuses_to_execute():
+    gd = load_golden("stencil_16x16")
+    p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"], host_only=True)
+    st = cs.lib.cutespmm_spmm(p._h, 16, 16, 16, 16, 16, None)
+    assert st == -4  # unsupported: there is no CPU execution path
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_plan_create_without_gpu_fails_loudly():
+    gd = load_golden("stencil_16x16")
+    with pytest.raises(cs.CuteSpmmError) as e:
+        cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"])
+    assert e.value.status == -3
+
+
+@pytest.mark.parametrize("name", ["general_5x7", "symmetric_20"])
+def test_mtx_reader_matches_reference(name):
+    gd = dict(np.load(GOLDEN / f"mtx_{name}.npz"))
+    r = cs.MtxReader(GOLDEN / f"{name}.mtx")
+    assert (r.M, r.K, r.nnz) == (int(gd["M"]), int(gd["K"]), int(gd["nnz"]))
+    assert np.array_equal(r.rowPtr, gd["row_ptr"])
+    assert np.array_equal(r.cols, gd["cols"])
+    assert np.array_equal(r.vals, gd["vals"])
+
+
+def test_mtx_reader_keeps_values_when_asked_and_reports_missing_file():
+    r = cs.MtxReader(GOLDEN / "general_5x7.mtx", pattern_only=False)
+    assert sorted(r.vals.tolist())[0] == -2.0 and 9.0 in r.vals
+    with pytest.raises(cs.CuteSpmmError) as e:
+        cs.MtxReader(GOLDEN / "does_not_exist.mtx")
+    assert e.value.status == -5
+
+
+def test_partition_rows_balances_nnz_and_aligns():
+    A = g.rmat(12, 8, seed=5)
+    rp = A.row_ptr.numpy().astype(np.uint64)
+    for parts in (1, 2, 3, 8):
+        b = cs.partition_rows(rp, parts, align_rows=16)
+        assert b[0] == 0 and b[-1] == A.M and np.all(np.diff(b.astype(np.int64)) >= 0)
+        assert np.all(b[1:-1] % 16 == 0)
+        cost = (rp[b[1:].astype(np.int64)] - rp[b[:-1].astype(np.int64)]).astype(np.float64) + 4.0 * np.diff(b.astype(np.int64))
+        assert cost.max() <= 1.25 * cost.mean() + 16 * 40
+    # more parts than panels: empty ranges allowed, still monotone
+    b = cs.partition_rows(np.array([0, 1, 2], np.uint64), 4, align_rows=16)
+    assert b[0] == 0 and b[-1] == 2 and np.all(np.diff(b.astype(np.int64)) >= 0)

@@ -1,0 +1,159 @@
+"""Parity of the CUDA path (called through the C ABI) with the CPU oracle, on a B200."""
+import numpy as np
+import pytest
+import torch
+
+import cutespmm_ae_b200 as cs
+from cutespmm_ae_b200 import generators as g
+from conftest import GOLDEN_CASES, REL_FRO_TOL, REL_FRO_TOL_FP32, load_golden
+
+pytestmark = pytest.mark.gpu
+
+PATHS = [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO]
+PATH_TOL = {cs.PATH_ROWS: REL_FRO_TOL_FP32, cs.PATH_BRICK: REL_FRO_TOL, cs.PATH_AUTO: REL_FRO_TOL}
+
+
+def run(plan, B_np, **kw):
+    B = torch.from_numpy(np.ascontiguousarray(B_np)).cuda()
+    C = torch.full((plan.M, B.shape[1]), float("nan"), device="cuda")  # every element must be overwritten
+    plan.spmm(B, C, **kw)
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    return C.cpu().numpy()
+
+
+@pytest.mark.parametrize("path", PATHS, ids=["rows", "brick", "auto"])
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_golden_fixtures(oracle_mod, name, path):
+    gd = load_golden(name)
+    N = int(gd["N"])
+    if path != cs.PATH_ROWS and N % 32:
+        pytest.skip("tensor-core path takes N in multiples of 32")
+    p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"], path=path)
+    C = run(p, gd["B"])
+    assert oracle_mod.rel_fro(gd["C"], C) <= PATH_TOL[path]
+
+
+@pytest.mark.parametrize("path", PATHS, ids=["rows", "brick", "auto"])
+@pytest.mark.parametrize("workload,Ns", [("uniform4096", [32]), ("stencil512", [128]),
+                                         ("elasticity40", [32, 64, 128, 256]), ("rmat20", [128])])
+def test_named_workloads_match_oracle(oracle_mod, workload, Ns, path):
+    w = g.WORKLOADS[workload]
+    A = w["make"]()
+    p = cs.Plan.from_csr(A, path=path)
+    for N in Ns:
+        B = g.dense_operand(A.K, N, w["b_seed"], w["b_dist"]).numpy()
+        ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K)
+        C = run(p, B)
+        err = oracle_mod.rel_fro(ref, C)
+        assert err <= PATH_TOL[path], (workload, N, err)
+        if path == cs.PATH_ROWS:
+            # the reference's own metric (max element-wise relative error, inc.h:84-110), informational bound
+            assert oracle_mod.max_rel_err(ref, C) < 5e-2
+
+
+@pytest.mark.parametrize("N", [1, 3, 8, 33, 48, 64, 100, 128, 130, 200, 256, 384, 512, 516, 640, 1024])
+def test_any_number_of_columns(oracle_mod, N):
+    A = g.rmat(9, 8, seed=31, values="uniform")
+    B = g.dense_operand(A.K, N, 32).numpy()
+    p = cs.Plan.from_csr(A, path=cs.PATH_ROWS, split_nnz=32)
+    assert p.info()["num_long_rows"] > 0
+    ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K)
+    assert oracle_mod.rel_fro(ref, run(p, B)) <= REL_FRO_TOL_FP32
+
+
+def test_strided_and_misaligned_operands(oracle_mod):
+    A = g.uniform_random(300, 200, 5, seed=41)  # M not a multiple of 16
+    p = cs.Plan.from_csr(A, path=cs.PATH_ROWS)
+    N = 96
+    big = g.dense_operand(A.K, N + 7, 42).cuda()
+    Bv = big[:, 3 : 3 + N]  # 12-byte offset: not 16-byte aligned, ld = N + 7
+    Cbig = torch.full((A.M, N + 5), float("nan"), device="cuda")
+    Cv = Cbig[:, 1 : 1 + N]
+    p.spmm(Bv, Cv)
+    torch.cuda.synchronize()
+    ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, Bv.cpu().contiguous().numpy(), A.M, A.K)
+    assert oracle_mod.rel_fro(ref, Cv.cpu().contiguous().numpy()) <= REL_FRO_TOL_FP32
+    assert torch.isnan(Cbig[:, 0]).all() and torch.isnan(Cbig[:, 1 + N :]).all()  # nothing outside the window
+
+
+def test_empty_rows_panels_and_matrix(oracle_mod):
+    # rows 0..63 empty, a dense row, then empties
+    M, K, N = 160, 64, 64
+    rp = np.zeros(M + 1, np.uint64)
+    rp[70:] = 64
+    rp[100:] = 65
+    cols = np.concatenate([np.arange(64), [5]]).astype(np.uint32)
+    vals = np.linspace(-1, 1, 65).astype(np.float32)
+    B = g.dense_operand(K, N, 51).numpy()
+    ref = oracle_mod.spmm_csr(rp, cols, vals, B, M, K)
+    for path in (cs.PATH_ROWS, cs.PATH_AUTO, cs.PATH_BRICK):
+        C = run(cs.Plan(M, K, rp, cols, vals, path=path), B)
+        assert oracle_mod.rel_fro(ref, C) <= REL_FRO_TOL
+        assert not C[:69].any() and not C[100:].any()
+    zero = cs.Plan(48, 16, np.zeros(49, np.uint64), np.zeros(0, np.uint32), np.zeros(0, np.float32))
+    assert not run(zero, np.ones((16, 32), np.float32)).any()
+
+
+def test_unsorted_and_duplicate_columns(oracle_mod):
+    gd = load_golden("uniform_256_unsorted")
+    p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"], path=cs.PATH_ROWS)
+    assert oracle_mod.rel_fro(gd["C"], run(p, gd["B"])) <= REL_FRO_TOL_FP32
+    # duplicates add up, as in spmm_coo
+    rp = np.array([0, 3, 3, 4], np.uint64)
+    cols = np.array([2, 2, 0, 1], np.uint32)
+    vals = np.array([1.0, 2.0, 4.0, 8.0], np.float32)
+    B = g.dense_operand(3, 32, 61).numpy()
+    ref = oracle_mod.spmm_csr(rp, cols, vals, B, 3, 3)
+    for path in (cs.PATH_ROWS, cs.PATH_BRICK):
+        assert oracle_mod.rel_fro(ref, run(cs.Plan(3, 3, rp, cols, vals, path=path), B)) <= REL_FRO_TOL
+
+
+def test_hub_rows_are_deterministic(oracle_mod):
+    A = g.rmat(14, 8, seed=71, values="uniform")
+    p = cs.Plan.from_csr(A, path=cs.PATH_ROWS, split_nnz=128)
+    assert p.info()["num_chunks"] > 100
+    B = g.dense_operand(A.K, 128, 72).numpy()
+    c1, c2 = run(p, B), run(p, B)
+    assert np.array_equal(c1.view(np.uint32), c2.view(np.uint32))  # no atomics: bit-stable run to run
+    ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K)
+    assert oracle_mod.rel_fro(ref, c1) <= REL_FRO_TOL_FP32
+
+
+def test_host_buffer_call(oracle_mod):
+    gd = load_golden("elasticity_4")
+    p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"])
+    Bh = torch.from_numpy(gd["B"]).pin_memory()
+    C, ms = p.spmm_host(Bh)
+    assert ms > 0.0
+    assert oracle_mod.rel_fro(gd["C"], C.numpy()) <= REL_FRO_TOL
+    C2, _ = p.spmm_host(gd["B"][:, :17].copy())  # narrower N reuses the staging buffers
+    assert oracle_mod.rel_fro(gd["C"][:, :17].copy(), C2.numpy()) <= REL_FRO_TOL
+
+
+def test_execution_errors_are_status_codes():
+    gd = load_golden("stencil_16x16")
+    p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"])
+    B = torch.zeros(int(gd["K"]), 16, device="cuda")
+    assert cs.lib.cutespmm_spmm(p._h, B.data_ptr(), 8, B.data_ptr(), 16, 16, None) == -1  # ldb < N
+    assert cs.lib.cutespmm_spmm(p._h, None, 16, B.data_ptr(), 16, 16, None) == -1
+    assert cs.lib.cutespmm_spmm(p._h, B.data_ptr() + 2, 16, B.data_ptr(), 16, 16, None) == -1  # misaligned
+
+
+def test_full_size_properties_without_cpu_product():
+    """At the size where the CPU product takes too long: linearity in B and the column-sum identity
+    1^T (A B) = (A^T 1)^T B, both checked on the device in fp64."""
+    A = g.rmat(22, 8, seed=1005, values="uniform", device="cuda")
+    N = 128
+    p = cs.Plan.from_csr(A)
+    B1 = g.dense_operand(A.K, N, 81, device="cuda")
+    B2 = g.dense_operand(A.K, N, 82, device="cuda")
+    C1, C2, C12 = p.spmm(B1), p.spmm(B2), p.spmm(B1 + B2)
+    torch.cuda.synchronize()
+    num = (C12.double() - C1.double() - C2.double()).norm()
+    assert float(num / C12.double().norm()) < 1e-5
+    colsum = torch.zeros(A.K, dtype=torch.float64, device="cuda")
+    colsum.index_add_(0, A.cols.long(), A.vals.double())
+    expect = colsum @ B1.double()
+    got = C1.double().sum(0)
+    assert float((got - expect).norm() / expect.norm()) < 1e-5
