@@ -16,7 +16,10 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBDIR = HERE / "lib"
-LIB = LIBDIR / "libcutespmm.so"
+# CUTESPMM_LIBNAME / CUTESPMM_DEFINES: build and load an alternative variant of the library side by
+# side with the default one (kernel tuning experiments); unset in normal use.
+LIB = LIBDIR / os.environ.get("CUTESPMM_LIBNAME", "libcutespmm.so")
+EXTRA = os.environ.get("CUTESPMM_DEFINES", "").split()
 SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "plan.cpp", "brick_build.cpp", "mtx_io.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
@@ -37,17 +40,17 @@ def _stamp() -> str:
         if f.is_file():
             h.update(f.name.encode())
             h.update(f.read_bytes())
-    h.update(" ".join(FLAGS).encode())
+    h.update(" ".join(FLAGS + EXTRA).encode())
     return h.hexdigest()
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
     LIBDIR.mkdir(exist_ok=True)
-    stamp_file = LIBDIR / "libcutespmm.stamp"
+    stamp_file = LIBDIR / (LIB.name + ".stamp")
     stamp = _stamp()
     if not force and LIB.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
         return LIB
-    cmd = [NVCC, *FLAGS, "-o", str(LIB), *map(str, _sources())]
+    cmd = [NVCC, *FLAGS, *EXTRA, "-o", str(LIB), *map(str, _sources())]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

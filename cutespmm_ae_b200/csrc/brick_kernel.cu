@@ -1,6 +1,188 @@
-// placeholder, replaced below
+// Tensor-core brick kernel: the path for row panels whose 16x8 bricks are full enough that a dense
+// contraction (zeros included) costs less than gathering a row of B per nonzero.
+//
+// It takes the place of SpMM<NUM_WARPS,ILP_LEVEL> + COMPUTE<ILP> (reference kernel.cu:16-288).
+// What is kept: 16-row panels, active-column compaction, occupancy bitmaps expanded into MMA
+// A-fragments by popcount (kernel.cu:20-27), TF32 inputs rounded to nearest (cvt.rna,
+// kernel.cu:28-35) with fp32 accumulation.  What is different:
+//   * every warp is an autonomous pipeline over a contiguous range of the flat brick stream; it
+//     owns a ring of kStages shared-memory stages and one mbarrier per stage.  The reference
+//     drains a depth-2 cp.async pipeline and runs __syncthreads after every block of 16 columns
+//     (kernel.cu:220-222); here no two warps ever wait for each other;
+//   * the eight gathered rows of B of a brick arrive by eight TMA bulk copies (one 512-byte row slab
+//     each at N = 128, issued by eight lanes), the brick's record (bitmap + values) by a ninth; the
+//     copies for brick k + kStages - 1 are issued before brick k is computed, across panel
+//     boundaries, so the gather latency is hidden without occupancy;
+//   * a brick is 16 x 8 and maps onto mma.m16n8k8 (the reference issues m16n8k4 on 16 x 4 bricks);
+//     a warp covers the whole 128-column slab (16 accumulator tiles), so a brick is expanded once,
+//     not once per warp of a block;
+//   * B rows sit in shared memory with a stride of SLAB + 8 floats, which makes the B-fragment
+//     reads (lane (g,t) reads B[t][g], B[t+4][g]) hit 32 different banks;
+//   * the work list is cut by brick count (nnz balance), not by a per-GPU occupancy table.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
 #include "device_plan.hpp"
+#include "plan.hpp"
+#include "ptx.cuh"
+
 namespace cutespmm {
-bool brick_supports(uint32_t, uint64_t, uint64_t, const void *, const void *) { return false; }
-cudaError_t launch_brick(const BrickArgs &, int, cudaStream_t) { return cudaErrorNotSupported; }
+
+namespace {
+
+#ifndef BRICK_STAGES
+#define BRICK_STAGES 4
+#endif
+constexpr int kStages = BRICK_STAGES;
+constexpr unsigned kFull = 0xffffffffu;
+constexpr int kRecWords = kBrickRecHeaderWords + 128;  // header + a full brick of values
+
+template <int NT> struct StageLayout {
+    static constexpr int kSlab = 8 * NT;         // columns of B / C a warp covers
+    static constexpr int kStride = kSlab + 8;    // floats between consecutive B rows in shared memory
+    static constexpr int kBBytes = 8 * kStride * 4;
+    static constexpr int kStageBytes = kBBytes + kRecWords * 4;
+    static constexpr int kWarpBytes = kStages * kStageBytes + kStages * 8;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickArgs a)
+{
+    using L = StageLayout<NT>;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t gw = blockIdx.x * kBrickWarps + warp;
+    const uint32_t kb = __ldg(a.warp_ranges + gw), ke = __ldg(a.warp_ranges + gw + 1);
+    if (kb >= ke) return;  // warps never synchronise with each other, so leaving early is safe
+    const uint32_t n0 = blockIdx.y * L::kSlab;
+
+    unsigned char *mine = smem_raw + (size_t)warp * L::kWarpBytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(mine + kStages * L::kStageBytes);
+    auto stage_b = [&](int s) { return reinterpret_cast<float *>(mine + s * L::kStageBytes); };
+    auto stage_rec = [&](int s) { return reinterpret_cast<uint32_t *>(mine + s * L::kStageBytes + L::kBBytes); };
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) ptx::mbar_init(&full[s], 1);
+        ptx::fence_mbar_init();
+    }
+    __syncwarp();
+
+    // Producer metadata, one group of 4 bricks at a time: lane l holds column l of the group's 32
+    // columns, lanes 0..4 hold the group's five record offsets.  The next group is loaded one group
+    // ahead of its use.
+    uint32_t G = kb >> 2;
+    auto load_cols = [&](uint32_t g) { return __ldg(a.cols + (size_t)g * 32 + lane); };
+    auto load_offs = [&](uint32_t g) { return lane < 5 ? __ldg(a.rec_off + (size_t)g * 4 + lane) : 0u; };
+    uint32_t mc_cur = load_cols(G), mo_cur = load_offs(G);
+    uint32_t mc_nxt = load_cols(G + 1), mo_nxt = load_offs(G + 1);
+
+    const float *Bn = a.B + n0;
+    const uint32_t ldb32 = (uint32_t)a.ldb;
+    auto issue = [&](uint32_t k) {  // start the copies of brick k into its stage
+        if ((k >> 2) != G) {
+            ++G;
+            mc_cur = mc_nxt;
+            mo_cur = mo_nxt;
+            mc_nxt = load_cols(G + 1);
+            mo_nxt = load_offs(G + 1);
+        }
+        const int s = (k - kb) % kStages;
+        const uint32_t col = __shfl_sync(kFull, mc_cur, (k & 3) * 8 + (lane & 7));
+        const uint32_t o0 = __shfl_sync(kFull, mo_cur, k & 3), o1 = __shfl_sync(kFull, mo_cur, (k & 3) + 1);
+        const uint32_t rec_bytes = (o1 - o0) * 16u;
+        if (lane == 0) ptx::mbar_expect_tx(&full[s], 8u * L::kSlab * 4u + rec_bytes);
+        __syncwarp();
+        if (lane < 8)
+            ptx::bulk_g2s(stage_b(s) + lane * L::kStride, Bn + (uint64_t)col * ldb32, L::kSlab * 4u, &full[s]);
+        else if (lane == 8)
+            ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)o0 * 4, rec_bytes, &full[s]);
+    };
+
+    // lane-constant pieces of the A-fragment expansion (mma.m16n8k8 row-major A: a0 = A[g][t],
+    // a1 = A[g+8][t], a2 = A[g][t+4], a3 = A[g+8][t+4]; map bit = row*8 + col)
+    const int g = lane >> 2, t = lane & 3;
+    const bool upper_word = (g >> 2) != 0;  // rows 4..7 (and 12..15) live in the odd words
+    const uint32_t bit0 = (g & 3) * 8 + t, bit2 = bit0 + 4;
+    const uint32_t below0 = (1u << bit0) - 1u, below2 = (1u << bit2) - 1u;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+
+    uint32_t pk = kb;
+    for (uint32_t k = kb; k < ke; ++k) {
+        while (pk < ke && pk < k + kStages) issue(pk++);
+        const int s = (k - kb) % kStages;
+        if (!ptx::mbar_wait(&full[s], ((k - kb) / kStages) & 1u)) {
+            if (lane == 0) atomicExch(a.status, 2u);  // the copies never landed: report, do not hang
+            // give the copies still in flight a bounded chance to land before the block's shared memory is reused
+            for (uint32_t j = k + 1; j < pk; ++j) ptx::mbar_wait(&full[(j - kb) % kStages], ((j - kb) / kStages) & 1u);
+            return;
+        }
+        const uint32_t *rec = stage_rec(s);
+        const uint4 map = *reinterpret_cast<const uint4 *>(rec);
+        const uint2 info = *reinterpret_cast<const uint2 *>(rec + 4);
+        const float *vals = reinterpret_cast<const float *>(rec + kBrickRecHeaderWords);
+        const uint32_t c1 = __popc(map.x), c2 = c1 + __popc(map.y), c3 = c2 + __popc(map.z);
+        const uint32_t wl = upper_word ? map.y : map.x, wh = upper_word ? map.w : map.z;
+        const uint32_t base_l = upper_word ? c1 : 0u, base_h = upper_word ? c3 : c2;
+        uint32_t af[4];
+        af[0] = ptx::f32_to_tf32_rna(((wl >> bit0) & 1u) ? vals[base_l + __popc(wl & below0)] : 0.f);
+        af[1] = ptx::f32_to_tf32_rna(((wh >> bit0) & 1u) ? vals[base_h + __popc(wh & below0)] : 0.f);
+        af[2] = ptx::f32_to_tf32_rna(((wl >> bit2) & 1u) ? vals[base_l + __popc(wl & below2)] : 0.f);
+        af[3] = ptx::f32_to_tf32_rna(((wh >> bit2) & 1u) ? vals[base_h + __popc(wh & below2)] : 0.f);
+        const float *b_lo = stage_b(s) + t * L::kStride + g, *b_hi = b_lo + 4 * L::kStride;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            uint32_t bf[2];
+            bf[0] = ptx::f32_to_tf32_rna(b_lo[nt * 8]);
+            bf[1] = ptx::f32_to_tf32_rna(b_hi[nt * 8]);
+            ptx::mma_m16n8k8_tf32(acc[nt], af, bf);
+        }
+        if (info.x & 1u) {  // last brick of the panel: write its 16 x SLAB tile of C
+            const uint64_t r_lo = (uint64_t)info.y * kPanelRows + g, r_hi = r_lo + 8;
+            float *c_lo = a.C + r_lo * a.ldc + n0 + 2 * t, *c_hi = a.C + r_hi * a.ldc + n0 + 2 * t;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                if (r_lo < a.M) __stcs(reinterpret_cast<float2 *>(c_lo + nt * 8), make_float2(acc[nt][0], acc[nt][1]));
+                if (r_hi < a.M) __stcs(reinterpret_cast<float2 *>(c_hi + nt * 8), make_float2(acc[nt][2], acc[nt][3]));
+                acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+            }
+        }
+        __syncwarp();  // every lane is done with stage s before the next iteration refills it
+    }
 }
+
+template <int NT> cudaError_t launch_brick_t(const BrickArgs &a, cudaStream_t s)
+{
+    using L = StageLayout<NT>;
+    constexpr int smem = kBrickWarps * L::kWarpBytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(spmm_brick_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    const uint32_t slabs = a.N / L::kSlab;
+    spmm_brick_kernel<NT><<<dim3(a.num_warps / kBrickWarps, slabs), kBrickWarps * 32, smem, s>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool brick_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const void *C)
+{
+    const uintptr_t pb = reinterpret_cast<uintptr_t>(B), pc = reinterpret_cast<uintptr_t>(C);
+    return N % 32 == 0 && N > 0 && !((pb | pc) & 15) && !((ldb | ldc) & 3);
+}
+
+cudaError_t launch_brick(const BrickArgs &a, int /*sm_count*/, cudaStream_t s)
+{
+    if (a.num_bricks == 0) return cudaSuccess;
+    if (a.N % 128 == 0) return launch_brick_t<16>(a, s);
+    if (a.N % 64 == 0) return launch_brick_t<8>(a, s);
+    return launch_brick_t<4>(a, s);
+}
+
+}  // namespace cutespmm

@@ -1,6 +1,7 @@
 // The extern "C" surface declared in include/cutespmm.h: plan life cycle, execution, sharding.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -45,10 +46,11 @@ struct cutespmm_plan {
     uint64_t device_bytes = 0;
     // device arrays
     void *d_row_ptr = nullptr, *d_pairs = nullptr, *d_tiles = nullptr, *d_chunks = nullptr, *d_long_rows = nullptr;
-    void *d_items = nullptr, *d_bcols = nullptr, *d_bmaps = nullptr, *d_bvals = nullptr;
+    void *d_tiles_all = nullptr, *d_chunks_all = nullptr, *d_long_rows_all = nullptr;
+    void *d_bcols = nullptr, *d_brecs = nullptr, *d_brec_off = nullptr, *d_warp_ranges = nullptr;
+    uint32_t brick_warps = 0;
     float *d_scratch = nullptr;
     uint32_t *d_status = nullptr;
-    uint32_t num_row_chunks = 0;
     // staging for the host-buffer call
     float *d_B = nullptr, *d_C = nullptr;
     uint64_t staged_B = 0, staged_C = 0;
@@ -60,8 +62,8 @@ struct cutespmm_plan {
         int cur = -1;
         cudaGetDevice(&cur);
         if (cur != device) cudaSetDevice(device);
-        for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_items, d_bcols, d_bmaps, d_bvals,
-                        (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
+        for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
+                        d_bcols, d_brecs, d_brec_off, d_warp_ranges, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
@@ -136,9 +138,6 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
     p->device = dev;
     p->sm_count = prop.multiProcessorCount;
     p->on_device = true;
-    p->num_row_chunks = 0;
-    for (const Chunk &c : h.chunks)
-        if (c.j1 > c.j0) ++p->num_row_chunks;  // row chunks come first; brick-piece slots carry no nonzeros
     uint64_t &by = p->device_bytes;
 #define UP(vec, ptr)                                                   \
     if ((e = upload(vec, &ptr, by)) != cudaSuccess) {                  \
@@ -146,17 +145,50 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
         *plan = nullptr;                                               \
         return fail_cuda(e, "uploading " #vec);                        \
     }
-    UP(h.row_ptr, p->d_row_ptr)
-    UP(h.pairs, p->d_pairs)
-    UP(h.tile_rows, p->d_tiles)
+    {   // bulk copies of a tile start/end on 16-byte boundaries: keep readable slack behind both arrays
+        std::vector<uint32_t> rp(h.row_ptr);
+        rp.resize(rp.size() + 8, rp.back());
+        std::vector<Pair> pr(h.pairs);
+        pr.resize(pr.size() + 2, Pair{0, 0});
+        UP(rp, p->d_row_ptr)
+        UP(pr, p->d_pairs)
+    }
+    UP(h.tiles, p->d_tiles)
     UP(h.chunks, p->d_chunks)
     UP(h.long_rows, p->d_long_rows)
-    UP(h.panel_items, p->d_items)
-    UP(h.brick_cols, p->d_bcols)
-    UP(h.brick_maps, p->d_bmaps)
-    UP(h.brick_vals, p->d_bvals)
+    UP(h.tiles_all, p->d_tiles_all)
+    UP(h.chunks_all, p->d_chunks_all)
+    UP(h.long_rows_all, p->d_long_rows_all)
+    if (h.num_bricks) {
+        // the producer lanes prefetch one group (4 bricks) beyond the one in use: keep that readable
+        std::vector<uint32_t> bc(h.brick_cols), ro(h.brick_rec_off);
+        bc.resize(bc.size() + 96, 0u);
+        ro.resize(ro.size() + 16, ro.back());
+        // contiguous brick ranges of about equal cost, one per warp, cut at panel boundaries
+        p->brick_warps = (uint32_t)prop.multiProcessorCount * kBrickWarps;
+        std::vector<uint32_t> wr(p->brick_warps + 1, (uint32_t)h.num_bricks);
+        const std::vector<uint32_t> &pf = h.panel_first_brick;  // brick_panels + 1 entries
+        const uint64_t np = pf.size() - 1;
+        auto cost_before = [&](uint64_t panel) { return 2ull * pf[panel] + panel; };  // brick = 2, panel epilogue = 1
+        const uint64_t total = cost_before(np);
+        wr[0] = 0;
+        uint64_t lo = 0;
+        for (uint32_t w = 1; w < p->brick_warps; ++w) {
+            const uint64_t want = total * w / p->brick_warps;
+            uint64_t hi = np;
+            while (lo < hi) {
+                const uint64_t mid = lo + (hi - lo) / 2;
+                if (cost_before(mid) < want) lo = mid + 1; else hi = mid;
+            }
+            wr[w] = pf[lo];
+        }
+        UP(bc, p->d_bcols)
+        UP(h.brick_recs, p->d_brecs)
+        UP(ro, p->d_brec_off)
+        UP(wr, p->d_warp_ranges)
+    }
 #undef UP
-    const uint64_t scratch = (uint64_t)h.chunks.size() * kScratchCols * sizeof(float);
+    const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
     if (scratch) {
         if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) { delete p; *plan = nullptr; return fail_cuda(e, "scratch"); }
         by += scratch;
@@ -191,13 +223,13 @@ int cutespmm_plan_info(const cutespmm_plan_t *p, cutespmm_plan_info_t *info)
     info->M = h.M; info->K = h.K; info->nnz = h.nnz;
     info->num_panels = h.num_panels();
     info->num_blocks = h.blocked_row_ptr.empty() ? 0 : h.blocked_row_ptr.back();
-    info->num_tiles = h.tile_rows.size() / 2;
+    info->num_tiles = h.tiles.size();
     info->num_long_rows = h.long_rows.size();
     info->num_chunks = h.chunks.size();
     info->brick_panels = h.brick_panels;
     info->num_bricks = h.num_bricks;
     info->device_bytes = p->device_bytes;
-    info->scratch_bytes_per_col = h.chunks.size() * sizeof(float);
+    info->scratch_bytes_per_col = std::max(h.chunks.size(), h.chunks_all.size()) * sizeof(float);
     return CUTESPMM_OK;
 }
 
@@ -220,48 +252,65 @@ int cutespmm_plan_decode_csr(const cutespmm_plan_t *p, uint64_t *rowPtr, uint32_
     return CUTESPMM_OK;
 }
 
-static RowsArgs rows_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
+static RowsArgs rows_args(const cutespmm_plan *p, bool all_rows, const float *B, uint64_t ldb, float *C, uint64_t ldc,
+                          uint32_t N)
 {
+    const HostPlan &h = p->host;
     RowsArgs a{};
     a.row_ptr = static_cast<const uint32_t *>(p->d_row_ptr);
     a.pairs = p->d_pairs;
-    a.tiles = p->d_tiles;
-    a.chunks = p->d_chunks;
-    a.long_rows = p->d_long_rows;
-    a.num_tiles = (uint32_t)(p->host.tile_rows.size() / 2);
-    a.num_chunks = p->num_row_chunks;
-    a.num_long_rows = (uint32_t)p->host.long_rows.size();
-    a.split_nnz = p->host.opts.split_nnz;
-    a.B = B; a.C = C; a.scratch = p->d_scratch;
-    a.ldb = ldb; a.ldc = ldc; a.ld_scratch = kScratchCols;
-    a.N = N;
-    return a;
-}
-static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
-{
-    BrickArgs a{};
-    a.items = p->d_items;
-    a.cols = static_cast<const uint32_t *>(p->d_bcols);
-    a.maps = static_cast<const uint32_t *>(p->d_bmaps);
-    a.vals = static_cast<const float *>(p->d_bvals);
-    a.num_items = (uint32_t)p->host.panel_items.size();
-    a.M = (uint32_t)p->host.M;
+    a.tiles = all_rows ? p->d_tiles_all : p->d_tiles;
+    a.chunks = all_rows ? p->d_chunks_all : p->d_chunks;
+    a.long_rows = all_rows ? p->d_long_rows_all : p->d_long_rows;
+    a.num_tiles = (uint32_t)(all_rows ? h.tiles_all.size() : h.tiles.size());
+    a.num_chunks = (uint32_t)(all_rows ? h.chunks_all.size() : h.chunks.size());
+    a.num_long_rows = (uint32_t)(all_rows ? h.long_rows_all.size() : h.long_rows.size());
+    a.split_nnz = h.opts.split_nnz;
     a.B = B; a.C = C; a.scratch = p->d_scratch;
     a.ldb = ldb; a.ldc = ldc; a.ld_scratch = kScratchCols;
     a.N = N;
     a.status = p->d_status;
     return a;
 }
+static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
+{
+    BrickArgs a{};
+    a.cols = static_cast<const uint32_t *>(p->d_bcols);
+    a.recs = static_cast<const uint32_t *>(p->d_brecs);
+    a.rec_off = static_cast<const uint32_t *>(p->d_brec_off);
+    a.warp_ranges = static_cast<const uint32_t *>(p->d_warp_ranges);
+    a.num_bricks = (uint32_t)p->host.num_bricks;
+    a.num_warps = p->brick_warps;
+    a.M = (uint32_t)p->host.M;
+    a.B = B; a.C = C;
+    a.ldb = ldb; a.ldc = ldc;
+    a.N = N;
+    a.status = p->d_status;
+    return a;
+}
+
+// Whether a window of N columns at these addresses runs the brick kernel for the brick panels; if
+// not, the row kernel executes every row from its all-rows work list.
+static bool use_brick(const cutespmm_plan *p, const float *B, uint64_t ldb, const float *C, uint64_t ldc, uint32_t N)
+{
+    return p->host.num_bricks && brick_supports(N, ldb, ldc, B, C);
+}
 
 int cutespmm_spmm_launch_count(const cutespmm_plan_t *p, uint32_t N)
 {
-    if (!p || N == 0) return 0;
-    const uint32_t windows = (N + kScratchCols - 1) / kScratchCols;
-    int per = 0;
-    if (!p->host.tile_rows.empty() || p->num_row_chunks) per += 1;
-    if (!p->host.panel_items.empty()) per += 1;
-    if (!p->host.long_rows.empty()) per += 1;
-    return per * (int)windows;
+    if (!p || N == 0 || p->host.M == 0) return 0;
+    int total = 0;
+    for (uint32_t n0 = 0; n0 < N; n0 += kScratchCols) {
+        const uint32_t nw = N - n0 < kScratchCols ? N - n0 : kScratchCols;
+        // alignment of the caller's pointers is unknown here: assume the aligned case
+        const HostPlan &h = p->host;
+        const bool brick = h.num_bricks && nw % 32 == 0;
+        const bool all_rows = !brick && h.num_bricks;
+        if (brick) total += 1;
+        if (all_rows ? (!h.tiles_all.empty() || !h.chunks_all.empty()) : (!h.tiles.empty() || !h.chunks.empty())) total += 1;
+        if (!(all_rows ? h.long_rows_all : h.long_rows).empty()) total += 1;
+    }
+    return total;
 }
 
 int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N,
@@ -273,19 +322,21 @@ int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float 
     if (!C && p->host.M) return fail(CUTESPMM_EINVAL, "C is NULL");
     if (!B && p->host.nnz) return fail(CUTESPMM_EINVAL, "B is NULL");
     if (ldb < N || ldc < N) return fail(CUTESPMM_EINVAL, "leading dimension smaller than N");
+    if (ldb >= (1ull << 32) || ldc >= (1ull << 32)) return fail(CUTESPMM_EUNSUPPORTED, "leading dimensions must be below 2^32 elements");
     if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 3) return fail(CUTESPMM_EINVAL, "B and C must be 4-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (p->host.M == 0) return CUTESPMM_OK;
     for (uint32_t n0 = 0; n0 < N; n0 += kScratchCols) {
         const uint32_t nw = N - n0 < kScratchCols ? N - n0 : kScratchCols;
         cudaError_t e;
-        if (!p->host.panel_items.empty()) {
+        const bool brick = use_brick(p, B + n0, ldb, C + n0, ldc, nw);
+        if (brick) {
             BrickArgs ba = brick_args(p, B + n0, ldb, C + n0, ldc, nw);
-            if (!brick_supports(nw, ldb, ldc, ba.B, ba.C))
-                return fail(CUTESPMM_EUNSUPPORTED, "the tensor-core path needs 16-byte aligned B and C, leading dimensions that are multiples of 4 and N a multiple of 32; build the plan with CUTESPMM_PATH_ROWS for other shapes");
             if ((e = launch_brick(ba, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "brick kernel launch");
         }
-        RowsArgs ra = rows_args(p, B + n0, ldb, C + n0, ldc, nw);
+        // brick panels whose shape the brick kernel does not take (N not a multiple of 32, unaligned
+        // operands) are executed by the row kernel from its all-rows work list
+        RowsArgs ra = rows_args(p, !brick && p->host.num_bricks, B + n0, ldb, C + n0, ldc, nw);
         if ((e = launch_rows(ra, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "row kernel launch");
         if ((e = launch_fixup(ra, s)) != cudaSuccess) return fail_cuda(e, "fix-up kernel launch");
     }

@@ -10,7 +10,7 @@ namespace cutespmm {
 struct RowsArgs {
     const uint32_t *row_ptr;   // M+1 offsets into pairs
     const void *pairs;         // nnz x {col, fp32 bits}
-    const void *tiles;         // num_tiles x {row_begin, row_end}
+    const void *tiles;         // num_tiles x {row_begin, row_end, pair_begin, pair_end}
     const void *chunks;        // num_chunks x {row, j0, j1, slot}
     const void *long_rows;     // num_long_rows x {row, slot0, slot1, -}
     uint32_t num_tiles, num_chunks, num_long_rows, split_nnz;
@@ -19,6 +19,7 @@ struct RowsArgs {
     float *scratch;            // partial sums, leading dimension ld_scratch
     uint64_t ldb, ldc, ld_scratch;
     uint32_t N;
+    uint32_t *status;          // device status word: set to 1 when a bounded wait gives up
 };
 
 cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s);
@@ -26,19 +27,19 @@ cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
 int rows_kernel_count(const RowsArgs &a);
 
 // Arguments of the tensor-core brick kernel.
+constexpr int kBrickWarps = 8;  // warps per block; each is an independent pipeline over its own brick range
 struct BrickArgs {
-    const void *items;           // num_items x PanelItem
-    const uint32_t *cols;        // active columns per item
-    const uint32_t *maps;        // 4 words per brick
-    const float *vals;           // packed values
-    uint32_t num_items;
+    const uint32_t *cols;         // 8 columns per brick (+ readable slack of one group behind the end)
+    const uint32_t *recs;         // brick records (map, flags, panel, values)
+    const uint32_t *rec_off;      // num_bricks+1 record offsets in 16-byte units (+ slack)
+    const uint32_t *warp_ranges;  // num_warps+1 brick indices: warp w runs bricks [w, w+1)
+    uint32_t num_bricks, num_warps;
     uint32_t M;
     const float *B;
     float *C;
-    float *scratch;
-    uint64_t ldb, ldc, ld_scratch;
+    uint64_t ldb, ldc;
     uint32_t N;
-    uint32_t *status;            // device status word (0 = fine)
+    uint32_t *status;             // device status word: set to 2 when a bounded wait gives up
 };
 
 cudaError_t launch_brick(const BrickArgs &a, int sm_count, cudaStream_t s);

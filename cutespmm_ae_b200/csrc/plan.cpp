@@ -32,6 +32,7 @@ static void fill_default_options(cutespmm_options_t &o, const cutespmm_options_t
     }
     o.struct_size = sizeof(o);
     if (o.split_nnz == 0) o.split_nnz = kDefaultSplitNnz;
+    if (o.split_nnz > kMaxSplitNnz) o.split_nnz = kMaxSplitNnz;
     if (o.tile_nnz == 0) o.tile_nnz = kDefaultTileCost;
     if (o.brick_density <= 0.0f) o.brick_density = 0.125f;
 }
@@ -82,49 +83,55 @@ static std::vector<uint32_t> analyze_panels(HostPlan &p)
     return ncols;
 }
 
-// Cuts the rows that the row kernel executes into tiles of about equal cost.  A tile is a run of
-// consecutive rows inside one stretch of row-kernel panels; long rows cost nothing here (their
-// nonzeros are executed as chunks).
-static void build_tiles(HostPlan &p)
+// Cuts the rows that the row kernel executes into tiles of about equal cost (nonzeros + kRowCost per
+// row).  A tile is a run of consecutive rows inside one stretch of row-kernel panels, bounded so that
+// its row pointers and pairs fit the kernel's shared-memory stage.  A long row ends the running
+// tile and is not part of any: its nonzeros are executed as chunks.
+static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &tiles, std::vector<Chunk> &chunks,
+                        std::vector<LongRow> &long_rows)
 {
     const uint64_t P = p.num_panels();
     const uint32_t split = p.opts.split_nnz;
     const uint64_t target = p.opts.tile_nnz;
-    p.tile_rows.clear();
-    p.chunks.clear();
-    p.long_rows.clear();
+    tiles.clear();
+    chunks.clear();
+    long_rows.clear();
     uint64_t q = 0;
     while (q < P) {
-        if (p.row_path[q]) { ++q; continue; }
+        if (!all_rows && p.row_path[q]) { ++q; continue; }
         uint64_t q1 = q;
-        while (q1 < P && !p.row_path[q1]) ++q1;
+        while (q1 < P && (all_rows || !p.row_path[q1])) ++q1;
         const uint64_t r_end = std::min<uint64_t>(p.M, q1 * kPanelRows);
         uint64_t r = q * kPanelRows;
         uint64_t begin = r, cost = 0;
+        auto close = [&](uint64_t end) {
+            if (end > begin) tiles.push_back(Tile{(uint32_t)begin, (uint32_t)end, p.row_ptr[begin], p.row_ptr[end]});
+            cost = 0;
+        };
         for (; r < r_end; ++r) {
             const uint32_t len = p.row_ptr[r + 1] - p.row_ptr[r];
             if (len > split) {
-                LongRow lr{(uint32_t)r, (uint32_t)p.chunks.size(), 0, 0};
-                for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; j += split)
-                    p.chunks.push_back(Chunk{(uint32_t)r, j, std::min<uint32_t>(j + split, p.row_ptr[r + 1]),
-                                             (uint32_t)p.chunks.size()});
-                lr.slot1 = (uint32_t)p.chunks.size();
-                p.long_rows.push_back(lr);
-                cost += kRowCost;
-            } else {
-                cost += len + kRowCost;
-            }
-            if (cost >= target || r + 1 - begin >= kMaxTileRows) {
-                p.tile_rows.push_back((uint32_t)begin);
-                p.tile_rows.push_back((uint32_t)(r + 1));
+                close(r);
                 begin = r + 1;
-                cost = 0;
+                LongRow lr{(uint32_t)r, (uint32_t)chunks.size(), 0, 0};
+                for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; j += split)
+                    chunks.push_back(Chunk{(uint32_t)r, j, std::min<uint32_t>(j + split, p.row_ptr[r + 1]),
+                                           (uint32_t)chunks.size()});
+                lr.slot1 = (uint32_t)chunks.size();
+                long_rows.push_back(lr);
+                continue;
+            }
+            if (p.row_ptr[r + 1] - p.row_ptr[begin] > kMaxTilePairs || r - begin >= kMaxTileRows) {
+                close(r);
+                begin = r;
+            }
+            cost += len + kRowCost;
+            if (cost >= target) {
+                close(r + 1);
+                begin = r + 1;
             }
         }
-        if (begin < r_end) {
-            p.tile_rows.push_back((uint32_t)begin);
-            p.tile_rows.push_back((uint32_t)r_end);
-        }
+        close(r_end);
         q = q1;
     }
 }
@@ -192,8 +199,9 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
             p.row_path[q] = (fill >= p.opts.brick_density && !long_row) ? 1 : 0;
         }
     }
-    build_tiles(p);
+    build_tiles(p, false, p.tiles, p.chunks, p.long_rows);
     build_brick_part(p, panel_ncols);
+    if (p.brick_panels) build_tiles(p, true, p.tiles_all, p.chunks_all, p.long_rows_all);
     return CUTESPMM_OK;
 }
 
@@ -213,20 +221,16 @@ void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float
                 rows[r].push_back({p.pairs[j].col, v});
             }
     }
-    for (const PanelItem &it : p.panel_items) {
-        const uint32_t nbricks = it.num_cols / kBrickCols;
-        uint32_t voff = it.val_begin;
-        for (uint32_t b = 0; b < nbricks; ++b) {
-            const uint32_t *map = &p.brick_maps[(size_t)(it.map_begin + b) * 4];
-            uint32_t cnt = 0;
-            for (uint32_t bit = 0; bit < 128; ++bit) {
-                if (!((map[bit >> 5] >> (bit & 31)) & 1u)) continue;
-                const uint32_t r = bit / kBrickCols, c = bit % kBrickCols;
-                rows[(size_t)it.panel * kPanelRows + r].push_back(
-                    {p.brick_cols[it.col_begin + b * kBrickCols + c], p.brick_vals[voff + cnt]});
-                ++cnt;
-            }
-            voff += (cnt + 3) / 4 * 4;
+    for (uint64_t k = 0; k < p.num_bricks; ++k) {
+        const uint32_t *rec = &p.brick_recs[(size_t)p.brick_rec_off[k] * 4];
+        const uint32_t panel = rec[5];
+        uint32_t cnt = 0;
+        for (uint32_t bit = 0; bit < 128; ++bit) {
+            if (!((rec[bit >> 5] >> (bit & 31)) & 1u)) continue;
+            float v;
+            std::memcpy(&v, &rec[kBrickRecHeaderWords + cnt], 4);
+            rows[(size_t)panel * kPanelRows + bit / kBrickCols].push_back({p.brick_cols[k * kBrickCols + bit % kBrickCols], v});
+            ++cnt;
         }
     }
     uint64_t off = 0;

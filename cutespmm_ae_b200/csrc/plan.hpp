@@ -14,9 +14,11 @@ constexpr uint32_t kPanelRows = 16;   // row-panel height; HRPB's TM (inc.h:18-2
 constexpr uint32_t kBlockCols = 16;   // active-column block width; HRPB's TK (inc.h:21-23)
 constexpr uint32_t kBrickCols = 8;    // one tensor-core brick is 16 rows x 8 active columns (mma m16n8k8)
 constexpr uint32_t kRowCost = 4;      // scheduling cost of a row besides its nonzeros (pointer loads, C store)
-constexpr uint32_t kDefaultSplitNnz = 1024;
-constexpr uint32_t kDefaultTileCost = 1024;
-constexpr uint32_t kMaxTileRows = 512;
+constexpr uint32_t kDefaultSplitNnz = 256;
+constexpr uint32_t kDefaultTileCost = 512;
+constexpr uint32_t kMaxTileRows = 128;   // rows of one scheduling tile (bounds the staged row-pointer slice)
+constexpr uint32_t kMaxTilePairs = 640;  // nonzeros of one scheduling tile (bounds the staged pair slice)
+constexpr uint32_t kMaxSplitNnz = 384;   // a row must fit a tile together with a part-filled one
 constexpr uint32_t kScratchCols = 512;  // widest N one launch handles; wider products run in column windows
 
 // One nonzero as the row kernel reads it: column index and fp32 bit pattern side by side (8 bytes,
@@ -24,6 +26,12 @@ constexpr uint32_t kScratchCols = 512;  // widest N one launch handles; wider pr
 struct Pair {
     uint32_t col;
     uint32_t val_bits;
+};
+
+// A scheduling tile of the row kernel: rows [row_begin, row_end) whose nonzeros are pairs
+// [pair_begin, pair_end); at most kMaxTileRows rows and kMaxTilePairs nonzeros, no long row inside.
+struct Tile {
+    uint32_t row_begin, row_end, pair_begin, pair_end;
 };
 
 // A chunk of a long row: nonzeros [j0, j1) of `row`; its partial result is row `slot` of the scratch.
@@ -35,17 +43,15 @@ struct LongRow {
     uint32_t row, slot0, slot1, pad;
 };
 
-// Work item of the brick kernel: one 16-row panel (or a piece of one).
-struct PanelItem {
-    uint32_t panel;       // panel index: rows [16*panel, 16*panel+16)
-    uint32_t col_begin;   // first entry of this item in brick_cols[]
-    uint32_t num_cols;    // active columns of the item (multiple of 8, padded entries repeat a valid column)
-    uint32_t val_begin;   // first fp32 of this item in brick_vals[]
-    uint32_t map_begin;   // first bitmap (one 128-bit map per brick) in brick_maps[]
-    uint32_t flags;       // bit 0: result goes to scratch slot `slot` instead of C
-    uint32_t slot;
-    uint32_t pad;
-};
+// The brick kernel reads one flat stream of bricks (16 rows x 8 active columns each), panel after
+// panel.  Brick k owns columns brick_cols[8k .. 8k+8) and the record that starts at 16-byte unit
+// brick_rec_off[k] of brick_recs:
+//     words 0-3   occupancy map, bit (r*8 + c) set when A[row r of the panel][column c of the brick] is stored
+//     word  4     bit 0: last brick of its panel
+//     word  5     panel index (rows 16*panel .. 16*panel+15)
+//     words 6-7   0
+//     words 8..   the stored values (fp32) in map-bit order, padded with zeros to a multiple of 4
+constexpr uint32_t kBrickRecHeaderWords = 8;
 
 struct HostPlan {
     uint64_t M = 0, K = 0, nnz = 0;
@@ -54,7 +60,7 @@ struct HostPlan {
     // ---- row kernel ----
     std::vector<uint32_t> row_ptr;       // M+1, offsets into pairs
     std::vector<Pair> pairs;             // nnz
-    std::vector<uint32_t> tile_rows;     // T+1 row boundaries of the scheduling tiles
+    std::vector<Tile> tiles;
     std::vector<uint8_t> row_path;       // per panel: 0 = rows kernel, 1 = brick kernel
     std::vector<Chunk> chunks;
     std::vector<LongRow> long_rows;
@@ -63,11 +69,16 @@ struct HostPlan {
     std::vector<uint32_t> blocked_row_ptr;  // num_panels+1
     std::vector<uint32_t> active_cols;      // per panel ascending distinct columns, zero-padded to x16
 
+    // ---- row kernel over every row (used when a product's N does not fit the brick kernel) ----
+    std::vector<Tile> tiles_all;
+    std::vector<Chunk> chunks_all;
+    std::vector<LongRow> long_rows_all;
+
     // ---- brick kernel ----
-    std::vector<PanelItem> panel_items;
-    std::vector<uint32_t> brick_cols;   // active columns per item (padded to x8)
-    std::vector<uint32_t> brick_maps;   // 4 words per brick, bit (r*8 + c) of the 128-bit map = A[r][c] present
-    std::vector<float> brick_vals;      // values in bit order, each brick padded to a multiple of 4 floats
+    std::vector<uint32_t> brick_cols;     // 8 per brick (a short last brick repeats its last column)
+    std::vector<uint32_t> brick_recs;     // records, see above
+    std::vector<uint32_t> brick_rec_off;  // num_bricks+1 offsets in 16-byte units
+    std::vector<uint32_t> panel_first_brick;  // per brick panel (+1): index of its first brick
     uint64_t num_bricks = 0;
     uint64_t brick_panels = 0;
 

@@ -17,12 +17,30 @@
 #include <cstdint>
 
 #include "device_plan.hpp"
+#include "plan.hpp"
+#include "ptx.cuh"
 
 namespace cutespmm {
 
 namespace {
 
+#ifndef ROWS_MIN_BLOCKS
+#define ROWS_MIN_BLOCKS 4
+#endif
+#ifndef ROWS_UNROLL
+#define ROWS_UNROLL 4
+#endif
 constexpr int kWarps = 8;
+constexpr int kStages = 3;  // tiles in flight per block (TMA bulk copies into shared memory)
+
+// One staged tile: its descriptor, the slice of row pointers and the slice of (column, value) pairs,
+// each fetched by one bulk copy that starts on a 16-byte boundary at or before the first needed
+// element (hence the slack of 3 words / 1 pair in front and behind).
+struct __align__(16) TileStage {
+    uint4 desc;                               // row_begin, row_end, pair_begin, pair_end
+    uint32_t row_ptr[kMaxTileRows + 8];
+    uint2 pairs[kMaxTilePairs + 2];
+};
 constexpr unsigned kFull = 0xffffffffu;
 
 template <int VEC> struct Vec;
@@ -101,7 +119,7 @@ __device__ __forceinline__ void accumulate(typename Vec<VEC>::T (&acc)[CH], cons
 }
 
 template <int VEC, int CH, bool FULL>
-__global__ void __launch_bounds__(kWarps * 32) spmm_rows_kernel(RowsArgs a)
+__global__ void __launch_bounds__(kWarps * 32, ROWS_MIN_BLOCKS) spmm_rows_kernel(RowsArgs a)
 {
     using V = typename Vec<VEC>::T;
     const int lane = threadIdx.x & 31;
@@ -111,6 +129,7 @@ __global__ void __launch_bounds__(kWarps * 32) spmm_rows_kernel(RowsArgs a)
 #pragma unroll
     for (int ch = 0; ch < CH; ++ch) ok[ch] = FULL || (col0 + ch * 32 * VEC < a.N);
     const float *bl = a.B + col0;
+    const uint32_t ldb32 = (uint32_t)a.ldb;  // < 2^32 (checked by the caller): one 32x32->64 multiply per address
     const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
 
     // chunks of long rows first: they are the largest single work items
@@ -129,19 +148,103 @@ __global__ void __launch_bounds__(kWarps * 32) spmm_rows_kernel(RowsArgs a)
         }
     }
 
-    for (uint32_t t = blockIdx.x; t < a.num_tiles; t += gridDim.x) {
-        const uint2 tr = __ldg(reinterpret_cast<const uint2 *>(a.tiles) + t);  // rows [x, y)
-        for (uint32_t r = tr.x + warp; r < tr.y; r += kWarps) {
-            const uint32_t j0 = __ldg(a.row_ptr + r), j1 = __ldg(a.row_ptr + r + 1);
-            if (j1 - j0 > a.split_nnz) continue;  // long row: done as chunks, written by the fix-up kernel
+    // ---- tiles: descriptor, row pointers and pairs arrive in shared memory by TMA, kStages deep ----
+    __shared__ TileStage stage[kStages];
+    __shared__ __align__(8) uint64_t full_bar[kStages];
+    __shared__ uint32_t next_row[kStages];  // rows of the staged tile already claimed by a warp
+    __shared__ uint32_t warps_done[kStages];
+
+    const uint4 *tiles = reinterpret_cast<const uint4 *>(a.tiles);
+    auto issue = [&](uint32_t t, int s) {  // one thread: fetch tile t into stage s
+        const uint4 d = __ldg(tiles + t);
+        const uint32_t rb = d.x & ~3u, re = (d.y + 1 + 3) & ~3u;  // row pointers [rb, re) cover d.x .. d.y
+        const uint32_t jb = d.z & ~1u, je = (d.w + 1) & ~1u;      // pairs [jb, je) cover d.z .. d.w-1
+        const uint32_t bytes = 16u + (re - rb) * 4u + (je - jb) * 8u;
+        ptx::mbar_expect_tx(&full_bar[s], bytes);
+        ptx::bulk_g2s(&stage[s].desc, tiles + t, 16u, &full_bar[s]);
+        ptx::bulk_g2s(stage[s].row_ptr, a.row_ptr + rb, (re - rb) * 4u, &full_bar[s]);
+        if (je > jb) ptx::bulk_g2s(stage[s].pairs, pairs + jb, (je - jb) * 8u, &full_bar[s]);
+    };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            next_row[s] = 0;
+            warps_done[s] = 0;
+        }
+        ptx::fence_mbar_init();
+        for (int s = 0; s < kStages; ++s) {
+            const uint64_t t = blockIdx.x + (uint64_t)s * gridDim.x;
+            if (t < a.num_tiles) issue((uint32_t)t, s);
+        }
+    }
+    __syncthreads();
+
+    for (uint32_t i = 0;; ++i) {
+        const uint64_t t = blockIdx.x + (uint64_t)i * gridDim.x;
+        if (t >= a.num_tiles) break;
+        const int s = i % kStages;
+        if (!ptx::mbar_wait(&full_bar[s], (i / kStages) & 1u)) {
+            if (lane == 0) atomicExch(a.status, 1u);  // the copy never landed: report, do not hang
+            break;
+        }
+        const uint4 d = stage[s].desc;
+        const uint32_t rb = d.x & ~3u, jb = d.z & ~1u;
+        for (;;) {
+            uint32_t r = 0;
+            if (lane == 0) r = atomicAdd(&next_row[s], 1u);
+            r = __shfl_sync(kFull, r, 0) + d.x;
+            if (r >= d.y) break;
+            const uint32_t j0 = stage[s].row_ptr[r - rb], j1 = stage[s].row_ptr[r - rb + 1];
             V acc[CH];
 #pragma unroll
             for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
-            accumulate<VEC, CH, FULL>(acc, pairs, j0, j1, bl, a.ldb, ok, lane);
+            constexpr int U = (CH == 1) ? ROWS_UNROLL : ROWS_UNROLL / 2;  // rows of B in flight per warp and step
+            uint32_t j = j0 - jb, jend = j1 - jb;  // positions in the staged pair slice
+            for (; j + U <= jend; j += U) {
+                float v[U];
+                V b[U][CH];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint2 pr = stage[s].pairs[j + u];  // all lanes read one address: broadcast
+                    v[u] = __uint_as_float(pr.y);
+                    const float *row = bl + (uint64_t)pr.x * ldb32;
+#pragma unroll
+                    for (int ch = 0; ch < CH; ++ch) {
+                        if (FULL || ok[ch]) b[u][ch] = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
+                        else zero_vec(b[u][ch]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int ch = 0; ch < CH; ++ch) fma_vec(acc[ch], v[u], b[u][ch]);
+            }
+            for (; j < jend; ++j) {
+                const uint2 pr = stage[s].pairs[j];
+                const float *row = bl + (uint64_t)pr.x * ldb32;
+#pragma unroll
+                for (int ch = 0; ch < CH; ++ch)
+                    if (FULL || ok[ch]) fma_vec(acc[ch], __uint_as_float(pr.y), ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC)));
+            }
             float *out = a.C + (uint64_t)r * a.ldc + col0;
 #pragma unroll
             for (int ch = 0; ch < CH; ++ch)
                 if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(out + ch * 32 * VEC), acc[ch]);
+        }
+        // this warp is finished with stage s; the last warp to say so refills it
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence_block();
+            if (atomicAdd(&warps_done[s], 1u) == kWarps - 1) {
+                __threadfence_block();
+                warps_done[s] = 0;
+                next_row[s] = 0;
+                const uint64_t t2 = t + (uint64_t)kStages * gridDim.x;
+                if (t2 < a.num_tiles) {
+                    ptx::fence_async_smem();
+                    issue((uint32_t)t2, s);
+                }
+            }
         }
     }
 }

@@ -27,8 +27,6 @@ def run(plan, B_np, **kw):
 def test_golden_fixtures(oracle_mod, name, path):
     gd = load_golden(name)
     N = int(gd["N"])
-    if path != cs.PATH_ROWS and N % 32:
-        pytest.skip("tensor-core path takes N in multiples of 32")
     p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"], path=path)
     C = run(p, gd["B"])
     assert oracle_mod.rel_fro(gd["C"], C) <= PATH_TOL[path]
@@ -47,9 +45,6 @@ def test_named_workloads_match_oracle(oracle_mod, workload, Ns, path):
         C = run(p, B)
         err = oracle_mod.rel_fro(ref, C)
         assert err <= PATH_TOL[path], (workload, N, err)
-        if path == cs.PATH_ROWS:
-            # the reference's own metric (max element-wise relative error, inc.h:84-110), informational bound
-            assert oracle_mod.max_rel_err(ref, C) < 5e-2
 
 
 @pytest.mark.parametrize("N", [1, 3, 8, 33, 48, 64, 100, 128, 130, 200, 256, 384, 512, 516, 640, 1024])
