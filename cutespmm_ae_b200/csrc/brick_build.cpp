@@ -18,6 +18,7 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
     p.brick_recs.clear();
     p.brick_rec_off.clear();
     p.panel_first_brick.clear();
+    p.panel_last_brick.clear();
     p.num_bricks = 0;
     p.brick_panels = 0;
     const uint64_t P = p.num_panels();
@@ -30,11 +31,12 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
         acol_off += (uint64_t)((nc + kBlockCols - 1) / kBlockCols) * kBlockCols;
         if (!p.row_path[q] || nc == 0) continue;
         ++p.brick_panels;
-        p.panel_first_brick.push_back((uint32_t)p.num_bricks);
+        p.panel_first_brick.push_back((uint32_t)p.brick_rec_off.size());  // slot index, a multiple of 4
         const uint32_t *acols = &p.active_cols[my_off];
         const uint64_t r0 = q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
         const uint32_t nbricks = (nc + kBrickCols - 1) / kBrickCols;
-        for (uint32_t c = 0; c < nbricks * kBrickCols; ++c) p.brick_cols.push_back(acols[std::min(c, nc - 1)]);
+        const uint32_t nslots = (nbricks + 3) / 4 * 4;  // the panel's brick slots: groups of 4 start on a panel boundary
+        for (uint32_t c = 0; c < nslots * kBrickCols; ++c) p.brick_cols.push_back(acols[std::min(c, nc - 1)]);
         img.assign((size_t)nbricks * 128, 0.0f);
         present.assign((size_t)nbricks * 128, 0);
         for (uint64_t r = r0; r < r1; ++r) {
@@ -67,9 +69,10 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
             for (; cnt % 4; ++cnt) p.brick_recs.push_back(0u);
             ++p.num_bricks;
         }
+        for (uint32_t b = nbricks; b < nslots; ++b) p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));  // empty slots
+        p.panel_last_brick.push_back((uint32_t)(p.brick_rec_off.size() - (nslots - nbricks)));
     }
     p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));
-    p.panel_first_brick.push_back((uint32_t)p.num_bricks);
 }
 
 }  // namespace cutespmm

@@ -5,8 +5,9 @@
 // What is kept: 16-row panels, active-column compaction, occupancy bitmaps expanded into MMA
 // A-fragments by popcount (kernel.cu:20-27), TF32 inputs rounded to nearest (cvt.rna,
 // kernel.cu:28-35) with fp32 accumulation.  What is different:
-//   * every warp is an autonomous pipeline over a contiguous range of the flat brick stream; it
-//     owns a ring of kStages shared-memory stages and one mbarrier per stage.  The reference
+//   * every warp is an autonomous pipeline over its own sequence of panels (panels are dealt
+//     round-robin over the warps of the grid); it owns a ring of kStages shared-memory stages and
+//     one mbarrier per stage.  The reference
 //     drains a depth-2 cp.async pipeline and runs __syncthreads after every block of 16 columns
 //     (kernel.cu:220-222); here no two warps ever wait for each other;
 //   * the eight gathered rows of B of a brick arrive by eight TMA bulk copies (one 512-byte row slab
@@ -32,7 +33,7 @@ namespace cutespmm {
 namespace {
 
 #ifndef BRICK_STAGES
-#define BRICK_STAGES 4
+#define BRICK_STAGES 5
 #endif
 constexpr int kStages = BRICK_STAGES;
 constexpr unsigned kFull = 0xffffffffu;
@@ -43,7 +44,9 @@ template <int NT> struct StageLayout {
     static constexpr int kStride = kSlab + 8;    // floats between consecutive B rows in shared memory
     static constexpr int kBBytes = 8 * kStride * 4;
     static constexpr int kStageBytes = kBBytes + kRecWords * 4;
-    static constexpr int kWarpBytes = kStages * kStageBytes + kStages * 8;
+    // a warp's region: its stages, then its mbarriers; rounded so the next warp's stages stay 128-byte aligned
+    static constexpr int kWarpBytes = (kStages * kStageBytes + kStages * 8 + 127) / 128 * 128;
+    static_assert(kStageBytes % 16 == 0 && kBBytes % 16 == 0, "TMA destinations must be 16-byte aligned");
 };
 
 template <int NT>
@@ -53,9 +56,12 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const uint32_t gw = blockIdx.x * kBrickWarps + warp;
-    const uint32_t kb = __ldg(a.warp_ranges + gw), ke = __ldg(a.warp_ranges + gw + 1);
-    if (kb >= ke) return;  // warps never synchronise with each other, so leaving early is safe
+    // Panels are dealt round-robin over all warps of the grid: at any moment the grid works on one
+    // contiguous window of the matrix, so a row of B that several panels share is fetched from HBM
+    // once and found in L2 by the others.
+    const uint32_t W = gridDim.x * kBrickWarps;
+    uint32_t ord = blockIdx.x * kBrickWarps + warp;  // this warp's current panel (ordinal among brick panels)
+    if (ord >= a.num_panels) return;  // warps never synchronise with each other, so leaving early is safe
     const uint32_t n0 = blockIdx.y * L::kSlab;
 
     unsigned char *mine = smem_raw + (size_t)warp * L::kWarpBytes;
@@ -68,18 +74,36 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     }
     __syncwarp();
 
-    // Producer metadata, one group of 4 bricks at a time: lane l holds column l of the group's 32
-    // columns, lanes 0..4 hold the group's five record offsets.  The next group is loaded one group
-    // ahead of its use.
-    uint32_t G = kb >> 2;
+    // ---- producer state --------------------------------------------------------------------------
+    // Metadata travels in groups of 4 brick slots: lane l holds column l of the group's 32 columns,
+    // lanes 0..4 hold its five record offsets.  A panel starts on a group boundary.  Loaded ahead of
+    // use: the next group of the current panel, the first group of the warp's next panel, and the
+    // slot range of the panel after that.
     auto load_cols = [&](uint32_t g) { return __ldg(a.cols + (size_t)g * 32 + lane); };
     auto load_offs = [&](uint32_t g) { return lane < 5 ? __ldg(a.rec_off + (size_t)g * 4 + lane) : 0u; };
-    uint32_t mc_cur = load_cols(G), mo_cur = load_offs(G);
-    uint32_t mc_nxt = load_cols(G + 1), mo_nxt = load_offs(G + 1);
+    auto load_range = [&](uint32_t o, uint32_t &k0, uint32_t &k1) {
+        k0 = k1 = 0;
+        if (o < a.num_panels) {
+            k0 = __ldg(a.panel_first + o);
+            k1 = __ldg(a.panel_last + o);
+        }
+    };
+    uint32_t pk, pk_end;  // producer cursor: next slot to issue, end of its panel
+    load_range(ord, pk, pk_end);
+    uint32_t G = pk >> 2;
+    uint32_t mc_cur = load_cols(G), mo_cur = load_offs(G), mc_nxt = load_cols(G + 1), mo_nxt = load_offs(G + 1);
+    uint32_t n_k0, n_k1, nn_k0, nn_k1;  // slot ranges of the next panel and the one after (k0 == k1: none)
+    load_range(ord + W, n_k0, n_k1);
+    load_range(ord + 2 * W, nn_k0, nn_k1);
+    uint32_t n_mc = load_cols(n_k0 >> 2), n_mo = load_offs(n_k0 >> 2);
+    uint32_t p_ord = ord;            // panel ordinal of the producer cursor
+    uint32_t issued = 0, done = 0;   // bricks issued / consumed by this warp so far
 
     const float *Bn = a.B + n0;
     const uint32_t ldb32 = (uint32_t)a.ldb;
-    auto issue = [&](uint32_t k) {  // start the copies of brick k into its stage
+    auto producer_has_work = [&]() { return pk < pk_end; };
+    auto issue_one = [&]() {  // start the copies of slot pk into stage issued % kStages, then advance the cursor
+        const uint32_t k = pk;
         if ((k >> 2) != G) {
             ++G;
             mc_cur = mc_nxt;
@@ -87,7 +111,7 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
             mc_nxt = load_cols(G + 1);
             mo_nxt = load_offs(G + 1);
         }
-        const int s = (k - kb) % kStages;
+        const int s = issued % kStages;
         const uint32_t col = __shfl_sync(kFull, mc_cur, (k & 3) * 8 + (lane & 7));
         const uint32_t o0 = __shfl_sync(kFull, mo_cur, k & 3), o1 = __shfl_sync(kFull, mo_cur, (k & 3) + 1);
         const uint32_t rec_bytes = (o1 - o0) * 16u;
@@ -97,6 +121,24 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
             ptx::bulk_g2s(stage_b(s) + lane * L::kStride, Bn + (uint64_t)col * ldb32, L::kSlab * 4u, &full[s]);
         else if (lane == 8)
             ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)o0 * 4, rec_bytes, &full[s]);
+        ++issued;
+        if (++pk == pk_end) {  // panel finished: move the cursor to the warp's next panel
+            p_ord += W;
+            pk = n_k0;
+            pk_end = n_k1;
+            G = pk >> 2;
+            mc_cur = n_mc;
+            mo_cur = n_mo;
+            n_k0 = nn_k0;
+            n_k1 = nn_k1;
+            if (pk < pk_end) {
+                mc_nxt = load_cols(G + 1);
+                mo_nxt = load_offs(G + 1);
+                n_mc = load_cols(n_k0 >> 2);
+                n_mo = load_offs(n_k0 >> 2);
+                load_range(p_ord + 2 * W, nn_k0, nn_k1);
+            }
+        }
     };
 
     // lane-constant pieces of the A-fragment expansion (mma.m16n8k8 row-major A: a0 = A[g][t],
@@ -110,14 +152,14 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
-    uint32_t pk = kb;
-    for (uint32_t k = kb; k < ke; ++k) {
-        while (pk < ke && pk < k + kStages) issue(pk++);
-        const int s = (k - kb) % kStages;
-        if (!ptx::mbar_wait(&full[s], ((k - kb) / kStages) & 1u)) {
+    for (;;) {
+        while (producer_has_work() && issued < done + kStages) issue_one();
+        if (done == issued) break;  // nothing in flight and nothing left to issue
+        const int s = done % kStages;
+        if (!ptx::mbar_wait(&full[s], (done / kStages) & 1u)) {
             if (lane == 0) atomicExch(a.status, 2u);  // the copies never landed: report, do not hang
-            // give the copies still in flight a bounded chance to land before the block's shared memory is reused
-            for (uint32_t j = k + 1; j < pk; ++j) ptx::mbar_wait(&full[(j - kb) % kStages], ((j - kb) / kStages) & 1u);
+            // give the copies still in flight a bounded chance to land before the shared memory is reused
+            for (uint32_t j = done + 1; j < issued; ++j) ptx::mbar_wait(&full[j % kStages], (j / kStages) & 1u);
             return;
         }
         const uint32_t *rec = stage_rec(s);
@@ -150,11 +192,12 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
                 acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
             }
         }
+        ++done;
         __syncwarp();  // every lane is done with stage s before the next iteration refills it
     }
 }
 
-template <int NT> cudaError_t launch_brick_t(const BrickArgs &a, cudaStream_t s)
+template <int NT> cudaError_t launch_brick_t(const BrickArgs &a, int sm_count, cudaStream_t s)
 {
     using L = StageLayout<NT>;
     constexpr int smem = kBrickWarps * L::kWarpBytes;
@@ -165,7 +208,9 @@ template <int NT> cudaError_t launch_brick_t(const BrickArgs &a, cudaStream_t s)
         configured = true;
     }
     const uint32_t slabs = a.N / L::kSlab;
-    spmm_brick_kernel<NT><<<dim3(a.num_warps / kBrickWarps, slabs), kBrickWarps * 32, smem, s>>>(a);
+    uint32_t blocks = (a.num_panels + kBrickWarps - 1) / kBrickWarps;
+    if (blocks > (uint32_t)sm_count) blocks = (uint32_t)sm_count;  // one resident block per SM, persistent
+    spmm_brick_kernel<NT><<<dim3(blocks, slabs), kBrickWarps * 32, smem, s>>>(a);
     return cudaGetLastError();
 }
 
@@ -177,12 +222,12 @@ bool brick_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const
     return N % 32 == 0 && N > 0 && !((pb | pc) & 15) && !((ldb | ldc) & 3);
 }
 
-cudaError_t launch_brick(const BrickArgs &a, int /*sm_count*/, cudaStream_t s)
+cudaError_t launch_brick(const BrickArgs &a, int sm_count, cudaStream_t s)
 {
     if (a.num_bricks == 0) return cudaSuccess;
-    if (a.N % 128 == 0) return launch_brick_t<16>(a, s);
-    if (a.N % 64 == 0) return launch_brick_t<8>(a, s);
-    return launch_brick_t<4>(a, s);
+    if (a.N % 128 == 0) return launch_brick_t<16>(a, sm_count, s);
+    if (a.N % 64 == 0) return launch_brick_t<8>(a, sm_count, s);
+    return launch_brick_t<4>(a, sm_count, s);
 }
 
 }  // namespace cutespmm

@@ -47,8 +47,7 @@ struct cutespmm_plan {
     // device arrays
     void *d_row_ptr = nullptr, *d_pairs = nullptr, *d_tiles = nullptr, *d_chunks = nullptr, *d_long_rows = nullptr;
     void *d_tiles_all = nullptr, *d_chunks_all = nullptr, *d_long_rows_all = nullptr;
-    void *d_bcols = nullptr, *d_brecs = nullptr, *d_brec_off = nullptr, *d_warp_ranges = nullptr;
-    uint32_t brick_warps = 0;
+    void *d_bcols = nullptr, *d_brecs = nullptr, *d_brec_off = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
     float *d_scratch = nullptr;
     uint32_t *d_status = nullptr;
     // staging for the host-buffer call
@@ -63,7 +62,7 @@ struct cutespmm_plan {
         cudaGetDevice(&cur);
         if (cur != device) cudaSetDevice(device);
         for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
-                        d_bcols, d_brecs, d_brec_off, d_warp_ranges, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
+                        d_bcols, d_brecs, d_brec_off, d_panel_first, d_panel_last, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
@@ -160,32 +159,15 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
     UP(h.chunks_all, p->d_chunks_all)
     UP(h.long_rows_all, p->d_long_rows_all)
     if (h.num_bricks) {
-        // the producer lanes prefetch one group (4 bricks) beyond the one in use: keep that readable
+        // the producer lanes prefetch a group (4 brick slots) beyond the one in use: keep that readable
         std::vector<uint32_t> bc(h.brick_cols), ro(h.brick_rec_off);
         bc.resize(bc.size() + 96, 0u);
         ro.resize(ro.size() + 16, ro.back());
-        // contiguous brick ranges of about equal cost, one per warp, cut at panel boundaries
-        p->brick_warps = (uint32_t)prop.multiProcessorCount * kBrickWarps;
-        std::vector<uint32_t> wr(p->brick_warps + 1, (uint32_t)h.num_bricks);
-        const std::vector<uint32_t> &pf = h.panel_first_brick;  // brick_panels + 1 entries
-        const uint64_t np = pf.size() - 1;
-        auto cost_before = [&](uint64_t panel) { return 2ull * pf[panel] + panel; };  // brick = 2, panel epilogue = 1
-        const uint64_t total = cost_before(np);
-        wr[0] = 0;
-        uint64_t lo = 0;
-        for (uint32_t w = 1; w < p->brick_warps; ++w) {
-            const uint64_t want = total * w / p->brick_warps;
-            uint64_t hi = np;
-            while (lo < hi) {
-                const uint64_t mid = lo + (hi - lo) / 2;
-                if (cost_before(mid) < want) lo = mid + 1; else hi = mid;
-            }
-            wr[w] = pf[lo];
-        }
         UP(bc, p->d_bcols)
         UP(h.brick_recs, p->d_brecs)
         UP(ro, p->d_brec_off)
-        UP(wr, p->d_warp_ranges)
+        UP(h.panel_first_brick, p->d_panel_first)
+        UP(h.panel_last_brick, p->d_panel_last)
     }
 #undef UP
     const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
@@ -278,9 +260,10 @@ static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb
     a.cols = static_cast<const uint32_t *>(p->d_bcols);
     a.recs = static_cast<const uint32_t *>(p->d_brecs);
     a.rec_off = static_cast<const uint32_t *>(p->d_brec_off);
-    a.warp_ranges = static_cast<const uint32_t *>(p->d_warp_ranges);
+    a.panel_first = static_cast<const uint32_t *>(p->d_panel_first);
+    a.panel_last = static_cast<const uint32_t *>(p->d_panel_last);
     a.num_bricks = (uint32_t)p->host.num_bricks;
-    a.num_warps = p->brick_warps;
+    a.num_panels = (uint32_t)p->host.brick_panels;
     a.M = (uint32_t)p->host.M;
     a.B = B; a.C = C;
     a.ldb = ldb; a.ldc = ldc;

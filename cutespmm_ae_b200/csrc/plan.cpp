@@ -221,7 +221,8 @@ void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float
                 rows[r].push_back({p.pairs[j].col, v});
             }
     }
-    for (uint64_t k = 0; k < p.num_bricks; ++k) {
+    for (uint64_t k = 0; k + 1 < p.brick_rec_off.size(); ++k) {
+        if (p.brick_rec_off[k + 1] == p.brick_rec_off[k]) continue;  // empty slot
         const uint32_t *rec = &p.brick_recs[(size_t)p.brick_rec_off[k] * 4];
         const uint32_t panel = rec[5];
         uint32_t cnt = 0;

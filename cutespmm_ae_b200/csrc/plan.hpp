@@ -77,8 +77,11 @@ struct HostPlan {
     // ---- brick kernel ----
     std::vector<uint32_t> brick_cols;     // 8 per brick (a short last brick repeats its last column)
     std::vector<uint32_t> brick_recs;     // records, see above
-    std::vector<uint32_t> brick_rec_off;  // num_bricks+1 offsets in 16-byte units
-    std::vector<uint32_t> panel_first_brick;  // per brick panel (+1): index of its first brick
+    std::vector<uint32_t> brick_rec_off;  // per brick slot (+1) the record offset in 16-byte units
+    // Brick slots: every panel's bricks are followed by empty slots up to a multiple of 4, so a
+    // panel starts on a group-of-4 boundary of brick_cols / brick_rec_off.
+    std::vector<uint32_t> panel_first_brick;  // per brick panel: slot of its first brick (multiple of 4)
+    std::vector<uint32_t> panel_last_brick;   // per brick panel: one past the slot of its last brick
     uint64_t num_bricks = 0;
     uint64_t brick_panels = 0;
 

@@ -28,7 +28,7 @@ namespace {
 #define ROWS_MIN_BLOCKS 4
 #endif
 #ifndef ROWS_UNROLL
-#define ROWS_UNROLL 4
+#define ROWS_UNROLL 8
 #endif
 constexpr int kWarps = 8;
 constexpr int kStages = 3;  // tiles in flight per block (TMA bulk copies into shared memory)
