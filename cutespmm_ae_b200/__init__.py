@@ -35,7 +35,7 @@ class CuteSpmmError(RuntimeError):
 
 class Options(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("path", C.c_uint32), ("split_nnz", C.c_uint32),
-                ("tile_nnz", C.c_uint32), ("brick_density", C.c_float), ("reserved", C.c_uint32 * 3)]
+                ("tile_nnz", C.c_uint32), ("brick_density", C.c_float), ("flags", C.c_uint32), ("reserved", C.c_uint32 * 2)]
 
 
 class PlanInfo(C.Structure):
@@ -100,12 +100,12 @@ class Plan:
     of SPMM_TC (spmm.cu:691-822).  `host_only=True` builds the plan without touching CUDA."""
 
     def __init__(self, M: int, K: int, row_ptr, cols, vals, *, path: int = PATH_AUTO, split_nnz: int = 0,
-                 tile_nnz: int = 0, brick_density: float = 0.0, host_only: bool = False):
+                 tile_nnz: int = 0, brick_density: float = 0.0, round_b_nearest: bool = False, host_only: bool = False):
         self._h = C.c_void_p()
         rp, cc, vv = _np(row_ptr, np.uint64), _np(cols, np.uint32), _np(vals, np.float32)
         if rp.shape[0] != M + 1:
             raise ValueError("row_ptr must have M+1 entries")
-        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density)
+        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, 1 if round_b_nearest else 0)
         fn = lib.cutespmm_plan_build_host if host_only else lib.cutespmm_plan_create
         _check(fn(C.byref(self._h), M, K, rp.ctypes.data, cc.ctypes.data, vv.ctypes.data, C.byref(opts)))
         self.M, self.K, self.nnz = M, K, int(rp[-1])
@@ -116,7 +116,7 @@ class Plan:
         return cls(A.M, A.K, A.row_ptr, A.cols, A.vals, **kw)
 
     def close(self) -> None:
-        if getattr(self, "_h", None) and self._h.value:
+        if getattr(self, "_h", None) and self._h.value and lib is not None:  # lib is None at interpreter shutdown
             lib.cutespmm_plan_destroy(self._h)
             self._h = C.c_void_p()
 

@@ -33,7 +33,7 @@ namespace cutespmm {
 namespace {
 
 #ifndef BRICK_STAGES
-#define BRICK_STAGES 5
+#define BRICK_STAGES 3
 #endif
 constexpr int kStages = BRICK_STAGES;
 constexpr unsigned kFull = 0xffffffffu;
@@ -49,7 +49,9 @@ template <int NT> struct StageLayout {
     static_assert(kStageBytes % 16 == 0 && kBBytes % 16 == 0, "TMA destinations must be 16-byte aligned");
 };
 
-template <int NT>
+// ROUND_B: round the elements of B to tf32 to nearest (cvt.rna, what the reference does,
+// kernel.cu:35) instead of letting the tensor core drop the low 13 mantissa bits.
+template <int NT, bool ROUND_B>
 __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickArgs a)
 {
     using L = StageLayout<NT>;
@@ -98,6 +100,8 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     uint32_t n_mc = load_cols(n_k0 >> 2), n_mo = load_offs(n_k0 >> 2);
     uint32_t p_ord = ord;            // panel ordinal of the producer cursor
     uint32_t issued = 0, done = 0;   // bricks issued / consumed by this warp so far
+    int is = 0, ds = 0;              // ring positions of the next brick to issue / to consume
+    uint32_t dpar = 0;               // mbarrier phase parity of stage ds
 
     const float *Bn = a.B + n0;
     const uint32_t ldb32 = (uint32_t)a.ldb;
@@ -111,7 +115,8 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
             mc_nxt = load_cols(G + 1);
             mo_nxt = load_offs(G + 1);
         }
-        const int s = issued % kStages;
+        const int s = is;
+        is = (is + 1 == kStages) ? 0 : is + 1;
         const uint32_t col = __shfl_sync(kFull, mc_cur, (k & 3) * 8 + (lane & 7));
         const uint32_t o0 = __shfl_sync(kFull, mo_cur, k & 3), o1 = __shfl_sync(kFull, mo_cur, (k & 3) + 1);
         const uint32_t rec_bytes = (o1 - o0) * 16u;
@@ -155,12 +160,16 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     for (;;) {
         while (producer_has_work() && issued < done + kStages) issue_one();
         if (done == issued) break;  // nothing in flight and nothing left to issue
-        const int s = done % kStages;
-        if (!ptx::mbar_wait(&full[s], (done / kStages) & 1u)) {
+        const int s = ds;
+        if (!ptx::mbar_wait(&full[s], dpar)) {
             if (lane == 0) atomicExch(a.status, 2u);  // the copies never landed: report, do not hang
             // give the copies still in flight a bounded chance to land before the shared memory is reused
             for (uint32_t j = done + 1; j < issued; ++j) ptx::mbar_wait(&full[j % kStages], (j / kStages) & 1u);
             return;
+        }
+        if (++ds == kStages) {
+            ds = 0;
+            dpar ^= 1u;
         }
         const uint32_t *rec = stage_rec(s);
         const uint4 map = *reinterpret_cast<const uint4 *>(rec);
@@ -178,8 +187,8 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             uint32_t bf[2];
-            bf[0] = ptx::f32_to_tf32_rna(b_lo[nt * 8]);
-            bf[1] = ptx::f32_to_tf32_rna(b_hi[nt * 8]);
+            bf[0] = ROUND_B ? ptx::f32_to_tf32_rna(b_lo[nt * 8]) : __float_as_uint(b_lo[nt * 8]);
+            bf[1] = ROUND_B ? ptx::f32_to_tf32_rna(b_hi[nt * 8]) : __float_as_uint(b_hi[nt * 8]);
             ptx::mma_m16n8k8_tf32(acc[nt], af, bf);
         }
         if (info.x & 1u) {  // last brick of the panel: write its 16 x SLAB tile of C
@@ -197,20 +206,20 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     }
 }
 
-template <int NT> cudaError_t launch_brick_t(const BrickArgs &a, int sm_count, cudaStream_t s)
+template <int NT, bool ROUND_B> cudaError_t launch_brick_t(const BrickArgs &a, int sm_count, cudaStream_t s)
 {
     using L = StageLayout<NT>;
     constexpr int smem = kBrickWarps * L::kWarpBytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(spmm_brick_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(spmm_brick_kernel<NT, ROUND_B>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     const uint32_t slabs = a.N / L::kSlab;
     uint32_t blocks = (a.num_panels + kBrickWarps - 1) / kBrickWarps;
     if (blocks > (uint32_t)sm_count) blocks = (uint32_t)sm_count;  // one resident block per SM, persistent
-    spmm_brick_kernel<NT><<<dim3(blocks, slabs), kBrickWarps * 32, smem, s>>>(a);
+    spmm_brick_kernel<NT, ROUND_B><<<dim3(blocks, slabs), kBrickWarps * 32, smem, s>>>(a);
     return cudaGetLastError();
 }
 
@@ -225,9 +234,14 @@ bool brick_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const
 cudaError_t launch_brick(const BrickArgs &a, int sm_count, cudaStream_t s)
 {
     if (a.num_bricks == 0) return cudaSuccess;
-    if (a.N % 128 == 0) return launch_brick_t<16>(a, sm_count, s);
-    if (a.N % 64 == 0) return launch_brick_t<8>(a, sm_count, s);
-    return launch_brick_t<4>(a, sm_count, s);
+    if (a.round_b) {
+        if (a.N % 128 == 0) return launch_brick_t<16, true>(a, sm_count, s);
+        if (a.N % 64 == 0) return launch_brick_t<8, true>(a, sm_count, s);
+        return launch_brick_t<4, true>(a, sm_count, s);
+    }
+    if (a.N % 128 == 0) return launch_brick_t<16, false>(a, sm_count, s);
+    if (a.N % 64 == 0) return launch_brick_t<8, false>(a, sm_count, s);
+    return launch_brick_t<4, false>(a, sm_count, s);
 }
 
 }  // namespace cutespmm

@@ -268,6 +268,7 @@ static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb
     a.B = B; a.C = C;
     a.ldb = ldb; a.ldc = ldc;
     a.N = N;
+    a.round_b = (p->host.opts.flags & CUTESPMM_FLAG_ROUND_B_NEAREST) ? 1u : 0u;
     a.status = p->d_status;
     return a;
 }

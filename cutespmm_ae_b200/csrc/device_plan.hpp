@@ -27,7 +27,10 @@ cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
 int rows_kernel_count(const RowsArgs &a);
 
 // Arguments of the tensor-core brick kernel.
-constexpr int kBrickWarps = 8;  // warps per block; each is an independent pipeline over its own brick range
+#ifndef BRICK_WARPS
+#define BRICK_WARPS 15
+#endif
+constexpr int kBrickWarps = BRICK_WARPS;  // warps per block; each is an independent pipeline over its own brick range
 struct BrickArgs {
     const uint32_t *cols;         // 8 columns per brick slot (+ readable slack of a few groups behind the end)
     const uint32_t *recs;         // brick records (map, flags, panel, values)
@@ -40,6 +43,7 @@ struct BrickArgs {
     float *C;
     uint64_t ldb, ldc;
     uint32_t N;
+    uint32_t round_b;             // 1: round B to tf32 to nearest, 0: truncate
     uint32_t *status;             // device status word: set to 2 when a bounded wait gives up
 };
 

@@ -48,13 +48,21 @@ typedef enum {
     CUTESPMM_PATH_BRICK = 2  /* tensor-core brick kernel for every panel */
 } cutespmm_path_t;
 
+/* Tensor-core path: A is always rounded to TF32 to nearest (cvt.rna, as the reference does,
+ * kernel.cu:28-29).  By default the elements of B reach the tensor core as fp32 bit patterns whose low
+ * 13 mantissa bits it ignores (truncation; measured relative Frobenius error about 4.5e-4 against the
+ * fp32 CPU product).  With this flag B is rounded to nearest as well (kernel.cu:35; about 2.5e-4) at
+ * the cost of one conversion per element of every gathered row. */
+#define CUTESPMM_FLAG_ROUND_B_NEAREST 1u
+
 typedef struct {
     uint32_t struct_size; /* sizeof(cutespmm_options_t), for forward compatibility */
     uint32_t path;        /* cutespmm_path_t */
-    uint32_t split_nnz;   /* rows longer than this are cut into chunks of this many nonzeros (0 = default 1024) */
+    uint32_t split_nnz;   /* rows longer than this are cut into chunks of this many nonzeros (0 = default 256, at most 384) */
     uint32_t tile_nnz;    /* nonzeros a thread block takes per scheduling tile (0 = default) */
     float brick_density;  /* AUTO: panels whose 16x8 bricks are at least this full go to the brick kernel (0 = default) */
-    uint32_t reserved[3];
+    uint32_t flags;       /* CUTESPMM_FLAG_* */
+    uint32_t reserved[2];
 } cutespmm_options_t;
 
 typedef struct {
