@@ -1,0 +1,73 @@
+"""Host side of the multi-GPU path on CPU ranks (gloo, world size 2 and 3): nnz-balanced contiguous
+row ranges, one plan per rank over its own rows, B delivered by a broadcast, C left row-sharded.
+The device kernels are not involved: each rank checks its plan's packed format against its slice of A
+and multiplies its slice with the CPU oracle, and the union of the shards must equal the
+single-process product bit for bit."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import cutespmm_ae_b200 as cs
+        import oracle
+        from cutespmm_ae_b200 import generators as g
+
+        A = g.rmat(11, 8, seed=77, values="uniform")  # every rank derives the same matrix from the seed
+        N = 24
+        bounds = cs.partition_rows(A.row_ptr, world, align_rows=16)
+        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+        mine = A.row_slice(r0, r1)
+        plan = cs.Plan.from_csr(mine, host_only=True)
+        rp, cols, vals = plan.decode_csr()
+        assert np.array_equal(cols, mine.cols.numpy().astype(np.uint32))
+        assert np.array_equal(vals, mine.vals.numpy())
+        # B lives on rank 0 and reaches the others by one broadcast
+        B = g.dense_operand(A.K, N, 78) if rank == 0 else torch.empty((A.K, N), dtype=torch.float32)
+        dist.broadcast(B, 0)
+        C_mine = torch.from_numpy(oracle.spmm_csr(mine.row_ptr, mine.cols, mine.vals, B.numpy(), mine.M, mine.K))
+        # bookkeeping every rank agrees on
+        counts = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([mine.M, mine.nnz], dtype=torch.int64))
+        assert sum(int(c[0]) for c in counts) == A.M and sum(int(c[1]) for c in counts) == A.nnz
+        nnzs = np.array([int(c[1]) for c in counts], dtype=np.float64)
+        assert nnzs.max() <= 1.3 * nnzs.mean() + 2048  # balanced by nonzeros, up to one hub row
+        torch.save({"r0": r0, "r1": r1, "C": C_mine}, Path(out_dir) / f"shard{rank}.pt")
+        dist.barrier()
+        if rank == 0:
+            full = oracle.spmm_csr(A.row_ptr, A.cols, A.vals, B.numpy(), A.M, A.K)
+            got = np.empty_like(full)
+            covered = 0
+            for r in range(world):
+                sh = torch.load(Path(out_dir) / f"shard{r}.pt")
+                got[sh["r0"] : sh["r1"]] = sh["C"].numpy()
+                covered += sh["r1"] - sh["r0"]
+            assert covered == A.M
+            assert np.array_equal(full.view(np.uint32), got.view(np.uint32))  # row shards: bit-identical union
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_row_sharding_over_gloo_ranks(tmp_path, world):
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
