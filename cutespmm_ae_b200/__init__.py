@@ -22,7 +22,7 @@ import numpy as np
 
 from . import _build
 
-__all__ = ["CuteSpmmError", "Plan", "MtxReader", "partition_rows", "lib", "PATH_AUTO", "PATH_ROWS", "PATH_BRICK"]
+__all__ = ["CuteSpmmError", "Plan", "MtxReader", "partition_rows", "spmm_csr_noalloc", "lib", "PATH_AUTO", "PATH_ROWS", "PATH_BRICK"]
 
 PATH_AUTO, PATH_ROWS, PATH_BRICK = 0, 1, 2
 
@@ -46,8 +46,8 @@ class PlanInfo(C.Structure):
 
 def _load() -> C.CDLL:
     path = _build.LIB
-    if not path.exists():
-        # building needs nvcc only, not a GPU
+    # (re)build when the library is missing or older than its sources; needs nvcc only, not a GPU
+    if not path.exists() or (_build.stale() and Path(_build.NVCC).exists()):
         _build.build()
     lib = C.CDLL(str(path))
     u64p, u32p, f32p, vp = C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.POINTER(C.c_float), C.c_void_p
@@ -66,6 +66,8 @@ def _load() -> C.CDLL:
         "cutespmm_spmm": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, vp]),
         "cutespmm_spmm_host": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, vp, f32p]),
         "cutespmm_spmm_launch_count": (C.c_int, [vp, C.c_uint32]),
+        "cutespmm_spmm_csr_noalloc": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, vp, vp, vp, vp, C.c_uint64, vp,
+                                                C.c_uint64, C.c_uint32, vp]),
         "cutespmm_plan_device_status": (C.c_int, [vp, u32p]),
         "cutespmm_partition_rows": (C.c_int, [C.c_uint64, vp, C.c_uint32, C.c_uint32, C.c_uint32, vp]),
         "cutespmm_mtx_open": (C.c_int, [C.POINTER(vp), C.c_char_p, C.c_int]),
@@ -189,6 +191,25 @@ class Plan:
         _check(lib.cutespmm_spmm_host(self._h, tb.data_ptr(), tb.stride(0) if self.K > 1 else max(N, 1), tc.data_ptr(),
                                       tc.stride(0) if self.M > 1 else max(N, 1), N, st, C.byref(ms)))
         return Cout, ms.value
+
+
+def spmm_csr_noalloc(M: int, K: int, row_ptr, cols, vals, B, Cout, stream=None):
+    """C = A @ B from CSR tensors that already live on the GPU (row_ptr/cols int32, vals/B/C fp32),
+    through the entry point that allocates nothing (cutespmm_spmm_csr_noalloc): for callers that
+    may not allocate device memory when they call.  The caller provides C."""
+    import torch
+
+    for t, dt in ((row_ptr, torch.int32), (cols, torch.int32), (vals, torch.float32), (B, torch.float32), (Cout, torch.float32)):
+        if not t.is_cuda or t.dtype != dt:
+            raise ValueError("all operands must be CUDA tensors: row_ptr/cols int32, vals/B/C float32")
+    if not (row_ptr.is_contiguous() and cols.is_contiguous() and vals.is_contiguous()) or B.stride(1) != 1 or Cout.stride(1) != 1:
+        raise ValueError("CSR arrays must be contiguous; B and C need unit column stride")
+    N = B.shape[1]
+    st = (stream or torch.cuda.current_stream(B.device)).cuda_stream
+    _check(lib.cutespmm_spmm_csr_noalloc(M, K, cols.numel(), row_ptr.data_ptr(), cols.data_ptr(), vals.data_ptr(), B.data_ptr(),
+                                         B.stride(0) if K > 1 else max(N, 1), Cout.data_ptr(),
+                                         Cout.stride(0) if M > 1 else max(N, 1), N, st))
+    return Cout
 
 
 def partition_rows(row_ptr, nparts: int, align_rows: int = 16, row_cost: int = 4) -> np.ndarray:

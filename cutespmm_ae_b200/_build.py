@@ -44,6 +44,12 @@ def _stamp() -> str:
     return h.hexdigest()
 
 
+def stale() -> bool:
+    """True when the built library does not correspond to the current sources and flags."""
+    stamp_file = LIBDIR / (LIB.name + ".stamp")
+    return not (LIB.exists() and stamp_file.exists() and stamp_file.read_text() == _stamp())
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     LIBDIR.mkdir(exist_ok=True)
     stamp_file = LIBDIR / (LIB.name + ".stamp")

@@ -15,6 +15,11 @@ using namespace cutespmm;
 
 namespace {
 thread_local std::string g_last_error;
+}
+namespace cutespmm {
+void set_last_error(const std::string &msg) { g_last_error = msg; }
+}
+namespace {
 
 int fail(int status, const std::string &msg)
 {

@@ -134,6 +134,30 @@ int cutespmm_spmm(const cutespmm_plan_t *plan, const float *B_dev, uint64_t ldb,
 int cutespmm_spmm_host(cutespmm_plan_t *plan, const float *B_host, uint64_t ldb, float *C_host,
                        uint64_t ldc, uint32_t N, void *stream, float *kernel_ms);
 
+/* ---- product without any allocation ------------------------------------------------------------
+ * No counterpart in the reference.  For callers that must not allocate device memory when they
+ * call (all of HBM already belongs to the host framework's pool, a real-time loop that may not make
+ * synchronising runtime calls, a fixed memory budget): they cannot create a plan, so they pass plain
+ * CSR arrays that already live in device memory -- rowPtr (M+1 entries, rowPtr[M] = nnz), cols, vals
+ * -- together with B and C, and get C = A * B computed in fp32 by the row kernel's method (a warp per
+ * row, rows longer than CUTESPMM_NOALLOC_SPLIT_NNZ cut into chunks whose partial sums are added in a
+ * fixed order).  The partial sums live in a CUTESPMM_NOALLOC_SCRATCH_BYTES array that is part of the
+ * library image: every GPU that loads the library holds it until the process exits.  The call makes no
+ * cudaMalloc/cudaFree and calls no allocating routine.
+ * Limits, checked before anything is launched (CUTESPMM_EUNSUPPORTED with a message otherwise):
+ *   N <= CUTESPMM_NOALLOC_MAX_N   and   (2*ceil(nnz/SPLIT_NNZ) + 2) * roundup(N, 4) * 4 <= SCRATCH_BYTES
+ *   (16.7 M nonzeros at N = 128).
+ * All calls on a device share the scratch, which keeps the previous call's contents; nothing in it
+ * needs clearing, but calls that overlap on the same GPU race on it -- keep them on one stream or
+ * order them with events.  The first call on each device looks up the scratch's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture. */
+#define CUTESPMM_NOALLOC_SCRATCH_BYTES (16u << 20)
+#define CUTESPMM_NOALLOC_SPLIT_NNZ 1024u
+#define CUTESPMM_NOALLOC_MAX_N 512u
+int cutespmm_spmm_csr_noalloc(uint32_t M, uint32_t K, uint32_t nnz, const uint32_t *rowPtr_dev,
+                              const uint32_t *cols_dev, const float *vals_dev, const float *B_dev, uint64_t ldb,
+                              float *C_dev, uint64_t ldc, uint32_t N, void *stream);
+
 /* Number of kernels one cutespmm_spmm call launches for this plan and N. */
 int cutespmm_spmm_launch_count(const cutespmm_plan_t *plan, uint32_t N);
 
