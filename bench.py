@@ -160,17 +160,26 @@ def cpu_baseline(A_cpu, N, b_seed, b_dist, budget_s=12.0, max_rows=None):
     from cutespmm_ae_b200 import generators as g
 
     cores = os.cpu_count() or 1
-    M, nnz = A_cpu.M, A_cpu.nnz
-    rows = M
-    est = 2.0 * nnz * N / (0.5e9 * cores)  # pessimistic 0.5 GFLOP/s per core
-    if est > budget_s / 2:
-        rows = max(16, int(M * (budget_s / 2) / est))
-    if max_rows:
-        rows = min(rows, max_rows)
-    sub = A_cpu.row_slice(0, rows) if rows < M else A_cpu
+    M = A_cpu.M
     B = g.dense_operand(A_cpu.K, N, b_seed, b_dist).numpy()
-    rp, cols, vals = sub.row_ptr.numpy().astype(np.uint64), sub.cols.numpy().astype(np.uint32), sub.vals.numpy()
+
+    def slice_rows(target_nnz):
+        rows = int(torch.searchsorted(A_cpu.row_ptr, torch.tensor(int(target_nnz))).item())
+        rows = max(16, min(M, rows))
+        if max_rows:
+            rows = min(rows, max_rows)
+        sub = A_cpu.row_slice(0, rows) if rows < M else A_cpu
+        return sub, (sub.row_ptr.numpy().astype(np.uint64), sub.cols.numpy().astype(np.uint32), sub.vals.numpy())
+
+    # probe on about 2 M nonzeros, then size the sample so that one pass takes about budget/4 seconds
+    sub, (rp, cols, vals) = slice_rows(min(A_cpu.nnz, 2_000_000))
     oracle.spmm_csr(rp, cols, vals, B, sub.M, sub.K)  # warm-up (page faults, thread pool)
+    t0 = time.perf_counter()
+    oracle.spmm_csr(rp, cols, vals, B, sub.M, sub.K)
+    rate = sub.nnz / max(time.perf_counter() - t0, 1e-6)  # nonzeros per second
+    if sub.nnz < A_cpu.nnz:
+        sub, (rp, cols, vals) = slice_rows(min(A_cpu.nnz, rate * budget_s / 4))
+    rows = sub.M
     reps, t_total = 0, 0.0
     while reps < 3 or (t_total < 2.0 and reps < 20):
         t0 = time.perf_counter()

@@ -22,9 +22,9 @@ import numpy as np
 
 from . import _build
 
-__all__ = ["CuteSpmmError", "Plan", "MtxReader", "partition_rows", "spmm_csr_noalloc", "lib", "PATH_AUTO", "PATH_ROWS", "PATH_BRICK"]
+__all__ = ["CuteSpmmError", "Plan", "MtxReader", "partition_rows", "spmm_csr_noalloc", "lib", "PATH_AUTO", "PATH_ROWS", "PATH_BRICK", "PATH_SLAB"]
 
-PATH_AUTO, PATH_ROWS, PATH_BRICK = 0, 1, 2
+PATH_AUTO, PATH_ROWS, PATH_BRICK, PATH_SLAB = 0, 1, 2, 3
 
 
 class CuteSpmmError(RuntimeError):

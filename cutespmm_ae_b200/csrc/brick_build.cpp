@@ -29,7 +29,7 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
         const uint32_t nc = panel_ncols[q];
         const uint64_t my_off = acol_off;
         acol_off += (uint64_t)((nc + kBlockCols - 1) / kBlockCols) * kBlockCols;
-        if (!p.row_path[q] || nc == 0) continue;
+        if (p.row_path[q] != 1 || nc == 0) continue;
         ++p.brick_panels;
         p.panel_first_brick.push_back((uint32_t)p.brick_rec_off.size());  // slot index, a multiple of 4
         const uint32_t *acols = &p.active_cols[my_off];

@@ -122,8 +122,13 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
         const uint32_t rec_bytes = (o1 - o0) * 16u;
         if (lane == 0) ptx::mbar_expect_tx(&full[s], 8u * L::kSlab * 4u + rec_bytes);
         __syncwarp();
+#ifdef BRICK_EXPERIMENT_ONECOPY  // timing experiment only (wrong results): one 8-row copy instead of eight row copies
+        if (lane == 0)
+            ptx::bulk_g2s(stage_b(s), Bn + (uint64_t)min(col, a.M - 8u) * ldb32, 8u * L::kSlab * 4u, &full[s]);
+#else
         if (lane < 8)
             ptx::bulk_g2s(stage_b(s) + lane * L::kStride, Bn + (uint64_t)col * ldb32, L::kSlab * 4u, &full[s]);
+#endif
         else if (lane == 8)
             ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)o0 * 4, rec_bytes, &full[s]);
         ++issued;

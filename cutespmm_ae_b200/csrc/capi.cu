@@ -53,6 +53,7 @@ struct cutespmm_plan {
     void *d_row_ptr = nullptr, *d_pairs = nullptr, *d_tiles = nullptr, *d_chunks = nullptr, *d_long_rows = nullptr;
     void *d_tiles_all = nullptr, *d_chunks_all = nullptr, *d_long_rows_all = nullptr;
     void *d_bcols = nullptr, *d_brecs = nullptr, *d_brec_off = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
+    void *d_scols = nullptr, *d_srecs = nullptr, *d_srec_off = nullptr, *d_sfirst = nullptr, *d_slast = nullptr;
     float *d_scratch = nullptr;
     uint32_t *d_status = nullptr;
     // staging for the host-buffer call
@@ -67,7 +68,8 @@ struct cutespmm_plan {
         cudaGetDevice(&cur);
         if (cur != device) cudaSetDevice(device);
         for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
-                        d_bcols, d_brecs, d_brec_off, d_panel_first, d_panel_last, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
+                        d_bcols, d_brecs, d_brec_off, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
+                        d_slast, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
@@ -174,6 +176,16 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
         UP(h.panel_first_brick, p->d_panel_first)
         UP(h.panel_last_brick, p->d_panel_last)
     }
+    if (h.slab_steps) {
+        std::vector<uint32_t> sc(h.slab_cols), so(h.slab_rec_off);
+        sc.resize(sc.size() + 96, 0u);
+        so.resize(so.size() + 16, so.back());
+        UP(sc, p->d_scols)
+        UP(h.slab_recs, p->d_srecs)
+        UP(so, p->d_srec_off)
+        UP(h.slab_first, p->d_sfirst)
+        UP(h.slab_last, p->d_slast)
+    }
 #undef UP
     const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
     if (scratch) {
@@ -278,6 +290,24 @@ static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb
     return a;
 }
 
+static SlabArgs slab_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
+{
+    SlabArgs a{};
+    a.cols = static_cast<const uint32_t *>(p->d_scols);
+    a.recs = static_cast<const uint32_t *>(p->d_srecs);
+    a.rec_off = static_cast<const uint32_t *>(p->d_srec_off);
+    a.panel_first = static_cast<const uint32_t *>(p->d_sfirst);
+    a.panel_last = static_cast<const uint32_t *>(p->d_slast);
+    a.num_panels = (uint32_t)p->host.slab_panels;
+    a.M = (uint32_t)p->host.M;
+    a.B = B; a.C = C;
+    a.ldb = ldb; a.ldc = ldc;
+    a.N = N;
+    a.round_b = (p->host.opts.flags & CUTESPMM_FLAG_ROUND_B_NEAREST) ? 1u : 0u;
+    a.status = p->d_status;
+    return a;
+}
+
 // Whether a window of N columns at these addresses runs the brick kernel for the brick panels; if
 // not, the row kernel executes every row from its all-rows work list.
 static bool use_brick(const cutespmm_plan *p, const float *B, uint64_t ldb, const float *C, uint64_t ldc, uint32_t N)
@@ -294,8 +324,10 @@ int cutespmm_spmm_launch_count(const cutespmm_plan_t *p, uint32_t N)
         // alignment of the caller's pointers is unknown here: assume the aligned case
         const HostPlan &h = p->host;
         const bool brick = h.num_bricks && nw % 32 == 0;
-        const bool all_rows = !brick && h.num_bricks;
+        const bool slab = h.slab_panels && nw % 128 == 0;
+        const bool all_rows = (!brick && h.num_bricks) || (!slab && h.slab_panels);
         if (brick) total += 1;
+        if (slab) total += 1;
         if (all_rows ? (!h.tiles_all.empty() || !h.chunks_all.empty()) : (!h.tiles.empty() || !h.chunks.empty())) total += 1;
         if (!(all_rows ? h.long_rows_all : h.long_rows).empty()) total += 1;
     }
@@ -318,6 +350,11 @@ int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float 
     for (uint32_t n0 = 0; n0 < N; n0 += kScratchCols) {
         const uint32_t nw = N - n0 < kScratchCols ? N - n0 : kScratchCols;
         cudaError_t e;
+        const bool slab = p->host.slab_panels && slab_supports(nw, ldb, ldc, B + n0, C + n0);
+        if (slab) {
+            SlabArgs sa = slab_args(p, B + n0, ldb, C + n0, ldc, nw);
+            if ((e = launch_slab(sa, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "slab kernel launch");
+        }
         const bool brick = use_brick(p, B + n0, ldb, C + n0, ldc, nw);
         if (brick) {
             BrickArgs ba = brick_args(p, B + n0, ldb, C + n0, ldc, nw);
@@ -325,7 +362,7 @@ int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float 
         }
         // brick panels whose shape the brick kernel does not take (N not a multiple of 32, unaligned
         // operands) are executed by the row kernel from its all-rows work list
-        RowsArgs ra = rows_args(p, !brick && p->host.num_bricks, B + n0, ldb, C + n0, ldc, nw);
+        RowsArgs ra = rows_args(p, (!brick && p->host.num_bricks) || (!slab && p->host.slab_panels), B + n0, ldb, C + n0, ldc, nw);
         if ((e = launch_rows(ra, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "row kernel launch");
         if ((e = launch_fixup(ra, s)) != cudaSuccess) return fail_cuda(e, "fix-up kernel launch");
     }

@@ -50,4 +50,23 @@ struct BrickArgs {
 cudaError_t launch_brick(const BrickArgs &a, int sm_count, cudaStream_t s);
 bool brick_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const void *C);
 
+// Arguments of the tcgen05 slab kernel (128-row panels).
+struct SlabArgs {
+    const uint32_t *cols;         // 8 columns per step slot (+ readable slack)
+    const uint32_t *recs;         // step records
+    const uint32_t *rec_off;      // per step slot (+1) record offsets in 16-byte units (+ slack)
+    const uint32_t *panel_first;  // per slab panel: slot of its first step (a multiple of 4)
+    const uint32_t *panel_last;   // per slab panel: one past the slot of its last step
+    uint32_t num_panels;
+    uint32_t M;
+    const float *B;
+    float *C;
+    uint64_t ldb, ldc;
+    uint32_t N;                   // a multiple of 128
+    uint32_t round_b;
+    uint32_t *status;             // device status word: set to 3 when a bounded wait gives up
+};
+cudaError_t launch_slab(const SlabArgs &a, int sm_count, cudaStream_t s);
+bool slab_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const void *C);
+
 }  // namespace cutespmm

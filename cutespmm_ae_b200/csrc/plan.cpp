@@ -22,6 +22,7 @@
 namespace cutespmm {
 
 void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols);  // brick_build.cpp
+void build_slab_part(HostPlan &p);                                             // slab_build.cpp
 
 static void fill_default_options(cutespmm_options_t &o, const cutespmm_options_t *in)
 {
@@ -145,7 +146,7 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
     const uint64_t nnz = rowPtr[M];
     if (nnz >= (1ull << 32)) { err = "more than 2^32-1 nonzeros in one plan: shard the rows"; return CUTESPMM_EUNSUPPORTED; }
     if (nnz && (!cols || !vals)) { err = "cols/vals is NULL"; return CUTESPMM_EINVAL; }
-    if (opts && opts->path > CUTESPMM_PATH_BRICK) { err = "unknown path"; return CUTESPMM_EINVAL; }
+    if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
     fill_default_options(p.opts, opts);
     p.M = M; p.K = K; p.nnz = nnz;
 
@@ -191,6 +192,7 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
             const uint32_t n = p.row_ptr[r1] - p.row_ptr[r0];
             if (n == 0) continue;  // empty panels: the row kernel writes their zeros
             if (p.opts.path == CUTESPMM_PATH_BRICK) { p.row_path[q] = 1; continue; }
+            if (p.opts.path == CUTESPMM_PATH_SLAB) continue;  // decided per 128-row panel below
             // AUTO: fill of the panel's 16 x (8*ceil(ncols/8)) dense image
             const uint32_t padded = (panel_ncols[q] + kBrickCols - 1) / kBrickCols * kBrickCols;
             const float fill = (float)n / (float)(kPanelRows * padded);
@@ -199,9 +201,21 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
             p.row_path[q] = (fill >= p.opts.brick_density && !long_row) ? 1 : 0;
         }
     }
+    // 128-row panels for the slab (tcgen05) kernel; their 16-row panels are marked 2
+    const uint64_t SP = (p.M + kSlabRows - 1) / kSlabRows;
+    p.slab_path.assign(SP, 0);
+    if (p.opts.path == CUTESPMM_PATH_SLAB) {
+        for (uint64_t q = 0; q < SP; ++q) {
+            const uint64_t r0 = q * kSlabRows, r1 = std::min<uint64_t>(p.M, r0 + kSlabRows);
+            if (p.row_ptr[r1] == p.row_ptr[r0]) continue;
+            p.slab_path[q] = 1;
+            for (uint64_t pq = r0 / kPanelRows; pq < (r1 + kPanelRows - 1) / kPanelRows; ++pq) p.row_path[pq] = 2;
+        }
+    }
     build_tiles(p, false, p.tiles, p.chunks, p.long_rows);
     build_brick_part(p, panel_ncols);
-    if (p.brick_panels) build_tiles(p, true, p.tiles_all, p.chunks_all, p.long_rows_all);
+    build_slab_part(p);
+    if (p.brick_panels || p.slab_panels) build_tiles(p, true, p.tiles_all, p.chunks_all, p.long_rows_all);
     return CUTESPMM_OK;
 }
 
@@ -232,6 +246,23 @@ void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float
             std::memcpy(&v, &rec[kBrickRecHeaderWords + cnt], 4);
             rows[(size_t)panel * kPanelRows + bit / kBrickCols].push_back({p.brick_cols[k * kBrickCols + bit % kBrickCols], v});
             ++cnt;
+        }
+    }
+    for (uint64_t t = 0; t + 1 < p.slab_rec_off.size(); ++t) {
+        if (p.slab_rec_off[t + 1] == p.slab_rec_off[t]) continue;  // empty slot
+        const uint32_t *rec = &p.slab_recs[(size_t)p.slab_rec_off[t] * 4];
+        const uint32_t cnt = rec[0] & 0xffffu, panel = rec[1];
+        const uint32_t *entries = rec + kSlabRecHeaderWords;
+        const uint32_t *vals = entries + (cnt + 3) / 4 * 4;
+        for (uint32_t e = 0; e < cnt; ++e) {
+            const uint32_t row = entries[e] & 0xffu, mask = (entries[e] >> 8) & 0xffu;
+            uint32_t k = entries[e] >> 16;
+            for (uint32_t c = 0; c < 8; ++c) {
+                if (!((mask >> c) & 1u)) continue;
+                float v;
+                std::memcpy(&v, &vals[k++], 4);
+                rows[(size_t)panel * kSlabRows + row].push_back({p.slab_cols[t * 8 + c], v});
+            }
         }
     }
     uint64_t off = 0;

@@ -52,6 +52,10 @@ struct LongRow {
 //     words 6-7   0
 //     words 8..   the stored values (fp32) in map-bit order, padded with zeros to a multiple of 4
 constexpr uint32_t kBrickRecHeaderWords = 8;
+constexpr uint32_t kSlabRows = 128;      // rows of a slab panel (the M of one tcgen05.mma)
+constexpr uint32_t kSlabMaxVals = 256;   // values one step record may hold (bounds the shared-memory stage)
+constexpr uint32_t kSlabRecHeaderWords = 8;
+constexpr uint32_t kSlabRecMaxWords = kSlabRecHeaderWords + kSlabRows + kSlabMaxVals;
 
 struct HostPlan {
     uint64_t M = 0, K = 0, nnz = 0;
@@ -84,6 +88,21 @@ struct HostPlan {
     std::vector<uint32_t> panel_last_brick;   // per brick panel: one past the slot of its last brick
     uint64_t num_bricks = 0;
     uint64_t brick_panels = 0;
+
+    // ---- slab kernel (tcgen05): 128-row panels, one record per step of 8 active columns ----
+    // Step t owns columns slab_cols[8t .. 8t+8) and the record at 16-byte unit slab_rec_off[t] of slab_recs:
+    //     word 0      number of rows with a nonzero in this step | (last step of its panel) << 16
+    //     word 1      128-row panel index
+    //     word 2      number of values stored (<= kSlabMaxVals), word 3: 0
+    //     words 4-7   128-bit map of the rows that have an entry
+    //     words 8..   one entry per such row, in row order: row in panel | 8-bit column mask << 8 | index of its first value << 16
+    //                 (padded to a multiple of 4 entries), then the values in (row, column) order, padded to x4
+    // A step with more than kSlabMaxVals values is stored as several steps over the same 8 columns.
+    // Every panel's steps are followed by empty slots up to a multiple of 4 (group-aligned metadata).
+    std::vector<uint32_t> slab_cols, slab_recs, slab_rec_off;
+    std::vector<uint32_t> slab_first, slab_last;  // per 128-row panel with nonzeros: slot range of its steps
+    std::vector<uint8_t> slab_path;               // per 128-row panel: 1 = executed by the slab kernel
+    uint64_t slab_steps = 0, slab_panels = 0;
 
     uint64_t num_panels() const { return (M + kPanelRows - 1) / kPanelRows; }
 };

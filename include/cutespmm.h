@@ -45,7 +45,9 @@ typedef enum {
 typedef enum {
     CUTESPMM_PATH_AUTO = 0,  /* per-panel choice by brick density */
     CUTESPMM_PATH_ROWS = 1,  /* CUDA-core row-gather kernel for every row */
-    CUTESPMM_PATH_BRICK = 2  /* tensor-core brick kernel for every panel */
+    CUTESPMM_PATH_BRICK = 2, /* tensor-core brick kernel (mma.sync, 16-row panels) for every panel */
+    CUTESPMM_PATH_SLAB = 3   /* tensor-core slab kernel (tcgen05/TMEM, 128-row panels) for every panel; N must be a
+                                multiple of 128, other N run on the row kernel */
 } cutespmm_path_t;
 
 /* Tensor-core path: A is always rounded to TF32 to nearest (cvt.rna, as the reference does,
