@@ -41,7 +41,7 @@ def test_panel_views_match_reference_preprocessing(name):
     assert info["nnz"] == gd["cols"].size
 
 
-@pytest.mark.parametrize("path", [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO])
+@pytest.mark.parametrize("path", [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO, cs.PATH_SLAB])
 @pytest.mark.parametrize("name", GOLDEN_CASES)
 def test_packed_format_round_trip(name, path):
     gd = load_golden(name)
@@ -61,7 +61,7 @@ def test_packed_format_round_trip(name, path):
 
 def test_round_trip_partial_last_panel_and_empty():
     A = g.uniform_random(37, 50, 3, seed=3)  # M not a multiple of 16
-    for path in (cs.PATH_ROWS, cs.PATH_BRICK):
+    for path in (cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_SLAB):
         p = cs.Plan.from_csr(A, host_only=True, path=path)
         rp, cols, vals = p.decode_csr()
         assert np.array_equal(cols, A.cols.numpy().astype(np.uint32))

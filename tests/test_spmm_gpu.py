@@ -9,8 +9,8 @@ from conftest import GOLDEN_CASES, REL_FRO_TOL, REL_FRO_TOL_FP32, load_golden
 
 pytestmark = pytest.mark.gpu
 
-PATHS = [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO]
-PATH_TOL = {cs.PATH_ROWS: REL_FRO_TOL_FP32, cs.PATH_BRICK: REL_FRO_TOL, cs.PATH_AUTO: REL_FRO_TOL}
+PATHS = [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO, cs.PATH_SLAB]
+PATH_TOL = {cs.PATH_ROWS: REL_FRO_TOL_FP32, cs.PATH_BRICK: REL_FRO_TOL, cs.PATH_AUTO: REL_FRO_TOL, cs.PATH_SLAB: REL_FRO_TOL}
 
 
 def run(plan, B_np, **kw):
@@ -22,7 +22,7 @@ def run(plan, B_np, **kw):
     return C.cpu().numpy()
 
 
-@pytest.mark.parametrize("path", PATHS, ids=["rows", "brick", "auto"])
+@pytest.mark.parametrize("path", PATHS, ids=["rows", "brick", "auto", "slab"])
 @pytest.mark.parametrize("name", GOLDEN_CASES)
 def test_golden_fixtures(oracle_mod, name, path):
     gd = load_golden(name)
@@ -32,10 +32,12 @@ def test_golden_fixtures(oracle_mod, name, path):
     assert oracle_mod.rel_fro(gd["C"], C) <= PATH_TOL[path]
 
 
-@pytest.mark.parametrize("path", PATHS, ids=["rows", "brick", "auto"])
+@pytest.mark.parametrize("path", PATHS, ids=["rows", "brick", "auto", "slab"])
 @pytest.mark.parametrize("workload,Ns", [("uniform4096", [32]), ("stencil512", [128]),
                                          ("elasticity40", [32, 64, 128, 256]), ("rmat20", [128])])
 def test_named_workloads_match_oracle(oracle_mod, workload, Ns, path):
+    if path == cs.PATH_SLAB and workload == "rmat20":
+        pytest.skip("forcing a power-law graph through the dense 128-row path is covered at 2^10 nodes (slab_try sizes); here it only costs time")
     w = g.WORKLOADS[workload]
     A = w["make"]()
     p = cs.Plan.from_csr(A, path=path)
@@ -55,6 +57,17 @@ def test_any_number_of_columns(oracle_mod, N):
     assert p.info()["num_long_rows"] > 0
     ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K)
     assert oracle_mod.rel_fro(ref, run(p, B)) <= REL_FRO_TOL_FP32
+
+
+def test_slab_path_on_a_small_power_law_graph_and_round_to_nearest(oracle_mod):
+    A = g.rmat(11, 8, seed=33, values="uniform")  # wide 128-row panels, steps split at 256 values
+    B = g.dense_operand(A.K, 256, 34).numpy()
+    ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K)
+    e_trunc = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_SLAB), B))
+    e_round = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_SLAB, round_b_nearest=True), B))
+    assert e_round < e_trunc <= REL_FRO_TOL
+    e_brick = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_BRICK, round_b_nearest=True), B))
+    assert e_brick <= REL_FRO_TOL
 
 
 def test_strided_and_misaligned_operands(oracle_mod):
@@ -82,7 +95,7 @@ def test_empty_rows_panels_and_matrix(oracle_mod):
     vals = np.linspace(-1, 1, 65).astype(np.float32)
     B = g.dense_operand(K, N, 51).numpy()
     ref = oracle_mod.spmm_csr(rp, cols, vals, B, M, K)
-    for path in (cs.PATH_ROWS, cs.PATH_AUTO, cs.PATH_BRICK):
+    for path in (cs.PATH_ROWS, cs.PATH_AUTO, cs.PATH_BRICK, cs.PATH_SLAB):
         C = run(cs.Plan(M, K, rp, cols, vals, path=path), B)
         assert oracle_mod.rel_fro(ref, C) <= REL_FRO_TOL
         assert not C[:69].any() and not C[100:].any()
@@ -100,7 +113,7 @@ def test_unsorted_and_duplicate_columns(oracle_mod):
     vals = np.array([1.0, 2.0, 4.0, 8.0], np.float32)
     B = g.dense_operand(3, 32, 61).numpy()
     ref = oracle_mod.spmm_csr(rp, cols, vals, B, 3, 3)
-    for path in (cs.PATH_ROWS, cs.PATH_BRICK):
+    for path in (cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_SLAB):
         assert oracle_mod.rel_fro(ref, run(cs.Plan(3, 3, rp, cols, vals, path=path), B)) <= REL_FRO_TOL
 
 
