@@ -54,7 +54,7 @@ def parse_args():
     ap.add_argument("--workload", default="stencil512",
                     choices=["uniform4096", "stencil512", "elasticity40", "rmat20", "rmat22", "rmat24"])
     ap.add_argument("--N", type=int, default=0, help="columns of B (0 = the workload's own)")
-    ap.add_argument("--path", default="auto", choices=["auto", "rows", "brick"])
+    ap.add_argument("--path", default="auto", choices=["auto", "rows", "brick", "slab"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -277,7 +277,7 @@ def run_ours(args):
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     mine = A.row_slice(r0, r1).cpu() if world > 1 else A.cpu()
     del A
-    path = {"auto": cs.PATH_AUTO, "rows": cs.PATH_ROWS, "brick": cs.PATH_BRICK}[args.path]
+    path = {"auto": cs.PATH_AUTO, "rows": cs.PATH_ROWS, "brick": cs.PATH_BRICK, "slab": cs.PATH_SLAB}[args.path]
     t0 = time.perf_counter()
     plan = cs.Plan.from_csr(mine, path=path)
     plan_ms = (time.perf_counter() - t0) * 1e3

@@ -24,12 +24,6 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
-#ifdef SLAB_PROFILE
-#include <cstdio>
-#define PROF(...) __VA_ARGS__
-#else
-#define PROF(...)
-#endif
 
 #include "device_plan.hpp"
 #include "plan.hpp"
@@ -77,7 +71,7 @@ constexpr int kMetaBytes = kMetaSlots * 32 + (kMetaSlots + 4) * 4;  // columns, 
 constexpr int kOffMeta = kStage0 + kStages * kStageBytes;  // two metadata buffers and their two barriers
 constexpr int kOffBars = kOffMeta + 2 * kMetaBytes + 32;  // after the buffers: meta_full[2], meta_free[2]
 // full[kStages], sfree[kStages], built[kTiles], mma_done[kTiles], panel_done, drained, then misc words
-constexpr int kSmemBytes = kOffBars + (2 * kStages + 2 * kTiles + 2) * 8 + 16 + kTiles * 4 + 64 + 8 * kStages;
+constexpr int kSmemBytes = kOffBars + (2 * kStages + 2 * kTiles + 2) * 8 + 16 + kTiles * 4;
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t cols)
@@ -230,7 +224,6 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
         uint32_t issued = 0, seg = 0;
         uint32_t cur_b = 0, cur_e = 0, nxt_b = 0, nxt_e = 0;
         bool have_cur = fetch_next(cur_b, cur_e);
-        PROF(long long prof_a = 0; long long prof_t0 = clock64();)
         while (have_cur && !misc[1]) {
             const bool have_nxt = fetch_next(nxt_b, nxt_e);  // one segment ahead
             const int m = seg & 1;
@@ -246,9 +239,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                 const int s = issued % kStages;
                 const uint32_t col = mcols[(k - cur_b) * 8 + (lane & 7)];
                 const uint32_t o0 = moffs[k - cur_b], o1 = moffs[k - cur_b + 1];
-                PROF(long long t0 = clock64();)
                 ok = ptx::mbar_wait(&sfree[s], ((issued / kStages) & 1u) ^ 1u);  // the landing stage has been consumed
-                PROF(prof_a += clock64() - t0;)
                 if (!ok) break;
                 unsigned char *st = smem + kStage0 + s * kStageBytes;
                 if (lane == 8) {
@@ -268,23 +259,17 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             cur_b = nxt_b; cur_e = nxt_e;
             have_cur = have_nxt;
         }
-        PROF(if (blockIdx.x == 0 && lane == 0) printf("producer %u: steps %u total %lld wait_sfree %lld\n", pw, issued, clock64() - prof_t0, prof_a);)
     } else if (warp == 4 + kProducers) {
         // ================= MMA warp: one thread issues every tcgen05.mma of the block =================
         if (lane == 0) {
             uint32_t step = 0;
-            PROF(long long prof_a = 0, prof_b = 0; long long prof_t0 = clock64();)
             for (uint32_t p = 0; p < my_panels && !misc[1]; ++p) {
-                PROF(long long t1 = clock64();)
                 // the previous panel's accumulator must have been read before it is overwritten
                 if (p > 0 && !ptx::mbar_wait(drained, (p - 1) & 1u)) { abort_now(); break; }
                 bool first = true;
-                PROF(prof_b += clock64() - t1;)
                 for (;;) {
                     const int s = step % kTiles;
-                    PROF(long long t0 = clock64();)
                     const bool okm = ptx::mbar_wait(&built[s], (step / kTiles) & 1u);
-                    PROF(prof_a += clock64() - t0;)
                     if (!okm) { abort_now(); break; }
                     tc_fence_after();
                     unsigned char *st = smem + s * kTileBytes;
@@ -298,22 +283,18 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                     if (last) break;
                 }
             }
-            PROF(if (blockIdx.x == 0) printf("mma: steps %u total %lld wait_built %lld wait_drained %lld\n", step, clock64() - prof_t0, prof_a, prof_b);)
         }
     } else {
         // ================= builder warps 0-3: operand tiles, then the accumulator read-back =================
         // Step i is built by warp i & 3 into tile pair i & 3 (its own), so four steps are under construction
         // at once; every warp still looks at every step's record header to follow the panel structure.
         uint32_t step = 0;
-        PROF(long long prof_a = 0, prof_b = 0, prof_c = 0, prof_d = 0, prof_lat = 0; long long prof_t0 = clock64();)
         for (uint32_t p = 0; p < my_panels && !misc[1]; ++p) {
             uint32_t panel_idx = 0;
             for (;;) {
                 const int ls = step % kStages, t = step & 3;
                 unsigned char *land = smem + kStage0 + ls * kStageBytes;  // gathered rows + record
-                PROF(long long t0 = clock64();)
                 const bool ok1 = ptx::mbar_wait(&full[ls], (step / kStages) & 1u);  // rows of B and record have landed
-                PROF(long long t1 = clock64(); prof_a += t1 - t0;)
                 if (!ok1) {
                     if (lane == 0) abort_now();
                     break;
@@ -326,7 +307,6 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                     unsigned char *st = smem + t * kTileBytes;  // this warp's operand tiles
                     // the MMA that read these tiles four steps ago must be done
                     const bool ok2 = ptx::mbar_wait(&mma_done[t], ((step >> 2) & 1u) ^ 1u);
-                    PROF(prof_b += clock64() - t1;)
                     if (!ok2) {
                         if (lane == 0) abort_now();
                         break;
@@ -393,9 +373,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             }
             if (misc[1]) break;
             // ---- end of panel: accumulator -> C (this warp's 32 rows) ----
-            PROF(long long t2 = clock64();)
             const bool ok3 = ptx::mbar_wait(panel_done, p & 1u);
-            PROF(prof_c += clock64() - t2;)
             if (!ok3) {
                 if (lane == 0) abort_now();
                 break;
@@ -418,9 +396,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(drained);
-            PROF(prof_d += clock64() - t2;)
         }
-        PROF(if (blockIdx.x == 0 && lane == 0) printf("builder warp %d: steps %u total %lld wait_full %lld wait_mma_done %lld wait_panel_done %lld epilogue_total %lld issue_to_seen %lld\n", warp, step, clock64() - prof_t0, prof_a, prof_b, prof_c, prof_d, prof_lat);)
     }
     // ---- wind down: everyone meets, then the allocating warp returns the tensor memory ----
     tc_fence_before();
