@@ -36,7 +36,6 @@ namespace {
 #define BRICK_STAGES 3
 #endif
 constexpr int kStages = BRICK_STAGES;
-constexpr unsigned kFull = 0xffffffffu;
 constexpr int kRecWords = kBrickRecHeaderWords + 128;  // header + a full brick of values
 
 template <int NT> struct StageLayout {
@@ -82,7 +81,10 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     // use: the next group of the current panel, the first group of the warp's next panel, and the
     // slot range of the panel after that.
     auto load_cols = [&](uint32_t g) { return __ldg(a.cols + (size_t)g * 32 + lane); };
-    auto load_offs = [&](uint32_t g) { return lane < 5 ? __ldg(a.rec_off + (size_t)g * 4 + lane) : 0u; };
+    // lanes 0..3: lane j holds the record offsets of slot j of the group and of the slot after it (as one 64-bit value)
+    auto load_offs = [&](uint32_t g) {
+        return lane < 4 ? ((uint64_t)__ldg(a.rec_off + (size_t)g * 4 + lane + 1) << 32) | __ldg(a.rec_off + (size_t)g * 4 + lane) : 0ull;
+    };
     auto load_range = [&](uint32_t o, uint32_t &k0, uint32_t &k1) {
         k0 = k1 = 0;
         if (o < a.num_panels) {
@@ -93,11 +95,13 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     uint32_t pk, pk_end;  // producer cursor: next slot to issue, end of its panel
     load_range(ord, pk, pk_end);
     uint32_t G = pk >> 2;
-    uint32_t mc_cur = load_cols(G), mo_cur = load_offs(G), mc_nxt = load_cols(G + 1), mo_nxt = load_offs(G + 1);
+    uint32_t mc_cur = load_cols(G), mc_nxt = load_cols(G + 1);
+    uint64_t mo_cur = load_offs(G), mo_nxt = load_offs(G + 1);
     uint32_t n_k0, n_k1, nn_k0, nn_k1;  // slot ranges of the next panel and the one after (k0 == k1: none)
     load_range(ord + W, n_k0, n_k1);
     load_range(ord + 2 * W, nn_k0, nn_k1);
-    uint32_t n_mc = load_cols(n_k0 >> 2), n_mo = load_offs(n_k0 >> 2);
+    uint32_t n_mc = load_cols(n_k0 >> 2);
+    uint64_t n_mo = load_offs(n_k0 >> 2);
     uint32_t p_ord = ord;            // panel ordinal of the producer cursor
     uint32_t issued = 0, done = 0;   // bricks issued / consumed by this warp so far
     int is = 0, ds = 0;              // ring positions of the next brick to issue / to consume
@@ -117,20 +121,16 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
         }
         const int s = is;
         is = (is + 1 == kStages) ? 0 : is + 1;
-        const uint32_t col = __shfl_sync(kFull, mc_cur, (k & 3) * 8 + (lane & 7));
-        const uint32_t o0 = __shfl_sync(kFull, mo_cur, k & 3), o1 = __shfl_sync(kFull, mo_cur, (k & 3) + 1);
-        const uint32_t rec_bytes = (o1 - o0) * 16u;
-        if (lane == 0) ptx::mbar_expect_tx(&full[s], 8u * L::kSlab * 4u + rec_bytes);
-        __syncwarp();
-#ifdef BRICK_EXPERIMENT_ONECOPY  // timing experiment only (wrong results): one 8-row copy instead of eight row copies
-        if (lane == 0)
-            ptx::bulk_g2s(stage_b(s), Bn + (uint64_t)min(col, a.M - 8u) * ldb32, 8u * L::kSlab * 4u, &full[s]);
-#else
-        if (lane < 8)
-            ptx::bulk_g2s(stage_b(s) + lane * L::kStride, Bn + (uint64_t)col * ldb32, L::kSlab * 4u, &full[s]);
-#endif
-        else if (lane == 8)
+        // lanes 8j..8j+7 hold the eight columns of slot j of the group, lane j its record offsets: the
+        // lanes that own slot k & 3 start its copies straight from their registers
+        const uint32_t j = k & 3;
+        if ((uint32_t)lane == j) {
+            const uint32_t o0 = (uint32_t)mo_cur, rec_bytes = ((uint32_t)(mo_cur >> 32) - o0) * 16u;
+            ptx::mbar_expect_tx(&full[s], 8u * L::kSlab * 4u + rec_bytes);
             ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)o0 * 4, rec_bytes, &full[s]);
+        }
+        if ((uint32_t)(lane >> 3) == j)
+            ptx::bulk_g2s(stage_b(s) + (lane & 7) * L::kStride, Bn + (uint64_t)mc_cur * ldb32, L::kSlab * 4u, &full[s]);
         ++issued;
         if (++pk == pk_end) {  // panel finished: move the cursor to the warp's next panel
             p_ord += W;
@@ -162,8 +162,9 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
+    for (int s0 = 1; s0 < kStages && producer_has_work(); ++s0) issue_one();  // fill the ring
     for (;;) {
-        while (producer_has_work() && issued < done + kStages) issue_one();
+        if (producer_has_work() && issued < done + kStages) issue_one();
         if (done == issued) break;  // nothing in flight and nothing left to issue
         const int s = ds;
         if (!ptx::mbar_wait(&full[s], dpar)) {

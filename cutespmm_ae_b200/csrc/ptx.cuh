@@ -45,7 +45,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 // Bounded wait for the phase with the given parity.  false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;  // the common case: the phase is already complete
+    for (uint32_t i = 1; i < kSpinLimit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

@@ -53,7 +53,6 @@ constexpr int kProducers = 4;                 // producer warps: warp 4 + j issu
 constexpr int kThreads = kConsumers + kProducers * 32 + 32;  // builders, producers, the MMA warp
 constexpr int kN = 128;                       // columns of B / C per block
 constexpr int kBStride = kN + 4;              // floats between staged rows of B
-constexpr unsigned kFull = 0xffffffffu;
 
 // shared memory: kTiles operand tile pairs, then kStages landing stages, then barriers
 constexpr int kOffA = 0;                              // canonical A tile, 128 x 8 tf32
