@@ -14,6 +14,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "liboracle.so"
 REF_PATH = HERE / "_ref" / "libcutespmm_ref.so"
+REF_LOADERS_PATH = HERE / "_ref" / "libcutespmm_ref_loaders.so"
 
 __all__ = ["build", "spmm_coo", "spmm_csr", "spmm_csr_rows", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
 
@@ -143,6 +144,21 @@ class Ref:
         vals = np.empty(max(nnz, 1), np.float32)
         self.lib.ref_mtx_copy(h, rp.ctypes.data, cols.ctypes.data, vals.ctypes.data)
         return M, K, nnz, rp, cols[:nnz], vals[:nnz]
+
+    def csr_from_mtx(self, path):
+        """The reference's SparseCoo(path) -> CSR_Matrix(coo) (inc/SparseCoo.hpp:91, inc/CSR.hpp:69): nrows, ncols, nnz, rowPtr, cols, values."""
+        L = C.CDLL(str(REF_LOADERS_PATH))
+        L.ref_csr_from_mtx.argtypes = [C.c_char_p]
+        L.ref_csr_from_mtx.restype = C.c_void_p
+        for f in ("ref_csr_nrows", "ref_csr_ncols", "ref_csr_nnz"):
+            getattr(L, f).argtypes = [C.c_void_p]
+            getattr(L, f).restype = C.c_int
+        L.ref_csr_copy.argtypes = [C.c_void_p] * 4
+        h = L.ref_csr_from_mtx(str(path).encode())
+        m, n, nnz = L.ref_csr_nrows(h), L.ref_csr_ncols(h), L.ref_csr_nnz(h)
+        rp, cols, vals = np.empty(m + 1, np.int32), np.empty(max(nnz, 1), np.int32), np.empty(max(nnz, 1), np.float32)
+        L.ref_csr_copy(h, rp.ctypes.data, cols.ctypes.data, vals.ctypes.data)
+        return m, n, nnz, rp, cols[:nnz], vals[:nnz]
 
     def hrpb(self, M, K, row_ptr, cols, vals):
         """blockedRowPtr, activeCols and packed-stream size of the reference's preprocessing.

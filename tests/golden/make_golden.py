@@ -100,6 +100,21 @@ MTX_SYMMETRIC = """%%MatrixMarket matrix coordinate pattern symmetric
 """
 
 
+MTX_VALUES_UNSORTED = """%%MatrixMarket matrix coordinate real general
+6 6 10
+6 1 0.5
+2 3 -1.25
+1 1 4
+2 1 3.5
+4 4 7
+2 2 -2
+6 6 1e-3
+5 2 2.5
+1 6 9
+3 3 -0.125
+"""
+
+
 def main():
     if not oracle.ref_available():
         raise SystemExit("oracle/_ref is not built: run `make -C oracle ref REF=<reference tree>`")
@@ -117,6 +132,14 @@ def main():
         M, K, nnz, rp, cols, vals = R.mtx_read(path)
         np.savez_compressed(OUT / f"mtx_{name}.npz", M=M, K=K, nnz=nnz, row_ptr=rp, cols=cols, vals=vals)
         print(name, M, K, nnz)
+    # SparseCoo -> CSR_Matrix of the reference (inc/SparseCoo.hpp:91-157, inc/CSR.hpp:162-187)
+    for name, text in (("general_5x7", None), ("symmetric_20", None), ("values_unsorted_6x6", MTX_VALUES_UNSORTED)):
+        path = OUT / f"{name}.mtx"
+        if text is not None:
+            path.write_text(text)
+        m, n, nnz, rp, cols, vals = R.csr_from_mtx(path)
+        np.savez_compressed(OUT / f"loader_{name}.npz", nrows=m, ncols=n, nnz=nnz, row_ptr=rp, cols=cols, vals=vals)
+        print("loader", name, m, n, nnz)
 
 
 if __name__ == "__main__":
