@@ -300,10 +300,10 @@ static SlabArgs slab_args(const cutespmm_plan *p, const float *B, uint64_t ldb, 
     a.panel_last = static_cast<const uint32_t *>(p->d_slast);
     a.num_panels = (uint32_t)p->host.slab_panels;
     a.M = (uint32_t)p->host.M;
+    a.K = (uint32_t)p->host.K;
     a.B = B; a.C = C;
     a.ldb = ldb; a.ldc = ldc;
     a.N = N;
-    a.round_b = (p->host.opts.flags & CUTESPMM_FLAG_ROUND_B_NEAREST) ? 1u : 0u;
     a.status = p->d_status;
     return a;
 }

@@ -58,12 +58,11 @@ struct SlabArgs {
     const uint32_t *panel_first;  // per slab panel: slot of its first step (a multiple of 4)
     const uint32_t *panel_last;   // per slab panel: one past the slot of its last step
     uint32_t num_panels;
-    uint32_t M;
+    uint32_t M, K;
     const float *B;
     float *C;
     uint64_t ldb, ldc;
     uint32_t N;                   // a multiple of 128
-    uint32_t round_b;
     uint32_t *status;             // device status word: set to 3 when a bounded wait gives up
 };
 cudaError_t launch_slab(const SlabArgs &a, int sm_count, cudaStream_t s);

@@ -148,6 +148,10 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
     if (nnz && (!cols || !vals)) { err = "cols/vals is NULL"; return CUTESPMM_EINVAL; }
     if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
     fill_default_options(p.opts, opts);
+    if (p.opts.path == CUTESPMM_PATH_SLAB && (p.opts.flags & CUTESPMM_FLAG_ROUND_B_NEAREST)) {
+        err = "the slab path cannot round B to nearest: the copy engine places B in the tensor core's operand layout and no thread touches it";
+        return CUTESPMM_EUNSUPPORTED;
+    }
     p.M = M; p.K = K; p.nnz = nnz;
 
     // validation + 32-bit row pointers

@@ -3,24 +3,25 @@
 // tensor memory (TMEM).
 //
 // Role in the reference: SpMM<NUM_WARPS,ILP_LEVEL> (kernel.cu:119-288) -- panels, active columns,
-// bitmask-compressed A -- but with the data flow of the 5th-generation tensor core:
-//   * four producer warps (taking turns, one step each) gather a step's eight rows of B (512 B each)
-//     and its record with TMA bulk copies into a shared-memory landing stage, kStages deep,
-//     mbarrier-tracked; the column lists and record offsets they need are themselves fetched by TMA
-//     one segment ahead (issuing one bulk copy costs a thread on the order of a hundred cycles, so
-//     a single issuing warp was the bottleneck);
-//   * four builder warps transpose the eight rows into the MMA's canonical K-major layout (column
-//     n's eight values as two 16-byte chunks at (n/8)*256 + (n%8)*16 + {0,128}; optionally rounding
-//     to TF32 to nearest on the way); one of them, taking turns, expands the step's rows of A into
-//     the same layout: it zeroes the rows written the previous time the stage was used and writes
-//     the rows the record lists;
-//   * one thread issues the MMA from shared-memory descriptors; B never passes through registers
-//     as an MMA fragment, there is no per-lane fragment arithmetic, and the 128 x 128 fp32
-//     accumulator lives in TMEM, not in registers;
-//   * tcgen05.commit signals an mbarrier when the MMAs that read a stage are done, which frees the
-//     stage; at the end of a panel the accumulator is read back with tcgen05.ld and stored to C.
-// Every wait is bounded; a wait that runs out sets the plan's status word (3) and the block winds
-// down: all threads still meet at the step barrier, leave the loops together, and TMEM is freed.
+// bitmask-compressed A -- with the data flow of the 5th-generation tensor core:
+//   * B never passes through a thread.  The eight gathered rows of a step are placed by the copy
+//     engine directly in the layout the MMA reads: eight cp.async.bulk.tensor...tile::gather4 loads
+//     (four rows x 32 columns each, tensor map with the 128-byte swizzle on 32-byte atoms) fill the
+//     step's 8 x 128 operand tile as an MN-major tf32 operand (the only shared-memory layout the
+//     tensor core takes for MN-major tf32 is that swizzle; with any other it returns zeros);
+//   * four producer warps take turns issuing a step's loads (issuing one TMA operation costs a thread
+//     on the order of a hundred cycles); the column lists and record offsets they need are
+//     themselves fetched by TMA one segment ahead;
+//   * four builder warps expand the rows of A: the warp that owns a step zeroes the rows it wrote
+//     the last time the stage was used and writes the rows the step's record lists (row, 8-bit
+//     column mask, packed values) into the canonical K-major operand layout, rounding to TF32;
+//   * one thread issues every MMA from shared-memory descriptors; tcgen05.commit signals an mbarrier
+//     when the MMAs that read a stage are done, which frees the stage for the producers; at the end
+//     of a panel the builder warps read the accumulator back with tcgen05.ld and store it to C.
+// All roles are coupled by mbarriers only.  Every wait is bounded; a wait that runs out sets the
+// plan's status word (3) and the block's abort flag, every role leaves its loop, the block meets at
+// one final barrier and the warp that allocated the tensor memory frees it.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -34,43 +35,38 @@ namespace cutespmm {
 namespace {
 
 #ifndef SLAB_STAGES
-#define SLAB_STAGES 4   // gathered rows of B + record in flight per block (hides the L2 / HBM gather latency)
+#define SLAB_STAGES 4   // steps in flight per block; a multiple of 4 (see static_assert)
 #endif
-#ifndef SLAB_TILES
-#define SLAB_TILES 4    // operand tile pairs per block: one per builder warp
-#endif
-#ifndef SLAB_BLOCKS_PER_SM
-#define SLAB_BLOCKS_PER_SM 3u
-#endif
-constexpr int kStages = SLAB_STAGES;
-constexpr int kTiles = SLAB_TILES;
-static_assert(kTiles == 4, "tile pair i & 3 belongs to builder warp i & 3");
-// A landing stage must always be refilled by the same producer warp: a warp is in order on its own
-// stages, so the one-bit phase parity of the stage's barriers can never be two phases stale.
-static_assert(kStages % 4 == 0, "landing stage i % kStages must belong to producer warp i % 4");
-constexpr int kConsumers = 128;               // 4 builder warps, one TMEM lane quadrant each
-constexpr int kProducers = 4;                 // producer warps: warp 4 + j issues the copies of steps i with i % 4 == j
-constexpr int kThreads = kConsumers + kProducers * 32 + 32;  // builders, producers, the MMA warp
-constexpr int kN = 128;                       // columns of B / C per block
-constexpr int kBStride = kN + 4;              // floats between staged rows of B
-
-// shared memory: kTiles operand tile pairs, then kStages landing stages, then barriers
-constexpr int kOffA = 0;                              // canonical A tile, 128 x 8 tf32
-constexpr int kOffB = 4096;                           // canonical B tile, 128 (N) x 8 (K) tf32
-constexpr int kOffDirty = 8192;                       // rows of the A tile that hold values: count (16 B), then row numbers
-constexpr int kTileBytes = 8192 + 256;
-constexpr int kOffRec = 8 * kBStride * 4;             // inside a landing stage: gathered rows first, then the step's record
-constexpr int kStageBytes = (kOffRec + (int)kSlabRecMaxWords * 4 + 127) / 128 * 128;
-constexpr int kStage0 = kTiles * kTileBytes;
 #ifndef SLAB_META_SLOTS
 #define SLAB_META_SLOTS 64
 #endif
-constexpr int kMetaSlots = SLAB_META_SLOTS;                          // step slots whose metadata one buffer holds
+#ifndef SLAB_BLOCKS_PER_SM
+#define SLAB_BLOCKS_PER_SM 4u
+#endif
+constexpr int kStages = SLAB_STAGES;
+// A stage is always refilled by the same producer warp and built by the same builder warp: a warp is
+// in order on its own stages, so the one-bit phase parity of the stage's barriers can never be two
+// phases stale.
+static_assert(kStages % 4 == 0, "stage i % kStages must belong to producer / builder warp i % 4");
+constexpr int kBuilders = 4;                  // builder warps 0-3, one TMEM lane quadrant each
+constexpr int kProducers = 4;                 // producer warps 4-7
+constexpr int kThreads = (kBuilders + kProducers + 1) * 32;  // + the MMA warp
+constexpr int kN = 128;                       // columns of B / C per block
+
+// shared memory: kStages stages (1024-byte aligned: the swizzle pattern is a function of the address),
+// two metadata buffers, barriers
+constexpr int kOffB = 0;                      // B operand tile: 4 column blocks x 2 K blocks x (4 rows x 128 B), swizzled
+constexpr int kOffA = 4096;                   // A operand tile: K-major, no swizzle
+constexpr int kOffRec = 8192;                 // the step's record
+constexpr int kOffDirty = kOffRec + (int)kSlabRecMaxWords * 4;  // rows of the A tile that hold values: count (16 B), row numbers
+constexpr int kStageBytes = (kOffDirty + 16 + 128 + 1023) / 1024 * 1024;
+constexpr int kMetaSlots = SLAB_META_SLOTS;   // step slots whose metadata one buffer holds
 constexpr int kMetaBytes = kMetaSlots * 32 + (kMetaSlots + 4) * 4;  // columns, then record offsets (+ next, padded)
-constexpr int kOffMeta = kStage0 + kStages * kStageBytes;  // two metadata buffers and their two barriers
-constexpr int kOffBars = kOffMeta + 2 * kMetaBytes + 32;  // after the buffers: meta_full[2], meta_free[2]
-// full[kStages], sfree[kStages], built[kTiles], mma_done[kTiles], panel_done, drained, then misc words
-constexpr int kSmemBytes = kOffBars + (2 * kStages + 2 * kTiles + 2) * 8 + 16 + kTiles * 4;
+constexpr int kOffMeta = kStages * kStageBytes;
+constexpr int kOffBars = kOffMeta + 2 * kMetaBytes;
+constexpr int kNumBars = 4 * kStages + 2 + 4;  // full, seen, built, mma_done per stage; panel_done, drained; meta_full[2], meta_free[2]
+constexpr int kOffMisc = kOffBars + kNumBars * 8;
+constexpr int kSmemBytes = kOffMisc + 16 + kStages * 4;
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t cols)
@@ -110,60 +106,71 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor, no swizzle (layout type 0), descriptor version 1 (bits 46-47).
-// lbo / sbo in bytes for a K-major operand: sbo = distance between 8-row groups, lbo = between the
-// two 16-byte K chunks of a row.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo)
+// Four rows of a 2-D tensor (row coordinates y0..y3, 32 columns from x) -> four consecutive 128-byte
+// rows of shared memory, swizzled as the tensor map says; completion counted on `bar`.
+__device__ __forceinline__ void tma_gather4(void *smem_dst, const CUtensorMap *tmap, int x, int y0, int y1, int y2, int y3, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(ptx::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3),
+        "r"(ptx::smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor (descriptor version 1 in bits 46-47).  lbo / sbo in bytes.
+//   A, K-major, no swizzle (layout type 0): sbo = distance between 8-row groups, lbo = between the two
+//   16-byte K chunks of a row.
+//   B, MN-major, 128-byte swizzle on 32-byte atoms (layout type 1): lbo = distance between blocks of 32
+//   columns, sbo = between blocks of 4 K rows.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t layout_type)
 {
     return (uint64_t)((saddr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
-           ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
+           ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) | ((uint64_t)layout_type << 61);
 }
-// Instruction descriptor: D fp32 (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2), A and B K-major
-// (bits 15, 16 = 0), N/8 in bits 17-22, M/16 in bits 24-28.  (With B MN-major and no swizzle the
-// tensor core returned zeros for tf32 on this part, so B is transposed on the way into its tile.)
-constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((kN / 8u) << 17) | ((kSlabRows / 16u) << 24);
+// Instruction descriptor: D fp32 (bits 4-5 = 1), A and B tf32 (bits 7-9, 10-12 = 2), A K-major (bit 15 = 0),
+// B MN-major (bit 16 = 1), N/8 in bits 17-22, M/16 in bits 24-28.
+constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((kN / 8u) << 17) | ((kSlabRows / 16u) << 24);
 
 }  // namespace
 
 namespace {
 
-template <bool ROUND_B>
-__global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel(SlabArgs a)
+__global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel(const __grid_constant__ CUtensorMap tmap_b, SlabArgs a)
 {
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kOffBars);   // TMA -> builders (1 arrival + bytes)
-    uint64_t *sfree = full + kStages;        // builders -> producer: the landing stage has been consumed (4 arrivals)
-    uint64_t *built = sfree + kStages;       // owning builder warp -> MMA warp: the tile pair is ready
-    uint64_t *mma_done = built + kTiles;     // tcgen05.commit -> builders: the tile pair may be rewritten
-    uint64_t *panel_done = mma_done + kTiles;  // tcgen05.commit -> builders: the accumulator is complete
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kOffBars);  // TMA -> builders and MMA warp (1 arrival + bytes)
+    uint64_t *seen = full + kStages;         // builders -> producer: all four have read the record header (4 arrivals)
+    uint64_t *built = seen + kStages;        // owning builder -> MMA warp: the A tile is ready
+    uint64_t *mma_done = built + kStages;    // tcgen05.commit -> producer and builder: the stage's tiles may be rewritten
+    uint64_t *panel_done = mma_done + kStages;  // tcgen05.commit -> builders: the accumulator is complete
     uint64_t *drained = panel_done + 1;      // builders -> MMA warp: the accumulator has been read (4 arrivals)
-    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(drained + 1);  // [0] TMEM base, [1] abort flag, [2+s] step flags
+    uint64_t *meta_full = drained + 1, *meta_free = meta_full + 2;
+    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(smem + kOffMisc);  // [0] TMEM base, [1] abort flag, [4+s] "last step" flags
     const uint32_t n0 = blockIdx.y * kN;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&sfree[s], 4);
-        }
-        for (int t = 0; t < kTiles; ++t) {
-            ptx::mbar_init(&built[t], 1);
-            ptx::mbar_init(&mma_done[t], 1);
+            ptx::mbar_init(&seen[s], kBuilders);
+            ptx::mbar_init(&built[s], 1);
+            ptx::mbar_init(&mma_done[s], 1);
         }
         ptx::mbar_init(panel_done, 1);
-        ptx::mbar_init(drained, 4);
+        ptx::mbar_init(drained, kBuilders);
         for (int m = 0; m < 2; ++m) {
-            ptx::mbar_init(reinterpret_cast<uint64_t *>(smem + kOffMeta + 2 * kMetaBytes) + m, 1);              // meta_full
-            ptx::mbar_init(reinterpret_cast<uint64_t *>(smem + kOffMeta + 2 * kMetaBytes) + 2 + m, kProducers);  // meta_free
+            ptx::mbar_init(&meta_full[m], 1);
+            ptx::mbar_init(&meta_free[m], kProducers);
         }
         misc[1] = 0;
         ptx::fence_mbar_init();
     }
-    // the A tiles start as zeros and hold no rows; afterwards the builder undoes exactly what was written
-    for (int i = tid; i < kTiles * 256; i += kThreads)
-        *reinterpret_cast<uint4 *>(smem + (i / 256) * kTileBytes + kOffA + (i % 256) * 16) = make_uint4(0, 0, 0, 0);
-    if (tid < kTiles) *reinterpret_cast<volatile uint32_t *>(smem + tid * kTileBytes + kOffDirty) = 0;
+    // the A tiles start as zeros and hold no rows; afterwards the owning builder undoes exactly what it wrote
+    for (int i = tid; i < kStages * 256; i += kThreads)
+        *reinterpret_cast<uint4 *>(smem + (i / 256) * kStageBytes + kOffA + (i % 256) * 16) = make_uint4(0, 0, 0, 0);
+    if (tid < kStages) *reinterpret_cast<volatile uint32_t *>(smem + tid * kStageBytes + kOffDirty) = 0;
     if (warp == 0) tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(&misc[0])), kN);  // 128 fp32 columns x 128 lanes
+    ptx::fence_async_smem();  // the zeroed tiles are read through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -174,14 +181,9 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
         misc[1] = 1;
     };
 
-    if (warp >= 4 && warp < 4 + kProducers) {
+    if (warp >= kBuilders && warp < kBuilders + kProducers) {
         // ================= producer warps: TMA gathers, kStages ahead =================
-        const uint32_t pw = warp - 4;  // this warp issues the steps i with i % kProducers == pw
-        // The column lists and record offsets of this block's panels are themselves fetched by TMA into a
-        // double-buffered shared-memory area, one segment (<= kMetaSlots step slots) ahead of their use, so
-        // the warp never waits on a global load while it issues: per step lanes 0-7 start the copies of the
-        // eight gathered rows and lane 8 announces the byte count and starts the copy of the record.
-        uint64_t *meta_full = reinterpret_cast<uint64_t *>(smem + kOffMeta + 2 * kMetaBytes), *meta_free = meta_full + 2;
+        const uint32_t pw = warp - kBuilders;  // this warp issues the steps i with i % 4 == pw
         auto load_range = [&](uint32_t o, uint32_t &k0, uint32_t &k1) {
             k0 = k1 = 0;
             if (o < a.num_panels) {
@@ -189,15 +191,13 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                 k1 = __ldg(a.panel_last + o);
             }
         };
-        const float *Bn = a.B + n0;
-        const uint32_t ldb32 = (uint32_t)a.ldb;
         // segment generator: walks this block's panels, cutting each into segments of <= kMetaSlots slots
         uint32_t g_ord = blockIdx.x, g_k, g_k1, r1_k0, r1_k1, r2_k0, r2_k1;
         load_range(g_ord, g_k, g_k1);
         load_range(g_ord + gridDim.x, r1_k0, r1_k1);
         load_range(g_ord + 2 * gridDim.x, r2_k0, r2_k1);
         uint32_t fetched = 0;  // segments whose metadata fetch has been started
-        auto fetch_next = [&](uint32_t &seg_begin, uint32_t &seg_end) {  // returns false when there is no further segment
+        auto fetch_next = [&](uint32_t &seg_begin, uint32_t &seg_end) {  // false when there is no further segment
             if (g_k >= g_k1) return false;
             seg_begin = g_k;
             seg_end = min(g_k1, g_k + kMetaSlots);
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             }
             ++fetched;
             g_k = seg_end;
-            if (g_k >= g_k1) {  // panel exhausted: move to this block's next panel (its range was loaded two panels ago)
+            if (g_k >= g_k1) {  // panel exhausted: this block's next panel (its range was loaded two panels ago)
                 g_ord += gridDim.x;
                 g_k = r1_k0; g_k1 = r1_k1;
                 r1_k0 = r2_k0; r1_k1 = r2_k1;
@@ -236,29 +236,33 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             for (uint32_t k = cur_b; k < cur_e; ++k, ++issued) {
                 if (issued % kProducers != pw) continue;
                 const int s = issued % kStages;
-                const uint32_t col = mcols[(k - cur_b) * 8 + (lane & 7)];
+                const uint32_t par = ((issued / kStages) & 1u) ^ 1u;
+                // lane l < 8 loads K rows 4*(l&1) .. +3 of column block l>>1; its four row coordinates:
+                const uint4 rows4 = *reinterpret_cast<const uint4 *>(mcols + (k - cur_b) * 8 + (lane & 1) * 4);
                 const uint32_t o0 = moffs[k - cur_b], o1 = moffs[k - cur_b + 1];
-                ok = ptx::mbar_wait(&sfree[s], ((issued / kStages) & 1u) ^ 1u);  // the landing stage has been consumed
+                // the stage is free once the MMA that read it is done and every builder has seen its record header
+                ok = ptx::mbar_wait(&mma_done[s], par) && ptx::mbar_wait(&seen[s], par);
                 if (!ok) break;
-                unsigned char *st = smem + kStage0 + s * kStageBytes;
+                unsigned char *st = smem + s * kStageBytes;
                 if (lane == 8) {
                     ptx::mbar_expect_tx(&full[s], 8u * kN * 4u + (o1 - o0) * 16u);
                     ptx::bulk_g2s(st + kOffRec, a.recs + (size_t)o0 * 4, (o1 - o0) * 16u, &full[s]);
                 } else if (lane < 8) {
-                    ptx::bulk_g2s(st + lane * kBStride * 4, Bn + (uint64_t)col * ldb32, kN * 4u, &full[s]);
+                    tma_gather4(st + kOffB + (lane >> 1) * 1024 + (lane & 1) * 512, &tmap_b, (int)(n0 + 32 * (lane >> 1)), (int)rows4.x,
+                                (int)rows4.y, (int)rows4.z, (int)rows4.w, &full[s]);
                 }
             }
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&meta_free[m]);  // this warp is done with the segment's metadata
             if (!ok) {
                 if (lane == 0) abort_now();
                 break;
             }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&meta_free[m]);  // this warp is done with the segment's metadata
             ++seg;
             cur_b = nxt_b; cur_e = nxt_e;
             have_cur = have_nxt;
         }
-    } else if (warp == 4 + kProducers) {
+    } else if (warp == kBuilders + kProducers) {
         // ================= MMA warp: one thread issues every tcgen05.mma of the block =================
         if (lane == 0) {
             uint32_t step = 0;
@@ -267,13 +271,13 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                 if (p > 0 && !ptx::mbar_wait(drained, (p - 1) & 1u)) { abort_now(); break; }
                 bool first = true;
                 for (;;) {
-                    const int s = step % kTiles;
-                    const bool okm = ptx::mbar_wait(&built[s], (step / kTiles) & 1u);
-                    if (!okm) { abort_now(); break; }
+                    const int s = step % kStages;
+                    const uint32_t par = (step / kStages) & 1u;
+                    if (!ptx::mbar_wait(&built[s], par) || !ptx::mbar_wait(&full[s], par)) { abort_now(); break; }
                     tc_fence_after();
-                    unsigned char *st = smem + s * kTileBytes;
-                    const uint32_t last = misc[2 + s];
-                    tc_mma_tf32(tmem, smem_desc(ptx::smem_u32(st + kOffA), 128u, 256u), smem_desc(ptx::smem_u32(st + kOffB), 128u, 256u),
+                    unsigned char *st = smem + s * kStageBytes;
+                    const uint32_t last = misc[4 + s];
+                    tc_mma_tf32(tmem, smem_desc(ptx::smem_u32(st + kOffA), 128u, 256u, 0u), smem_desc(ptx::smem_u32(st + kOffB), 1024u, 512u, 1u),
                                 kIdesc, first ? 0u : 1u);
                     tc_commit(&mma_done[s]);
                     if (last) tc_commit(panel_done);
@@ -284,48 +288,27 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             }
         }
     } else {
-        // ================= builder warps 0-3: operand tiles, then the accumulator read-back =================
-        // Step i is built by warp i & 3 into tile pair i & 3 (its own), so four steps are under construction
-        // at once; every warp still looks at every step's record header to follow the panel structure.
+        // ================= builder warps 0-3: rows of A, then the accumulator read-back =================
+        // Step i is built by warp i & 3; every warp still reads every step's record header to follow the
+        // panel structure.
         uint32_t step = 0;
         for (uint32_t p = 0; p < my_panels && !misc[1]; ++p) {
             uint32_t panel_idx = 0;
             for (;;) {
-                const int ls = step % kStages, t = step & 3;
-                unsigned char *land = smem + kStage0 + ls * kStageBytes;  // gathered rows + record
-                const bool ok1 = ptx::mbar_wait(&full[ls], (step / kStages) & 1u);  // rows of B and record have landed
-                if (!ok1) {
+                const int s = step % kStages;
+                const uint32_t par = (step / kStages) & 1u;
+                unsigned char *st = smem + s * kStageBytes;
+                if (!ptx::mbar_wait(&full[s], par)) {  // the step's record (and its rows of B) have landed
                     if (lane == 0) abort_now();
                     break;
                 }
-                const uint32_t *rec = reinterpret_cast<const uint32_t *>(land + kOffRec);
+                const uint32_t *rec = reinterpret_cast<const uint32_t *>(st + kOffRec);
                 const uint32_t head = rec[0];
                 const uint32_t last = (head >> 16) & 1u, cnt = head & 0xffffu;
                 panel_idx = rec[1];
-                if (warp == t) {
-                    unsigned char *st = smem + t * kTileBytes;  // this warp's operand tiles
-                    // the MMA that read these tiles four steps ago must be done
-                    const bool ok2 = ptx::mbar_wait(&mma_done[t], ((step >> 2) & 1u) ^ 1u);
-                    if (!ok2) {
-                        if (lane == 0) abort_now();
-                        break;
-                    }
-                    // ---- B: column n of the gathered rows -> one 32-byte row of the K-major operand ----
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int n = lane + 32 * q;
-                        const float *col = reinterpret_cast<const float *>(land) + n;
-                        float x[8];
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            x[k] = col[k * kBStride];
-                            if (ROUND_B) x[k] = __uint_as_float(ptx::f32_to_tf32_rna(x[k]));
-                        }
-                        float4 *d = reinterpret_cast<float4 *>(st + kOffB + (n >> 3) * 256 + (n & 7) * 16);
-                        d[0] = make_float4(x[0], x[1], x[2], x[3]);
-                        d[8] = make_float4(x[4], x[5], x[6], x[7]);  // + 128 bytes
-                    }
-                    // ---- A: clear the rows written the last time, write this step's ----
+                if (warp == (int)(step & 3u)) {
+                    // clear the rows written the last time this stage was used (that MMA is done: the producer
+                    // waited for it before refilling the stage), then write this step's rows
                     volatile uint32_t *dirty_cnt = reinterpret_cast<volatile uint32_t *>(st + kOffDirty);
                     unsigned char *dirty_rows = st + kOffDirty + 16;
                     const uint32_t old = *dirty_cnt;
@@ -333,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                         const uint32_t r = dirty_rows[e];
                         float4 *d = reinterpret_cast<float4 *>(st + kOffA + (r >> 3) * 256 + (r & 7) * 16);
                         d[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        d[8] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        d[8] = make_float4(0.f, 0.f, 0.f, 0.f);  // + 128 bytes: the row's second K chunk
                     }
                     __syncwarp();
                     const uint32_t *entries = rec + kSlabRecHeaderWords;
@@ -355,25 +338,24 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                     }
                     if (lane == 0) {
                         *dirty_cnt = cnt;
-                        misc[2 + t] = last;
+                        misc[4 + s] = last;
                     }
-                    ptx::fence_async_smem();  // the tensor core reads the tiles through the async proxy
+                    ptx::fence_async_smem();  // the tensor core reads the tile through the async proxy
                     __syncwarp();
                     if (lane == 0) {
-                        ptx::mbar_arrive(&built[t]);
-                        ptx::mbar_arrive(&sfree[ls]);
+                        ptx::mbar_arrive(&built[s]);
+                        ptx::mbar_arrive(&seen[s]);
                     }
                 } else {
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&sfree[ls]);  // this warp only needed the header
+                    if (lane == 0) ptx::mbar_arrive(&seen[s]);  // this warp only needed the header
                 }
                 ++step;
                 if (last) break;
             }
             if (misc[1]) break;
             // ---- end of panel: accumulator -> C (this warp's 32 rows) ----
-            const bool ok3 = ptx::mbar_wait(panel_done, p & 1u);
-            if (!ok3) {
+            if (!ptx::mbar_wait(panel_done, p & 1u)) {
                 if (lane == 0) abort_now();
                 break;
             }
@@ -406,6 +388,22 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
     }
 }
 
+// cuTensorMapEncodeTiled, looked up through the runtime (the library does not link libcuda)
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
 }  // namespace
 
 bool slab_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const void *C)
@@ -419,17 +417,23 @@ cudaError_t launch_slab(const SlabArgs &a, int sm_count, cudaStream_t s)
     if (a.num_panels == 0) return cudaSuccess;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(spmm_slab_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(spmm_slab_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(spmm_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    // three blocks per SM: 3 x 62 KB of shared memory, 3 x 128 of the 512 columns of tensor memory
-    uint32_t blocks = (uint32_t)sm_count * SLAB_BLOCKS_PER_SM;
+    // B as a 2-D tensor (columns innermost); one gather4 brings 4 rows x 32 columns = a 4 x 128-byte atom
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {a.N, a.K};
+    const cuuint64_t strides[1] = {a.ldb * sizeof(float)};
+    const cuuint32_t box[2] = {32, 1}, estr[2] = {1, 1};
+    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(a.B), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    uint32_t blocks = (uint32_t)sm_count * SLAB_BLOCKS_PER_SM;  // shared memory and tensor memory (128 of 512 columns each) allow this many per SM
     if (blocks > a.num_panels) blocks = a.num_panels;
-    const dim3 grid(blocks, a.N / kN);
-    if (a.round_b) spmm_slab_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(a);
-    else spmm_slab_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(a);
+    spmm_slab_kernel<<<dim3(blocks, a.N / kN), kThreads, kSmemBytes, s>>>(tmap, a);
     return cudaGetLastError();
 }
 

@@ -54,7 +54,8 @@ typedef enum {
  * kernel.cu:28-29).  By default the elements of B reach the tensor core as fp32 bit patterns whose low
  * 13 mantissa bits it ignores (truncation; measured relative Frobenius error about 4.5e-4 against the
  * fp32 CPU product).  With this flag B is rounded to nearest as well (kernel.cu:35; about 2.5e-4) at
- * the cost of one conversion per element of every gathered row. */
+ * the cost of one conversion per element of every gathered row.  Not available on CUTESPMM_PATH_SLAB, where
+ * the copy engine places B in the tensor core's operand layout and no thread touches it. */
 #define CUTESPMM_FLAG_ROUND_B_NEAREST 1u
 
 typedef struct {

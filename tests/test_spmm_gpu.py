@@ -59,15 +59,17 @@ def test_any_number_of_columns(oracle_mod, N):
     assert oracle_mod.rel_fro(ref, run(p, B)) <= REL_FRO_TOL_FP32
 
 
-def test_slab_path_on_a_small_power_law_graph_and_round_to_nearest(oracle_mod):
+def test_slab_path_on_a_small_power_law_graph_and_rounding_modes(oracle_mod):
     A = g.rmat(11, 8, seed=33, values="uniform")  # wide 128-row panels, steps split at 256 values
     B = g.dense_operand(A.K, 256, 34).numpy()
     ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K)
-    e_trunc = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_SLAB), B))
-    e_round = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_SLAB, round_b_nearest=True), B))
-    assert e_round < e_trunc <= REL_FRO_TOL
-    e_brick = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_BRICK, round_b_nearest=True), B))
-    assert e_brick <= REL_FRO_TOL
+    e_slab = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_SLAB), B))
+    e_brick = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_BRICK), B))
+    e_round = oracle_mod.rel_fro(ref, run(cs.Plan.from_csr(A, path=cs.PATH_BRICK, round_b_nearest=True), B))
+    assert e_round < e_brick <= REL_FRO_TOL and e_slab <= REL_FRO_TOL
+    with pytest.raises(cs.CuteSpmmError) as e:  # B never passes a thread on the slab path, so it cannot be re-rounded
+        cs.Plan.from_csr(A, path=cs.PATH_SLAB, round_b_nearest=True)
+    assert e.value.status == -4
 
 
 def test_strided_and_misaligned_operands(oracle_mod):
