@@ -53,7 +53,7 @@ struct cutespmm_plan {
     void *d_row_ptr = nullptr, *d_pairs = nullptr, *d_tiles = nullptr, *d_chunks = nullptr, *d_long_rows = nullptr;
     void *d_tiles_all = nullptr, *d_chunks_all = nullptr, *d_long_rows_all = nullptr;
     void *d_bcols = nullptr, *d_brecs = nullptr, *d_brec_off = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
-    void *d_scols = nullptr, *d_srecs = nullptr, *d_srec_off = nullptr, *d_sfirst = nullptr, *d_slast = nullptr;
+    void *d_scols = nullptr, *d_srecs = nullptr, *d_srec_off = nullptr, *d_sfirst = nullptr, *d_slast = nullptr, *d_sids = nullptr;
     float *d_scratch = nullptr;
     uint32_t *d_status = nullptr;
     // staging for the host-buffer call
@@ -69,7 +69,7 @@ struct cutespmm_plan {
         if (cur != device) cudaSetDevice(device);
         for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
                         d_bcols, d_brecs, d_brec_off, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
-                        d_slast, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
+                        d_slast, d_sids, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
         if (ev0) cudaEventDestroy(ev0);
         if (ev1) cudaEventDestroy(ev1);
@@ -185,6 +185,7 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
         UP(so, p->d_srec_off)
         UP(h.slab_first, p->d_sfirst)
         UP(h.slab_last, p->d_slast)
+        UP(h.slab_ids, p->d_sids)
     }
 #undef UP
     const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
@@ -298,6 +299,7 @@ static SlabArgs slab_args(const cutespmm_plan *p, const float *B, uint64_t ldb, 
     a.rec_off = static_cast<const uint32_t *>(p->d_srec_off);
     a.panel_first = static_cast<const uint32_t *>(p->d_sfirst);
     a.panel_last = static_cast<const uint32_t *>(p->d_slast);
+    a.panel_ids = static_cast<const uint32_t *>(p->d_sids);
     a.num_panels = (uint32_t)p->host.slab_panels;
     a.M = (uint32_t)p->host.M;
     a.K = (uint32_t)p->host.K;

@@ -57,6 +57,7 @@ struct SlabArgs {
     const uint32_t *rec_off;      // per step slot (+1) record offsets in 16-byte units (+ slack)
     const uint32_t *panel_first;  // per slab panel: slot of its first step (a multiple of 4)
     const uint32_t *panel_last;   // per slab panel: one past the slot of its last step
+    const uint32_t *panel_ids;    // per slab panel: its 128-row panel index
     uint32_t num_panels;
     uint32_t M, K;
     const float *B;

@@ -53,9 +53,10 @@ struct LongRow {
 //     words 8..   the stored values (fp32) in map-bit order, padded with zeros to a multiple of 4
 constexpr uint32_t kBrickRecHeaderWords = 8;
 constexpr uint32_t kSlabRows = 128;      // rows of a slab panel (the M of one tcgen05.mma)
-constexpr uint32_t kSlabMaxVals = 256;   // values one step record may hold (bounds the shared-memory stage)
+constexpr uint32_t kSlabMaxVals = 192;   // values one step record may hold (bounds the shared-memory stage)
+constexpr uint32_t kSlabMaxRows = 32;    // rows one step record may list (one builder lane each)
 constexpr uint32_t kSlabRecHeaderWords = 8;
-constexpr uint32_t kSlabRecMaxWords = kSlabRecHeaderWords + kSlabRows + kSlabMaxVals;
+constexpr uint32_t kSlabRecMaxWords = kSlabRecHeaderWords + kSlabMaxRows + kSlabMaxVals;
 
 struct HostPlan {
     uint64_t M = 0, K = 0, nnz = 0;
@@ -97,10 +98,11 @@ struct HostPlan {
     //     words 4-7   128-bit map of the rows that have an entry
     //     words 8..   one entry per such row, in row order: row in panel | 8-bit column mask << 8 | index of its first value << 16
     //                 (padded to a multiple of 4 entries), then the values in (row, column) order, padded to x4
-    // A step with more than kSlabMaxVals values is stored as several steps over the same 8 columns.
+    // A step with more than kSlabMaxRows rows or kSlabMaxVals values is stored as several steps over the same 8 columns.
     // Every panel's steps are followed by empty slots up to a multiple of 4 (group-aligned metadata).
     std::vector<uint32_t> slab_cols, slab_recs, slab_rec_off;
     std::vector<uint32_t> slab_first, slab_last;  // per 128-row panel with nonzeros: slot range of its steps
+    std::vector<uint32_t> slab_ids;               // ... and its panel index (rows 128*id .. 128*id+127)
     std::vector<uint8_t> slab_path;               // per 128-row panel: 1 = executed by the slab kernel
     uint64_t slab_steps = 0, slab_panels = 0;
 

@@ -19,7 +19,7 @@ struct Ent {
 void build_slab_part(HostPlan &p)
 {
     p.slab_cols.clear(); p.slab_recs.clear(); p.slab_rec_off.clear();
-    p.slab_first.clear(); p.slab_last.clear();
+    p.slab_first.clear(); p.slab_last.clear(); p.slab_ids.clear();
     p.slab_steps = 0; p.slab_panels = 0;
     const uint64_t SP = (p.M + kSlabRows - 1) / kSlabRows;
     std::vector<uint32_t> acols;
@@ -61,17 +61,19 @@ void build_slab_part(HostPlan &p)
         }
         ++p.slab_panels;
         p.slab_first.push_back((uint32_t)p.slab_rec_off.size());
+        p.slab_ids.push_back((uint32_t)q);
         const size_t first_rec_of_panel = p.slab_rec_off.size();
         for (uint32_t t = 0; t < nsteps; ++t) {
             uint32_t a = count[t];
             const uint32_t b = count[t + 1];
-            while (a < b) {  // one record per <= kSlabMaxVals values, cut at a row boundary
-                uint32_t e = a, nv = 0;
+            while (a < b) {  // one record per <= kSlabMaxRows rows and <= kSlabMaxVals values, cut at a row boundary
+                uint32_t e = a, nv = 0, nr = 0;
                 while (e < b) {
                     uint32_t f = e;
                     while (f < b && sorted[f].row == sorted[e].row) ++f;
-                    if (nv + (f - e) > kSlabMaxVals) break;
+                    if (nv + (f - e) > kSlabMaxVals || nr == kSlabMaxRows) break;
                     nv += f - e;
+                    ++nr;
                     e = f;
                 }
                 // header + entries

@@ -35,38 +35,40 @@ namespace cutespmm {
 namespace {
 
 #ifndef SLAB_STAGES
-#define SLAB_STAGES 4   // steps in flight per block; a multiple of 4 (see static_assert)
+#define SLAB_STAGES 8   // steps of B in flight per block; a multiple of 4 (see static_assert)
 #endif
 #ifndef SLAB_META_SLOTS
 #define SLAB_META_SLOTS 64
 #endif
 #ifndef SLAB_BLOCKS_PER_SM
-#define SLAB_BLOCKS_PER_SM 4u
+#define SLAB_BLOCKS_PER_SM 3u
 #endif
 constexpr int kStages = SLAB_STAGES;
-// A stage is always refilled by the same producer warp and built by the same builder warp: a warp is
-// in order on its own stages, so the one-bit phase parity of the stage's barriers can never be two
+// A stage is always refilled by the same producer warp and its step built by the same builder warp: a
+// warp is in order on its own stages, so the one-bit phase parity of a barrier can never be two
 // phases stale.
 static_assert(kStages % 4 == 0, "stage i % kStages must belong to producer / builder warp i % 4");
-constexpr int kBuilders = 4;                  // builder warps 0-3, one TMEM lane quadrant each
+constexpr int kBuilders = 4;                  // builder warps 0-3, one TMEM lane quadrant each; warp w owns A tile w
 constexpr int kProducers = 4;                 // producer warps 4-7
 constexpr int kThreads = (kBuilders + kProducers + 1) * 32;  // + the MMA warp
 constexpr int kN = 128;                       // columns of B / C per block
 
-// shared memory: kStages stages (1024-byte aligned: the swizzle pattern is a function of the address),
-// two metadata buffers, barriers
-constexpr int kOffB = 0;                      // B operand tile: 4 column blocks x 2 K blocks x (4 rows x 128 B), swizzled
-constexpr int kOffA = 4096;                   // A operand tile: K-major, no swizzle
-constexpr int kOffRec = 8192;                 // the step's record
-constexpr int kOffDirty = kOffRec + (int)kSlabRecMaxWords * 4;  // rows of the A tile that hold values: count (16 B), row numbers
-constexpr int kStageBytes = (kOffDirty + 16 + 128 + 1023) / 1024 * 1024;
+// shared memory: kStages B stages (1024-byte aligned: the swizzle pattern is a function of the address),
+// four A tiles, two metadata buffers, barriers
+constexpr int kOffRec = 4096;                 // inside a B stage: the operand tile (4 column blocks x 2 K blocks x 512 B), then the record
+static_assert(kSlabRecMaxWords * 4 <= 1024, "a step record must fit behind the B tile");
+constexpr int kStageBytes = 4096 + 1024;
+constexpr int kOffATiles = kStages * kStageBytes;
+constexpr int kOffDirty = 4096;               // inside an A tile: the K-major operand tile, then the rows that hold values (count, row numbers)
+constexpr int kATileBytes = 4096 + 128;
 constexpr int kMetaSlots = SLAB_META_SLOTS;   // step slots whose metadata one buffer holds
 constexpr int kMetaBytes = kMetaSlots * 32 + (kMetaSlots + 4) * 4;  // columns, then record offsets (+ next, padded)
-constexpr int kOffMeta = kStages * kStageBytes;
+constexpr int kOffMeta = kOffATiles + kBuilders * kATileBytes;
 constexpr int kOffBars = kOffMeta + 2 * kMetaBytes;
-constexpr int kNumBars = 4 * kStages + 2 + 4;  // full, seen, built, mma_done per stage; panel_done, drained; meta_full[2], meta_free[2]
+// full, seen, mma_done per B stage; built per A tile; panel_done, drained; meta_full[2], meta_free[2]
+constexpr int kNumBars = 3 * kStages + kBuilders + 2 + 4;
 constexpr int kOffMisc = kOffBars + kNumBars * 8;
-constexpr int kSmemBytes = kOffMisc + 16 + kStages * 4;
+constexpr int kSmemBytes = kOffMisc + 16;
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t cols)
@@ -140,22 +142,22 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + kOffBars);  // TMA -> builders and MMA warp (1 arrival + bytes)
-    uint64_t *seen = full + kStages;         // builders -> producer: all four have read the record header (4 arrivals)
-    uint64_t *built = seen + kStages;        // owning builder -> MMA warp: the A tile is ready
-    uint64_t *mma_done = built + kStages;    // tcgen05.commit -> producer and builder: the stage's tiles may be rewritten
-    uint64_t *panel_done = mma_done + kStages;  // tcgen05.commit -> builders: the accumulator is complete
+    uint64_t *seen = full + kStages;         // owning builder -> producer: the record has been consumed
+    uint64_t *mma_done = seen + kStages;     // tcgen05.commit -> producer (B tile may be refilled) and builder (its A tile may be rewritten)
+    uint64_t *built = mma_done + kStages;    // owning builder -> MMA warp: A tile w is ready
+    uint64_t *panel_done = built + kBuilders;   // tcgen05.commit -> builders: the accumulator is complete
     uint64_t *drained = panel_done + 1;      // builders -> MMA warp: the accumulator has been read (4 arrivals)
     uint64_t *meta_full = drained + 1, *meta_free = meta_full + 2;
-    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(smem + kOffMisc);  // [0] TMEM base, [1] abort flag, [4+s] "last step" flags
+    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(smem + kOffMisc);  // [0] TMEM base, [1] abort flag
     const uint32_t n0 = blockIdx.y * kN;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&seen[s], kBuilders);
-            ptx::mbar_init(&built[s], 1);
+            ptx::mbar_init(&seen[s], 1);
             ptx::mbar_init(&mma_done[s], 1);
         }
+        for (int t = 0; t < kBuilders; ++t) ptx::mbar_init(&built[t], 1);
         ptx::mbar_init(panel_done, 1);
         ptx::mbar_init(drained, kBuilders);
         for (int m = 0; m < 2; ++m) {
@@ -166,9 +168,9 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
         ptx::fence_mbar_init();
     }
     // the A tiles start as zeros and hold no rows; afterwards the owning builder undoes exactly what it wrote
-    for (int i = tid; i < kStages * 256; i += kThreads)
-        *reinterpret_cast<uint4 *>(smem + (i / 256) * kStageBytes + kOffA + (i % 256) * 16) = make_uint4(0, 0, 0, 0);
-    if (tid < kStages) *reinterpret_cast<volatile uint32_t *>(smem + tid * kStageBytes + kOffDirty) = 0;
+    for (int i = tid; i < kBuilders * 256; i += kThreads)
+        *reinterpret_cast<uint4 *>(smem + kOffATiles + (i / 256) * kATileBytes + (i % 256) * 16) = make_uint4(0, 0, 0, 0);
+    if (tid < kBuilders) *reinterpret_cast<volatile uint32_t *>(smem + kOffATiles + tid * kATileBytes + kOffDirty) = 0;
     if (warp == 0) tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(&misc[0])), kN);  // 128 fp32 columns x 128 lanes
     ptx::fence_async_smem();  // the zeroed tiles are read through the async proxy
     tc_fence_before();
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                 // lane l < 8 loads K rows 4*(l&1) .. +3 of column block l>>1; its four row coordinates:
                 const uint4 rows4 = *reinterpret_cast<const uint4 *>(mcols + (k - cur_b) * 8 + (lane & 1) * 4);
                 const uint32_t o0 = moffs[k - cur_b], o1 = moffs[k - cur_b + 1];
-                // the stage is free once the MMA that read it is done and every builder has seen its record header
+                // the stage is free once the MMA that read its B tile is done and its builder has consumed the record
                 ok = ptx::mbar_wait(&mma_done[s], par) && ptx::mbar_wait(&seen[s], par);
                 if (!ok) break;
                 unsigned char *st = smem + s * kStageBytes;
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                     ptx::mbar_expect_tx(&full[s], 8u * kN * 4u + (o1 - o0) * 16u);
                     ptx::bulk_g2s(st + kOffRec, a.recs + (size_t)o0 * 4, (o1 - o0) * 16u, &full[s]);
                 } else if (lane < 8) {
-                    tma_gather4(st + kOffB + (lane >> 1) * 1024 + (lane & 1) * 512, &tmap_b, (int)(n0 + 32 * (lane >> 1)), (int)rows4.x,
+                    tma_gather4(st + (lane >> 1) * 1024 + (lane & 1) * 512, &tmap_b, (int)(n0 + 32 * (lane >> 1)), (int)rows4.x,
                                 (int)rows4.y, (int)rows4.z, (int)rows4.w, &full[s]);
                 }
             }
@@ -265,94 +267,88 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
     } else if (warp == kBuilders + kProducers) {
         // ================= MMA warp: one thread issues every tcgen05.mma of the block =================
         if (lane == 0) {
+            const uint64_t adesc0 = smem_desc(ptx::smem_u32(smem + kOffATiles), 128u, 256u, 0u);
+            const uint64_t bdesc0 = smem_desc(ptx::smem_u32(smem), 1024u, 512u, 1u);
             uint32_t step = 0;
             for (uint32_t p = 0; p < my_panels && !misc[1]; ++p) {
+                const uint32_t ord = blockIdx.x + p * gridDim.x;
+                const uint32_t nsteps = __ldg(a.panel_last + ord) - __ldg(a.panel_first + ord);
                 // the previous panel's accumulator must have been read before it is overwritten
                 if (p > 0 && !ptx::mbar_wait(drained, (p - 1) & 1u)) { abort_now(); break; }
-                bool first = true;
-                for (;;) {
-                    const int s = step % kStages;
-                    const uint32_t par = (step / kStages) & 1u;
-                    if (!ptx::mbar_wait(&built[s], par) || !ptx::mbar_wait(&full[s], par)) { abort_now(); break; }
+                bool ok = true;
+                for (uint32_t i = 0; i < nsteps; ++i, ++step) {
+                    const int s = step % kStages, t = step & 3;
+                    ok = ptx::mbar_wait(&built[t], (step >> 2) & 1u) && ptx::mbar_wait(&full[s], (step / kStages) & 1u);
+                    if (!ok) break;
                     tc_fence_after();
-                    unsigned char *st = smem + s * kStageBytes;
-                    const uint32_t last = misc[4 + s];
-                    tc_mma_tf32(tmem, smem_desc(ptx::smem_u32(st + kOffA), 128u, 256u, 0u), smem_desc(ptx::smem_u32(st + kOffB), 1024u, 512u, 1u),
-                                kIdesc, first ? 0u : 1u);
+                    // descriptors differ from the first tile's only in the address field (16-byte units)
+                    tc_mma_tf32(tmem, adesc0 + (uint64_t)(t * (kATileBytes >> 4)), bdesc0 + (uint64_t)(s * (kStageBytes >> 4)), kIdesc, i ? 1u : 0u);
                     tc_commit(&mma_done[s]);
-                    if (last) tc_commit(panel_done);
-                    first = false;
-                    ++step;
-                    if (last) break;
                 }
+                if (!ok) { abort_now(); break; }
+                tc_commit(panel_done);
             }
         }
     } else {
         // ================= builder warps 0-3: rows of A, then the accumulator read-back =================
-        // Step i is built by warp i & 3; every warp still reads every step's record header to follow the
-        // panel structure.
-        uint32_t step = 0;
+        // Step i of the block is built by warp i & 3 into its own A tile.  The number of steps of each of
+        // the block's panels comes from the panel table, so a warp touches only the steps it owns.
+        uint32_t step0 = 0;  // block-wide index of the current panel's first step
         for (uint32_t p = 0; p < my_panels && !misc[1]; ++p) {
-            uint32_t panel_idx = 0;
-            for (;;) {
+            const uint32_t ord = blockIdx.x + p * gridDim.x;
+            const uint32_t nsteps = __ldg(a.panel_last + ord) - __ldg(a.panel_first + ord);
+            const uint32_t panel_idx = __ldg(a.panel_ids + ord);
+            unsigned char *at = smem + kOffATiles + warp * kATileBytes;  // this warp's A tile
+            bool ok = true;
+            for (uint32_t step = step0 + ((warp - step0) & 3u); step < step0 + nsteps; step += 4) {
                 const int s = step % kStages;
-                const uint32_t par = (step / kStages) & 1u;
-                unsigned char *st = smem + s * kStageBytes;
-                if (!ptx::mbar_wait(&full[s], par)) {  // the step's record (and its rows of B) have landed
-                    if (lane == 0) abort_now();
-                    break;
+                // the step's record has landed; the MMA that read this warp's A tile four steps ago is done
+                ok = ptx::mbar_wait(&full[s], (step / kStages) & 1u) &&
+                     (step < 4 || ptx::mbar_wait(&mma_done[(step - 4) % kStages], ((step - 4) / kStages) & 1u));
+                if (!ok) break;
+                const uint32_t *rec = reinterpret_cast<const uint32_t *>(smem + s * kStageBytes + kOffRec);
+                const uint32_t cnt = rec[0] & 0xffffu;
+                // clear the rows written for that earlier step, then write this step's rows
+                volatile uint32_t *dirty_cnt = reinterpret_cast<volatile uint32_t *>(at + kOffDirty);
+                unsigned char *dirty_rows = at + kOffDirty + 16;
+                const uint32_t old = *dirty_cnt;
+                if ((uint32_t)lane < old) {
+                    const uint32_t r = dirty_rows[lane];
+                    float4 *d = reinterpret_cast<float4 *>(at + (r >> 3) * 256 + (r & 7) * 16);
+                    d[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    d[8] = make_float4(0.f, 0.f, 0.f, 0.f);  // + 128 bytes: the row's second K chunk
                 }
-                const uint32_t *rec = reinterpret_cast<const uint32_t *>(st + kOffRec);
-                const uint32_t head = rec[0];
-                const uint32_t last = (head >> 16) & 1u, cnt = head & 0xffffu;
-                panel_idx = rec[1];
-                if (warp == (int)(step & 3u)) {
-                    // clear the rows written the last time this stage was used (that MMA is done: the producer
-                    // waited for it before refilling the stage), then write this step's rows
-                    volatile uint32_t *dirty_cnt = reinterpret_cast<volatile uint32_t *>(st + kOffDirty);
-                    unsigned char *dirty_rows = st + kOffDirty + 16;
-                    const uint32_t old = *dirty_cnt;
-                    for (uint32_t e = lane; e < old; e += 32) {
-                        const uint32_t r = dirty_rows[e];
-                        float4 *d = reinterpret_cast<float4 *>(st + kOffA + (r >> 3) * 256 + (r & 7) * 16);
-                        d[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        d[8] = make_float4(0.f, 0.f, 0.f, 0.f);  // + 128 bytes: the row's second K chunk
-                    }
-                    __syncwarp();
+                __syncwarp();
+                if ((uint32_t)lane < cnt) {  // a record lists at most 32 rows: one lane each
                     const uint32_t *entries = rec + kSlabRecHeaderWords;
                     const float *vals = reinterpret_cast<const float *>(entries + (cnt + 3) / 4 * 4);
-                    for (uint32_t e = lane; e < cnt; e += 32) {
-                        const uint32_t ent = entries[e];
-                        const uint32_t r = ent & 0xffu, mask = (ent >> 8) & 0xffu;
-                        const float *v0 = vals + (ent >> 16);
-                        float v[8];
+                    const uint32_t ent = entries[lane];
+                    const uint32_t r = ent & 0xffu, mask = (ent >> 8) & 0xffu;
+                    const float *v0 = vals + (ent >> 16);
+                    float v[8];
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const float x = ((mask >> c) & 1u) ? v0[__popc(mask & ((1u << c) - 1u))] : 0.f;
-                            v[c] = __uint_as_float(ptx::f32_to_tf32_rna(x));
-                        }
-                        float4 *d = reinterpret_cast<float4 *>(st + kOffA + (r >> 3) * 256 + (r & 7) * 16);
-                        d[0] = make_float4(v[0], v[1], v[2], v[3]);
-                        d[8] = make_float4(v[4], v[5], v[6], v[7]);
-                        dirty_rows[e] = (unsigned char)r;
+                    for (int c = 0; c < 8; ++c) {
+                        const float x = ((mask >> c) & 1u) ? v0[__popc(mask & ((1u << c) - 1u))] : 0.f;
+                        v[c] = __uint_as_float(ptx::f32_to_tf32_rna(x));
                     }
-                    if (lane == 0) {
-                        *dirty_cnt = cnt;
-                        misc[4 + s] = last;
-                    }
-                    ptx::fence_async_smem();  // the tensor core reads the tile through the async proxy
-                    __syncwarp();
-                    if (lane == 0) {
-                        ptx::mbar_arrive(&built[s]);
-                        ptx::mbar_arrive(&seen[s]);
-                    }
-                } else {
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&seen[s]);  // this warp only needed the header
+                    float4 *d = reinterpret_cast<float4 *>(at + (r >> 3) * 256 + (r & 7) * 16);
+                    d[0] = make_float4(v[0], v[1], v[2], v[3]);
+                    d[8] = make_float4(v[4], v[5], v[6], v[7]);
+                    dirty_rows[lane] = (unsigned char)r;
                 }
-                ++step;
-                if (last) break;
+                if (lane == 0) *dirty_cnt = cnt;
+                ptx::fence_async_smem();  // the tensor core reads the tile through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&built[warp]);
+                    ptx::mbar_arrive(&seen[s]);
+                }
             }
+            if (!ok) {
+                if (lane == 0) abort_now();
+                break;
+            }
+            step0 += nsteps;
             if (misc[1]) break;
             // ---- end of panel: accumulator -> C (this warp's 32 rows) ----
             if (!ptx::mbar_wait(panel_done, p & 1u)) {
