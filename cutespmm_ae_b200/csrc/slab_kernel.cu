@@ -48,7 +48,14 @@ constexpr int kStages = SLAB_STAGES;
 // warp is in order on its own stages, so the one-bit phase parity of a barrier can never be two
 // phases stale.
 static_assert(kStages % 4 == 0, "stage i % kStages must belong to producer / builder warp i % 4");
-constexpr int kBuilders = 4;                  // builder warps 0-3, one TMEM lane quadrant each; warp w owns A tile w
+#ifndef SLAB_ATILES
+#define SLAB_ATILES 4    // A operand tiles per block; a multiple of 4: step i uses tile i % SLAB_ATILES, built by warp i & 3
+#endif
+constexpr int kATiles = SLAB_ATILES;
+// kATiles <= kStages: a builder waits for the MMA of step i - kATiles on that step's stage barrier, which must not
+// have been reused in between (the one-bit phase parity cannot tell two phases apart).
+static_assert(kATiles % 4 == 0 && kATiles <= kStages, "A tiles are owned by builder warps in turn");
+constexpr int kBuilders = 4;                  // builder warps 0-3, one TMEM lane quadrant each
 constexpr int kProducers = 4;                 // producer warps 4-7
 constexpr int kThreads = (kBuilders + kProducers + 1) * 32;  // + the MMA warp
 constexpr int kN = 128;                       // columns of B / C per block
@@ -63,10 +70,10 @@ constexpr int kOffDirty = 4096;               // inside an A tile: the K-major o
 constexpr int kATileBytes = 4096 + 128;
 constexpr int kMetaSlots = SLAB_META_SLOTS;   // step slots whose metadata one buffer holds
 constexpr int kMetaBytes = kMetaSlots * 32 + (kMetaSlots + 4) * 4;  // columns, then record offsets (+ next, padded)
-constexpr int kOffMeta = kOffATiles + kBuilders * kATileBytes;
+constexpr int kOffMeta = kOffATiles + kATiles * kATileBytes;
 constexpr int kOffBars = kOffMeta + 2 * kMetaBytes;
 // full, seen, mma_done per B stage; built per A tile; panel_done, drained; meta_full[2], meta_free[2]
-constexpr int kNumBars = 3 * kStages + kBuilders + 2 + 4;
+constexpr int kNumBars = 3 * kStages + kATiles + 2 + 4;
 constexpr int kOffMisc = kOffBars + kNumBars * 8;
 constexpr int kSmemBytes = kOffMisc + 16;
 
@@ -97,12 +104,15 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uin
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -145,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
     uint64_t *seen = full + kStages;         // owning builder -> producer: the record has been consumed
     uint64_t *mma_done = seen + kStages;     // tcgen05.commit -> producer (B tile may be refilled) and builder (its A tile may be rewritten)
     uint64_t *built = mma_done + kStages;    // owning builder -> MMA warp: A tile w is ready
-    uint64_t *panel_done = built + kBuilders;   // tcgen05.commit -> builders: the accumulator is complete
+    uint64_t *panel_done = built + kATiles;     // tcgen05.commit -> builders: the accumulator is complete
     uint64_t *drained = panel_done + 1;      // builders -> MMA warp: the accumulator has been read (4 arrivals)
     uint64_t *meta_full = drained + 1, *meta_free = meta_full + 2;
     volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(smem + kOffMisc);  // [0] TMEM base, [1] abort flag
@@ -157,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             ptx::mbar_init(&seen[s], 1);
             ptx::mbar_init(&mma_done[s], 1);
         }
-        for (int t = 0; t < kBuilders; ++t) ptx::mbar_init(&built[t], 1);
+        for (int t = 0; t < kATiles; ++t) ptx::mbar_init(&built[t], 1);
         ptx::mbar_init(panel_done, 1);
         ptx::mbar_init(drained, kBuilders);
         for (int m = 0; m < 2; ++m) {
@@ -168,9 +178,9 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
         ptx::fence_mbar_init();
     }
     // the A tiles start as zeros and hold no rows; afterwards the owning builder undoes exactly what it wrote
-    for (int i = tid; i < kBuilders * 256; i += kThreads)
+    for (int i = tid; i < kATiles * 256; i += kThreads)
         *reinterpret_cast<uint4 *>(smem + kOffATiles + (i / 256) * kATileBytes + (i % 256) * 16) = make_uint4(0, 0, 0, 0);
-    if (tid < kBuilders) *reinterpret_cast<volatile uint32_t *>(smem + kOffATiles + tid * kATileBytes + kOffDirty) = 0;
+    if (tid < kATiles) *reinterpret_cast<volatile uint32_t *>(smem + kOffATiles + tid * kATileBytes + kOffDirty) = 0;
     if (warp == 0) tmem_alloc(ptx::smem_u32(const_cast<uint32_t *>(&misc[0])), kN);  // 128 fp32 columns x 128 lanes
     ptx::fence_async_smem();  // the zeroed tiles are read through the async proxy
     tc_fence_before();
@@ -277,8 +287,8 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                 if (p > 0 && !ptx::mbar_wait(drained, (p - 1) & 1u)) { abort_now(); break; }
                 bool ok = true;
                 for (uint32_t i = 0; i < nsteps; ++i, ++step) {
-                    const int s = step % kStages, t = step & 3;
-                    ok = ptx::mbar_wait(&built[t], (step >> 2) & 1u) && ptx::mbar_wait(&full[s], (step / kStages) & 1u);
+                    const int s = step % kStages, t = step % kATiles;
+                    ok = ptx::mbar_wait(&built[t], (step / kATiles) & 1u) && ptx::mbar_wait(&full[s], (step / kStages) & 1u);
                     if (!ok) break;
                     tc_fence_after();
                     // descriptors differ from the first tile's only in the address field (16-byte units)
@@ -298,13 +308,13 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             const uint32_t ord = blockIdx.x + p * gridDim.x;
             const uint32_t nsteps = __ldg(a.panel_last + ord) - __ldg(a.panel_first + ord);
             const uint32_t panel_idx = __ldg(a.panel_ids + ord);
-            unsigned char *at = smem + kOffATiles + warp * kATileBytes;  // this warp's A tile
             bool ok = true;
             for (uint32_t step = step0 + ((warp - step0) & 3u); step < step0 + nsteps; step += 4) {
-                const int s = step % kStages;
-                // the step's record has landed; the MMA that read this warp's A tile four steps ago is done
+                const int s = step % kStages, t = step % kATiles;
+                unsigned char *at = smem + kOffATiles + t * kATileBytes;  // the step's A tile (one of this warp's)
+                // the step's record has landed; the MMA that read this A tile kATiles steps ago is done
                 ok = ptx::mbar_wait(&full[s], (step / kStages) & 1u) &&
-                     (step < 4 || ptx::mbar_wait(&mma_done[(step - 4) % kStages], ((step - 4) / kStages) & 1u));
+                     (step < (uint32_t)kATiles || ptx::mbar_wait(&mma_done[(step - kATiles) % kStages], ((step - kATiles) / kStages) & 1u));
                 if (!ok) break;
                 const uint32_t *rec = reinterpret_cast<const uint32_t *>(smem + s * kStageBytes + kOffRec);
                 const uint32_t cnt = rec[0] & 0xffffu;
@@ -340,7 +350,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                 ptx::fence_async_smem();  // the tensor core reads the tile through the async proxy
                 __syncwarp();
                 if (lane == 0) {
-                    ptx::mbar_arrive(&built[warp]);
+                    ptx::mbar_arrive(&built[t]);
                     ptx::mbar_arrive(&seen[s]);
                 }
             }
@@ -359,13 +369,13 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
             const uint64_t r = (uint64_t)panel_idx * kSlabRows + tid;
             float *crow = a.C + r * a.ldc + n0;
 #pragma unroll 1
-            for (int ch = 0; ch < 8; ++ch) {
-                uint32_t v[16];
-                tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + ch * 16, v);
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + ch * 32, v);
                 if (r < a.M) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        __stcs(reinterpret_cast<float4 *>(crow + ch * 16 + j * 4),
+                    for (int j = 0; j < 8; ++j)
+                        __stcs(reinterpret_cast<float4 *>(crow + ch * 32 + j * 4),
                                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
                                            __uint_as_float(v[4 * j + 3])));
                 }
