@@ -10,15 +10,18 @@
 //     one mbarrier per stage.  The reference
 //     drains a depth-2 cp.async pipeline and runs __syncthreads after every block of 16 columns
 //     (kernel.cu:220-222); here no two warps ever wait for each other;
-//   * the eight gathered rows of B of a brick arrive by eight TMA bulk copies (one 512-byte row slab
-//     each at N = 128, issued by eight lanes), the brick's record (bitmap + values) by a ninth; the
+//   * the eight gathered rows of B of a brick arrive by two TMA gather4 loads (four rows of the slab
+//     each, through a tensor map over B), the brick's record (bitmap + values) by a bulk copy; the
 //     copies for brick k + kStages - 1 are issued before brick k is computed, across panel
 //     boundaries, so the gather latency is hidden without occupancy;
 //   * a brick is 16 x 8 and maps onto mma.m16n8k8 (the reference issues m16n8k4 on 16 x 4 bricks);
 //     a warp covers the whole 128-column slab (16 accumulator tiles), so a brick is expanded once,
 //     not once per warp of a block;
-//   * B rows sit in shared memory with a stride of SLAB + 8 floats, which makes the B-fragment
-//     reads (lane (g,t) reads B[t][g], B[t+4][g]) hit 32 different banks;
+//   * B rows sit in shared memory with a stride of SLAB + 8 floats (the box of the tensor map is that
+//     wide; its last 8 columns are padding, filled without touching memory when they lie beyond N),
+//     which makes the B-fragment reads (lane (g,t) reads B[t][g], B[t+4][g]) hit 32 different banks.
+//     (Reading four tiles' fragments with one 128-bit load was measured slower: the register pairs
+//     the MMA wants then cost two moves per MMA.)
 //   * the work list is cut by brick count (nnz balance), not by a per-GPU occupancy table.
 #include <cuda_runtime.h>
 
@@ -27,6 +30,7 @@
 #include "device_plan.hpp"
 #include "plan.hpp"
 #include "ptx.cuh"
+#include "tmap.hpp"
 
 namespace cutespmm {
 
@@ -42,16 +46,18 @@ template <int NT> struct StageLayout {
     static constexpr int kSlab = 8 * NT;         // columns of B / C a warp covers
     static constexpr int kStride = kSlab + 8;    // floats between consecutive B rows in shared memory
     static constexpr int kBBytes = 8 * kStride * 4;
-    static constexpr int kStageBytes = kBBytes + kRecWords * 4;
+    static constexpr int kHalfBytes = 4 * kStride * 4;  // what one gather4 load writes
+    static constexpr int kStageBytes = kBBytes + kRecWords * 4;  // a warp's region: the B tiles of its stages, then their records
     // a warp's region: its stages, then its mbarriers; rounded so the next warp's stages stay 128-byte aligned
     static constexpr int kWarpBytes = (kStages * kStageBytes + kStages * 8 + 127) / 128 * 128;
-    static_assert(kStageBytes % 16 == 0 && kBBytes % 16 == 0, "TMA destinations must be 16-byte aligned");
+    static_assert(kBBytes % 128 == 0 && kHalfBytes % 128 == 0 && (kRecWords * 4) % 16 == 0, "gather4 destinations must be 128-byte aligned");
+    static_assert(kStride % 32 == 8, "the B-fragment reads are conflict-free only with this stride");
 };
 
 // ROUND_B: round the elements of B to tf32 to nearest (cvt.rna, what the reference does,
 // kernel.cu:35) instead of letting the tensor core drop the low 13 mantissa bits.
 template <int NT, bool ROUND_B>
-__global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickArgs a)
+__global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const __grid_constant__ CUtensorMap tmap_b, BrickArgs a)
 {
     using L = StageLayout<NT>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -67,8 +73,8 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
 
     unsigned char *mine = smem_raw + (size_t)warp * L::kWarpBytes;
     uint64_t *full = reinterpret_cast<uint64_t *>(mine + kStages * L::kStageBytes);
-    auto stage_b = [&](int s) { return reinterpret_cast<float *>(mine + s * L::kStageBytes); };
-    auto stage_rec = [&](int s) { return reinterpret_cast<uint32_t *>(mine + s * L::kStageBytes + L::kBBytes); };
+    auto stage_b = [&](int s) { return reinterpret_cast<float *>(mine + s * L::kBBytes); };
+    auto stage_rec = [&](int s) { return reinterpret_cast<uint32_t *>(mine + kStages * L::kBBytes + s * (kRecWords * 4)); };
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) ptx::mbar_init(&full[s], 1);
         ptx::fence_mbar_init();
@@ -76,14 +82,17 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     __syncwarp();
 
     // ---- producer state --------------------------------------------------------------------------
-    // Metadata travels in groups of 4 brick slots: lane l holds column l of the group's 32 columns,
-    // lanes 0..4 hold its five record offsets.  A panel starts on a group boundary.  Loaded ahead of
-    // use: the next group of the current panel, the first group of the warp's next panel, and the
+    // Metadata travels in groups of 4 brick slots: lane 2j+h (lanes 0..7) holds columns 4h..4h+3 of
+    // slot j, lanes 8..11 hold the record offsets.  A panel starts on a group boundary.  Loaded ahead
+    // of use: the next group of the current panel, the first group of the warp's next panel, and the
     // slot range of the panel after that.
-    auto load_cols = [&](uint32_t g) { return __ldg(a.cols + (size_t)g * 32 + lane); };
-    // lanes 0..3: lane j holds the record offsets of slot j of the group and of the slot after it (as one 64-bit value)
+    auto load_cols = [&](uint32_t g) {
+        return lane < 8 ? __ldg(reinterpret_cast<const uint4 *>(a.cols + (size_t)g * 32) + lane) : make_uint4(0, 0, 0, 0);
+    };
+    // lane 8+j holds the record offsets of slot j of the group and of the slot after it (as one 64-bit value)
     auto load_offs = [&](uint32_t g) {
-        return lane < 4 ? ((uint64_t)__ldg(a.rec_off + (size_t)g * 4 + lane + 1) << 32) | __ldg(a.rec_off + (size_t)g * 4 + lane) : 0ull;
+        const uint32_t j = (uint32_t)lane - 8u;
+        return j < 4u ? ((uint64_t)__ldg(a.rec_off + (size_t)g * 4 + j + 1) << 32) | __ldg(a.rec_off + (size_t)g * 4 + j) : 0ull;
     };
     auto load_range = [&](uint32_t o, uint32_t &k0, uint32_t &k1) {
         k0 = k1 = 0;
@@ -95,20 +104,18 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
     uint32_t pk, pk_end;  // producer cursor: next slot to issue, end of its panel
     load_range(ord, pk, pk_end);
     uint32_t G = pk >> 2;
-    uint32_t mc_cur = load_cols(G), mc_nxt = load_cols(G + 1);
+    uint4 mc_cur = load_cols(G), mc_nxt = load_cols(G + 1);
     uint64_t mo_cur = load_offs(G), mo_nxt = load_offs(G + 1);
     uint32_t n_k0, n_k1, nn_k0, nn_k1;  // slot ranges of the next panel and the one after (k0 == k1: none)
     load_range(ord + W, n_k0, n_k1);
     load_range(ord + 2 * W, nn_k0, nn_k1);
-    uint32_t n_mc = load_cols(n_k0 >> 2);
+    uint4 n_mc = load_cols(n_k0 >> 2);
     uint64_t n_mo = load_offs(n_k0 >> 2);
     uint32_t p_ord = ord;            // panel ordinal of the producer cursor
     uint32_t issued = 0, done = 0;   // bricks issued / consumed by this warp so far
     int is = 0, ds = 0;              // ring positions of the next brick to issue / to consume
     uint32_t dpar = 0;               // mbarrier phase parity of stage ds
 
-    const float *Bn = a.B + n0;
-    const uint32_t ldb32 = (uint32_t)a.ldb;
     auto producer_has_work = [&]() { return pk < pk_end; };
     auto issue_one = [&]() {  // start the copies of slot pk into stage issued % kStages, then advance the cursor
         const uint32_t k = pk;
@@ -121,16 +128,17 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(BrickAr
         }
         const int s = is;
         is = (is + 1 == kStages) ? 0 : is + 1;
-        // lanes 8j..8j+7 hold the eight columns of slot j of the group, lane j its record offsets: the
-        // lanes that own slot k & 3 start its copies straight from their registers
+        // the lanes that own slot k & 3 start its copies straight from their registers: lane 8+j the
+        // record, lanes 2j and 2j+1 one gather4 load of four rows of B each
         const uint32_t j = k & 3;
-        if ((uint32_t)lane == j) {
+        if ((uint32_t)lane == 8u + j) {
             const uint32_t o0 = (uint32_t)mo_cur, rec_bytes = ((uint32_t)(mo_cur >> 32) - o0) * 16u;
-            ptx::mbar_expect_tx(&full[s], 8u * L::kSlab * 4u + rec_bytes);
+            ptx::mbar_expect_tx(&full[s], (uint32_t)L::kBBytes + rec_bytes);
             ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)o0 * 4, rec_bytes, &full[s]);
         }
-        if ((uint32_t)(lane >> 3) == j)
-            ptx::bulk_g2s(stage_b(s) + (lane & 7) * L::kStride, Bn + (uint64_t)mc_cur * ldb32, L::kSlab * 4u, &full[s]);
+        if ((uint32_t)(lane >> 1) == j)
+            ptx::tma_gather4(reinterpret_cast<unsigned char *>(stage_b(s)) + (lane & 1) * L::kHalfBytes, &tmap_b, (int)n0, (int)mc_cur.x,
+                             (int)mc_cur.y, (int)mc_cur.z, (int)mc_cur.w, &full[s]);
         ++issued;
         if (++pk == pk_end) {  // panel finished: move the cursor to the warp's next panel
             p_ord += W;
@@ -225,7 +233,11 @@ template <int NT, bool ROUND_B> cudaError_t launch_brick_t(const BrickArgs &a, i
     const uint32_t slabs = a.N / L::kSlab;
     uint32_t blocks = (a.num_panels + kBrickWarps - 1) / kBrickWarps;
     if (blocks > (uint32_t)sm_count) blocks = (uint32_t)sm_count;  // one resident block per SM, persistent
-    spmm_brick_kernel<NT, ROUND_B><<<dim3(blocks, slabs), kBrickWarps * 32, smem, s>>>(a);
+    // B as a 2-D tensor; the box is the slab plus the 8 columns of padding that give the shared-memory stride
+    CUtensorMap tmap;
+    cudaError_t e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, L::kStride, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (e != cudaSuccess) return e;
+    spmm_brick_kernel<NT, ROUND_B><<<dim3(blocks, slabs), kBrickWarps * 32, smem, s>>>(tmap, a);
     return cudaGetLastError();
 }
 

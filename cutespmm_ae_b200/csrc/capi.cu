@@ -283,6 +283,7 @@ static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb
     a.num_bricks = (uint32_t)p->host.num_bricks;
     a.num_panels = (uint32_t)p->host.brick_panels;
     a.M = (uint32_t)p->host.M;
+    a.K = (uint32_t)p->host.K;
     a.B = B; a.C = C;
     a.ldb = ldb; a.ldc = ldc;
     a.N = N;

@@ -38,7 +38,7 @@ struct BrickArgs {
     const uint32_t *panel_first;  // per brick panel: slot of its first brick (a multiple of 4)
     const uint32_t *panel_last;   // per brick panel: one past the slot of its last brick
     uint32_t num_bricks, num_panels;
-    uint32_t M;
+    uint32_t M, K;
     const float *B;
     float *C;
     uint64_t ldb, ldc;

@@ -61,6 +61,17 @@ __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gmem_src, u
                  : "memory");
 }
 
+// TMA gather4: four rows (coordinates y0..y3) of the 2-D tensor described by `tmap`, box-width columns from
+// column x (x * element size must be a multiple of 16 bytes), land as four consecutive rows at smem_dst
+// (128-byte aligned; more for swizzled maps); completion counted on `bar`.
+__device__ __forceinline__ void tma_gather4(void *smem_dst, const void *tmap, int x, int y0, int y1, int y2, int y3, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(smem_u32(bar))
+        : "memory");
+}
+
 __device__ __forceinline__ uint32_t f32_to_tf32_rna(float x)
 {
     uint32_t r;

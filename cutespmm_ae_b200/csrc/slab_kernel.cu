@@ -29,6 +29,7 @@
 #include "device_plan.hpp"
 #include "plan.hpp"
 #include "ptx.cuh"
+#include "tmap.hpp"
 
 namespace cutespmm {
 
@@ -116,17 +117,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Four rows of a 2-D tensor (row coordinates y0..y3, 32 columns from x) -> four consecutive 128-byte
-// rows of shared memory, swizzled as the tensor map says; completion counted on `bar`.
-__device__ __forceinline__ void tma_gather4(void *smem_dst, const CUtensorMap *tmap, int x, int y0, int y1, int y2, int y3, uint64_t *bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-        ::"r"(ptx::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3),
-        "r"(ptx::smem_u32(bar))
-        : "memory");
 }
 
 // Shared-memory matrix descriptor (descriptor version 1 in bits 46-47).  lbo / sbo in bytes.
@@ -260,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
                     ptx::mbar_expect_tx(&full[s], 8u * kN * 4u + (o1 - o0) * 16u);
                     ptx::bulk_g2s(st + kOffRec, a.recs + (size_t)o0 * 4, (o1 - o0) * 16u, &full[s]);
                 } else if (lane < 8) {
-                    tma_gather4(st + (lane >> 1) * 1024 + (lane & 1) * 512, &tmap_b, (int)(n0 + 32 * (lane >> 1)), (int)rows4.x,
+                    ptx::tma_gather4(st + (lane >> 1) * 1024 + (lane & 1) * 512, &tmap_b, (int)(n0 + 32 * (lane >> 1)), (int)rows4.x,
                                 (int)rows4.y, (int)rows4.z, (int)rows4.w, &full[s]);
                 }
             }
@@ -394,22 +384,6 @@ __global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel
     }
 }
 
-// cuTensorMapEncodeTiled, looked up through the runtime (the library does not link libcuda)
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled()
-{
-    static EncodeTiledFn fn = [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
 }  // namespace
 
 bool slab_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const void *C)
@@ -428,15 +402,9 @@ cudaError_t launch_slab(const SlabArgs &a, int sm_count, cudaStream_t s)
         configured = true;
     }
     // B as a 2-D tensor (columns innermost); one gather4 brings 4 rows x 32 columns = a 4 x 128-byte atom
-    EncodeTiledFn enc = encode_tiled();
-    if (!enc) return cudaErrorNotSupported;
     CUtensorMap tmap;
-    const cuuint64_t dims[2] = {a.N, a.K};
-    const cuuint64_t strides[1] = {a.ldb * sizeof(float)};
-    const cuuint32_t box[2] = {32, 1}, estr[2] = {1, 1};
-    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(a.B), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
+    cudaError_t e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (e != cudaSuccess) return e;
     uint32_t blocks = (uint32_t)sm_count * SLAB_BLOCKS_PER_SM;  // shared memory and tensor memory (128 of 512 columns each) allow this many per SM
     if (blocks > a.num_panels) blocks = a.num_panels;
     spmm_slab_kernel<<<dim3(blocks, a.N / kN), kThreads, kSmemBytes, s>>>(tmap, a);
