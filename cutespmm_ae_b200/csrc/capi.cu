@@ -59,7 +59,11 @@ struct cutespmm_plan {
     // staging for the host-buffer call
     float *d_B = nullptr, *d_C = nullptr;
     uint64_t staged_B = 0, staged_C = 0;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    // the host-buffer call pipelines column windows: copy-in, product and copy-out each on a stream of their own
+    static constexpr int kMaxWindows = 4;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_entry = nullptr, ev_done = nullptr;
+    cudaEvent_t ev_in[kMaxWindows] = {}, ev_k0[kMaxWindows] = {}, ev_k1[kMaxWindows] = {};
 
     ~cutespmm_plan()
     {
@@ -71,8 +75,13 @@ struct cutespmm_plan {
                         d_bcols, d_brecs, d_brec_off, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
                         d_slast, d_sids, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
-        if (ev0) cudaEventDestroy(ev0);
-        if (ev1) cudaEventDestroy(ev1);
+        for (cudaEvent_t ev : {ev_entry, ev_done})
+            if (ev) cudaEventDestroy(ev);
+        for (int w = 0; w < kMaxWindows; ++w)
+            for (cudaEvent_t ev : {ev_in[w], ev_k0[w], ev_k1[w]})
+                if (ev) cudaEventDestroy(ev);
+        if (s_in) cudaStreamDestroy(s_in);
+        if (s_out) cudaStreamDestroy(s_out);
         if (cur != device && cur >= 0) cudaSetDevice(cur);
     }
 };
@@ -382,8 +391,18 @@ int cutespmm_spmm_host(cutespmm_plan_t *p, const float *B_host, uint64_t ldb, fl
     if (ldb < N || ldc < N) return fail(CUTESPMM_EINVAL, "leading dimension smaller than N");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    const uint64_t ldd = (N + 3) / 4 * 4;  // device leading dimension: rows start 16-byte aligned
-    const uint64_t needB = p->host.K * ldd * sizeof(float), needC = p->host.M * ldd * sizeof(float);
+    // Column windows are independent products (C[:, w] = A * B[:, w]), so the call is a pipeline over them:
+    // while window w is multiplied and copied out, window w+1 is already coming in; the two copy directions
+    // run on different engines.  Small operands go in one piece.
+    const uint64_t M = p->host.M, K = p->host.K;
+    uint32_t nw = 1;
+    if ((uint64_t)N * std::max(M, K) * sizeof(float) >= (8u << 20)) nw = std::max(1u, std::min<uint32_t>(cutespmm_plan::kMaxWindows, N / 64));
+    // window width: a multiple of 64 columns (the last may be narrower); strided copies of rows shorter than 256 bytes
+    // were measured at 2/3 of the link rate, 256-byte rows at the full rate
+    const uint32_t wcols = ((N + nw - 1) / nw + 63) / 64 * 64;
+    nw = (N + wcols - 1) / wcols;
+    const uint64_t ldd = nw == 1 ? (uint64_t)(N + 3) / 4 * 4 : wcols;  // device leading dimension: rows start 16-byte aligned
+    const uint64_t needB = (uint64_t)nw * K * ldd * sizeof(float), needC = (uint64_t)nw * M * ldd * sizeof(float);
     if (needB > p->staged_B) {
         if (p->d_B) cudaFree(p->d_B);
         p->d_B = nullptr; p->staged_B = 0;
@@ -396,24 +415,54 @@ int cutespmm_spmm_host(cutespmm_plan_t *p, const float *B_host, uint64_t ldb, fl
         if ((e = cudaMalloc(&p->d_C, needC)) != cudaSuccess) return fail_cuda(e, "staging buffer for C");
         p->staged_C = needC;
     }
-    if (!p->ev0) {
-        if ((e = cudaEventCreate(&p->ev0)) != cudaSuccess || (e = cudaEventCreate(&p->ev1)) != cudaSuccess)
+    if (!p->s_in) {
+        if ((e = cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking)) != cudaSuccess ||
+            (e = cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking)) != cudaSuccess)
+            return fail_cuda(e, "cudaStreamCreate");
+        if ((e = cudaEventCreateWithFlags(&p->ev_entry, cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming)) != cudaSuccess)
             return fail_cuda(e, "cudaEventCreate");
+        for (int w = 0; w < cutespmm_plan::kMaxWindows; ++w)
+            if ((e = cudaEventCreateWithFlags(&p->ev_in[w], cudaEventDisableTiming)) != cudaSuccess ||
+                (e = cudaEventCreate(&p->ev_k0[w])) != cudaSuccess || (e = cudaEventCreate(&p->ev_k1[w])) != cudaSuccess)
+                return fail_cuda(e, "cudaEventCreate");
     }
-    if (p->host.K &&
-        (e = cudaMemcpy2DAsync(p->d_B, ldd * sizeof(float), B_host, ldb * sizeof(float), (size_t)N * sizeof(float),
-                               p->host.K, cudaMemcpyHostToDevice, s)) != cudaSuccess)
-        return fail_cuda(e, "copy of B to the device");
-    cudaEventRecord(p->ev0, s);
-    int st = cutespmm_spmm(p, p->d_B, ldd, p->d_C, ldd, N, s);
-    if (st != CUTESPMM_OK) return st;
-    cudaEventRecord(p->ev1, s);
-    if (p->host.M &&
-        (e = cudaMemcpy2DAsync(C_host, ldc * sizeof(float), p->d_C, ldd * sizeof(float), (size_t)N * sizeof(float),
-                               p->host.M, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
-        return fail_cuda(e, "copy of C to the host");
+    // whatever the caller queued on `stream` comes first
+    cudaEventRecord(p->ev_entry, s);
+    cudaStreamWaitEvent(p->s_in, p->ev_entry, 0);
+    for (uint32_t w = 0; w < nw; ++w) {
+        const uint32_t c0 = w * wcols, cw = std::min(wcols, N - c0);
+        float *dB = p->d_B + (uint64_t)w * K * ldd, *dC = p->d_C + (uint64_t)w * M * ldd;
+        if (K && (e = cudaMemcpy2DAsync(dB, ldd * sizeof(float), B_host + c0, ldb * sizeof(float), (size_t)cw * sizeof(float), K,
+                                        cudaMemcpyHostToDevice, p->s_in)) != cudaSuccess)
+            return fail_cuda(e, "copy of B to the device");
+        cudaEventRecord(p->ev_in[w], p->s_in);
+        cudaStreamWaitEvent(s, p->ev_in[w], 0);
+        cudaEventRecord(p->ev_k0[w], s);
+        int st = cutespmm_spmm(p, dB, ldd, dC, ldd, cw, s);
+        if (st != CUTESPMM_OK) {
+            cudaStreamSynchronize(p->s_in);
+            cudaStreamSynchronize(p->s_out);
+            cudaStreamSynchronize(s);
+            return st;
+        }
+        cudaEventRecord(p->ev_k1[w], s);
+        cudaStreamWaitEvent(p->s_out, p->ev_k1[w], 0);
+        if (M && (e = cudaMemcpy2DAsync(C_host + c0, ldc * sizeof(float), dC, ldd * sizeof(float), (size_t)cw * sizeof(float), M,
+                                        cudaMemcpyDeviceToHost, p->s_out)) != cudaSuccess)
+            return fail_cuda(e, "copy of C to the host");
+    }
+    cudaEventRecord(p->ev_done, p->s_out);
+    cudaStreamWaitEvent(s, p->ev_done, 0);  // later work on `stream` sees the finished call
     if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return fail_cuda(e, "SpMM execution");
-    if (kernel_ms) cudaEventElapsedTime(kernel_ms, p->ev0, p->ev1);
+    if (kernel_ms) {
+        *kernel_ms = 0.f;
+        for (uint32_t w = 0; w < nw; ++w) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, p->ev_k0[w], p->ev_k1[w]);
+            *kernel_ms += ms;
+        }
+    }
     uint32_t dev_status = 0;
     cutespmm_plan_device_status(p, &dev_status);
     if (dev_status) return fail(CUTESPMM_ETIMEOUT, "a device-side wait ran out (status " + std::to_string(dev_status) + ")");

@@ -131,9 +131,11 @@ int cutespmm_spmm(const cutespmm_plan_t *plan, const float *B_dev, uint64_t ldb,
 
 /* Host-buffer call in the style of the reference driver loop (run.cu:38-53) and of its
  * float GPU_xxx(host pointers..., m, k, n, ...) wrappers (spmm.cu:860): copies B to the device,
- * runs the product, copies C back, all on `stream`, and waits for it.  The device staging buffers
- * belong to the plan and are (re)allocated only when N grows.  kernel_ms (may be NULL) receives
- * the device time of the product alone. */
+ * runs the product, copies C back, ordered after the work already queued on `stream`, and waits
+ * for it.  Large operands are pipelined in up to four column windows (copy-in, product and
+ * copy-out on streams of the plan's own), so pinned host buffers let the two copy directions
+ * overlap.  The device staging buffers belong to the plan and are (re)allocated only when N
+ * grows.  kernel_ms (may be NULL) receives the device time of the products alone. */
 int cutespmm_spmm_host(cutespmm_plan_t *plan, const float *B_host, uint64_t ldb, float *C_host,
                        uint64_t ldc, uint32_t N, void *stream, float *kernel_ms);
 

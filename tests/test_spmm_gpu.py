@@ -141,6 +141,28 @@ def test_host_buffer_call(oracle_mod):
     assert oracle_mod.rel_fro(gd["C"][:, :17].copy(), C2.numpy()) <= REL_FRO_TOL
 
 
+@pytest.mark.parametrize("N,pad,pinned", [(128, 0, True), (256, 0, True), (200, 12, True), (160, 0, False), (40, 8, True)])
+def test_host_call_pipelined_in_column_windows(oracle_mod, N, pad, pinned):
+    """Operands of 8 MB and more go through the host call in up to four column windows (copy-in,
+    product, copy-out overlapped); the result must be the one-piece product for every window
+    shape: full windows, a narrow last window, padded leading dimensions, pageable memory."""
+    A = g.stencil9(192)  # M = K = 36864: 36864 x 128 x 4 B = 18.9 MB at N = 128 (two windows), 5.9 MB at N = 40 (one piece)
+    p = cs.Plan.from_csr(A)
+    Bfull = torch.randn(A.K, N + pad)
+    Cfull = torch.full((A.M, N + pad), float("nan"))
+    if pinned:
+        Bfull, Cfull = Bfull.pin_memory(), Cfull.pin_memory()
+    Bh, Ch = Bfull[:, :N], Cfull[:, :N]
+    _, ms = p.spmm_host(Bh, Ch)
+    assert ms > 0.0
+    ref = p.spmm(Bh.cuda().contiguous()).cpu()  # device-resident call, one piece (may take another kernel: compare at tolerance)
+    assert oracle_mod.rel_fro(ref.numpy(), Ch.contiguous().numpy()) <= REL_FRO_TOL
+    if pad:
+        assert torch.isnan(Cfull[:, N:]).all()  # nothing written beyond column N
+    want = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, Bh.contiguous().numpy(), A.M, A.K)
+    assert oracle_mod.rel_fro(want, Ch.contiguous().numpy()) <= REL_FRO_TOL
+
+
 def test_execution_errors_are_status_codes():
     gd = load_golden("stencil_16x16")
     p = cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"])
