@@ -24,12 +24,15 @@ namespace cutespmm {
 
 namespace {
 
-#ifndef ROWS_MIN_BLOCKS
-#define ROWS_MIN_BLOCKS 4
-#endif
-#ifndef ROWS_UNROLL
-#define ROWS_UNROLL 8
-#endif
+// Two tunings of the row kernel, chosen per launch (measured on R-MAT 2^20 and the 512x512 stencil at N = 128):
+//   DEEP = false  4 rows of B in flight per warp, 6 blocks (48 warps) per SM: more warps hide the gather latency
+//                 better than more loads per warp once the grid is several waves of tiles long;
+//   DEEP = true   8 rows in flight, 4 blocks per SM: fewer dependent steps per row, better when the whole job
+//                 is a single wave of tiles and the time is a handful of latencies.
+template <bool DEEP> struct Tuning {
+    static constexpr int kUnroll = DEEP ? 8 : 4;
+    static constexpr int kMinBlocks = DEEP ? 4 : 6;
+};
 constexpr int kWarps = 8;
 constexpr int kStages = 3;  // tiles in flight per block (TMA bulk copies into shared memory)
 
@@ -118,8 +121,37 @@ __device__ __forceinline__ void accumulate(typename Vec<VEC>::T (&acc)[CH], cons
     }
 }
 
-template <int VEC, int CH, bool FULL>
-__global__ void __launch_bounds__(kWarps * 32, ROWS_MIN_BLOCKS) spmm_rows_kernel(RowsArgs a)
+// acc[ch] += sum of val * B[col][lane's columns] over `cnt` staged (column, value) pairs, UU rows of B in flight.
+// TAIL: cnt may be smaller than UU; the surplus positions load the row of the last pair again (an L1 hit) and
+// are left out of the sum.
+template <int VEC, int CH, bool FULL, int UU, bool TAIL>
+__device__ __forceinline__ void row_group(typename Vec<VEC>::T (&acc)[CH], const uint2 *pairs_smem, uint32_t cnt, const float *__restrict__ bl,
+                                          uint32_t ldb32, const bool (&ok)[CH])
+{
+    using V = typename Vec<VEC>::T;
+    float v[UU];
+    V b[UU][CH];
+#pragma unroll
+    for (int u = 0; u < UU; ++u) {
+        const uint2 pr = pairs_smem[TAIL ? min((uint32_t)u, cnt - 1) : (uint32_t)u];  // all lanes read one address: broadcast
+        v[u] = __uint_as_float(pr.y);
+        const float *row = bl + (uint64_t)pr.x * ldb32;
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+            if (FULL || ok[ch]) b[u][ch] = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
+            else zero_vec(b[u][ch]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UU; ++u)
+        if (!TAIL || (uint32_t)u < cnt) {
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) fma_vec(acc[ch], v[u], b[u][ch]);
+        }
+}
+
+template <int VEC, int CH, bool FULL, bool DEEP>
+__global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_rows_kernel(RowsArgs a)
 {
     using V = typename Vec<VEC>::T;
     const int lane = threadIdx.x & 31;
@@ -198,33 +230,14 @@ __global__ void __launch_bounds__(kWarps * 32, ROWS_MIN_BLOCKS) spmm_rows_kernel
             V acc[CH];
 #pragma unroll
             for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
-            constexpr int U = (CH == 1) ? ROWS_UNROLL : ROWS_UNROLL / 2;  // rows of B in flight per warp and step
+            constexpr int U = (CH == 1) ? Tuning<DEEP>::kUnroll : Tuning<DEEP>::kUnroll / 2;  // rows of B in flight per warp and step
             uint32_t j = j0 - jb, jend = j1 - jb;  // positions in the staged pair slice
-            for (; j + U <= jend; j += U) {
-                float v[U];
-                V b[U][CH];
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const uint2 pr = stage[s].pairs[j + u];  // all lanes read one address: broadcast
-                    v[u] = __uint_as_float(pr.y);
-                    const float *row = bl + (uint64_t)pr.x * ldb32;
-#pragma unroll
-                    for (int ch = 0; ch < CH; ++ch) {
-                        if (FULL || ok[ch]) b[u][ch] = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
-                        else zero_vec(b[u][ch]);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-#pragma unroll
-                    for (int ch = 0; ch < CH; ++ch) fma_vec(acc[ch], v[u], b[u][ch]);
-            }
-            for (; j < jend; ++j) {
-                const uint2 pr = stage[s].pairs[j];
-                const float *row = bl + (uint64_t)pr.x * ldb32;
-#pragma unroll
-                for (int ch = 0; ch < CH; ++ch)
-                    if (FULL || ok[ch]) fma_vec(acc[ch], __uint_as_float(pr.y), ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC)));
+            for (; j + U <= jend; j += U) row_group<VEC, CH, FULL, U, false>(acc, stage[s].pairs + j, U, bl, ldb32, ok);
+            // what is left of the row (fewer than U nonzeros) goes as one more group, so that its loads are in flight
+            // together instead of one after the other: positions past the end repeat the row's last pair and are not added
+            if (const uint32_t rem = jend - j) {
+                if (rem > U / 2) row_group<VEC, CH, FULL, U, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
+                else row_group<VEC, CH, FULL, U / 2, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
             }
             float *out = a.C + (uint64_t)r * a.ldc + col0;
 #pragma unroll
@@ -264,13 +277,13 @@ __global__ void __launch_bounds__(128) spmm_fixup_kernel(const uint4 *__restrict
     }
 }
 
-template <int VEC, int CH, bool FULL>
+template <int VEC, int CH, bool FULL, bool DEEP>
 cudaError_t launch_rows_t(const RowsArgs &a, uint32_t slabs, int sm_count, cudaStream_t s)
 {
     static int blocks_per_sm = 0;  // same for every device of one model; queried once
     if (blocks_per_sm == 0) {
         int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, spmm_rows_kernel<VEC, CH, FULL>, kWarps * 32, 0);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, spmm_rows_kernel<VEC, CH, FULL, DEEP>, kWarps * 32, 0);
         if (e != cudaSuccess) return e;
         blocks_per_sm = n > 0 ? n : 1;
     }
@@ -279,7 +292,7 @@ cudaError_t launch_rows_t(const RowsArgs &a, uint32_t slabs, int sm_count, cudaS
     uint32_t gx = (uint32_t)(work < want ? work : want);
     if (slabs > 1) gx = (gx + slabs - 1) / slabs;  // keep the whole grid about one resident wave
     if (gx == 0) gx = 1;
-    spmm_rows_kernel<VEC, CH, FULL><<<dim3(gx, slabs), kWarps * 32, 0, s>>>(a);
+    spmm_rows_kernel<VEC, CH, FULL, DEEP><<<dim3(gx, slabs), kWarps * 32, 0, s>>>(a);
     return cudaGetLastError();
 }
 
@@ -296,11 +309,15 @@ cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s)
     const bool v4 = !((pb | pc | ps) & 15) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 3);
     const bool v2 = !((pb | pc | ps) & 7) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 1);
     const uint32_t N = a.N;
+    const bool deep = (uint64_t)a.num_tiles <= (uint64_t)sm_count * 6;  // at most one resident wave of tiles
 #define CUTESPMM_GO(VEC, CH)                                                                   \
     do {                                                                                       \
         const uint32_t w = 32 * VEC * CH, slabs = (N + w - 1) / w;                             \
-        return (N % w == 0) ? launch_rows_t<VEC, CH, true>(a, slabs, sm_count, s)              \
-                            : launch_rows_t<VEC, CH, false>(a, slabs, sm_count, s);            \
+        if (deep)                                                                              \
+            return (N % w == 0) ? launch_rows_t<VEC, CH, true, true>(a, slabs, sm_count, s)    \
+                                : launch_rows_t<VEC, CH, false, true>(a, slabs, sm_count, s);  \
+        return (N % w == 0) ? launch_rows_t<VEC, CH, true, false>(a, slabs, sm_count, s)       \
+                            : launch_rows_t<VEC, CH, false, false>(a, slabs, sm_count, s);     \
     } while (0)
     if (v4 && N > 64) {
         if (N >= 256) CUTESPMM_GO(4, 2);

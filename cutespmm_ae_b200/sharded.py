@@ -1,0 +1,110 @@
+"""Row-sharded SpMM over the ranks of a torch.distributed process group (one process per GPU).
+
+Row panels are independent, so A is cut into contiguous row ranges of equal cost (nonzeros plus a
+per-row term, 16-row aligned: `cutespmm_partition_rows`), every rank builds a plan over its own rows
+only, and C stays row-sharded: rank p owns rows [bounds[p], bounds[p+1]).  The one exchange of the
+path is B, which every rank needs in its own memory.  Two ways to run a product:
+
+* `spmm(B)`           B is already replicated (iterative solvers, the layers of a GNN after the
+                      first): purely local, no collective.
+* `spmm_from_root(B)` B lives on one rank.  It travels by broadcast in column windows, and the
+                      product of a window starts as soon as that window has arrived, so the
+                      multiplication overlaps the tail of the transfer (column windows of B are
+                      independent products: C[:, w] = A @ B[:, w]).
+
+The reference has no multi-GPU path; its single-GPU driver loop (run.cu:38-53) is what a rank runs
+on its shard.  No kernel reads another GPU's memory: B comes into local memory first (NCCL).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import numpy as np
+
+from . import PATH_AUTO, Plan, partition_rows
+
+
+def column_windows(N: int, max_windows: int = 4, min_cols: int = 32) -> list[tuple[int, int]]:
+    """Cuts N columns into at most `max_windows` windows [c0, c1) whose width is a multiple of
+    `min_cols` (the last may be narrower)."""
+    if N <= 0:
+        return []
+    nw = max(1, min(max_windows, N // min_cols))
+    width = -(-N // nw)
+    width = -(-width // min_cols) * min_cols
+    return [(c0, min(c0 + width, N)) for c0 in range(0, N, width)]
+
+
+class ShardedSpmm:
+    """This rank's shard of A and the operations on it.
+
+    A: anything with M, K, row_ptr, cols, vals and row_slice(r0, r1) (generators.CsrMatrix); every
+    rank passes the same matrix (or its own way of producing the same rows).  `group` is a
+    torch.distributed process group (None: the default group; a single process works without one).
+    `host_only=True` builds the plan without touching CUDA (tests of the host logic on CPU ranks).
+    """
+
+    def __init__(self, A, group=None, *, path: int = PATH_AUTO, host_only: bool = False, align_rows: int = 16, **plan_kw):
+        import torch.distributed as dist
+
+        self.group = group
+        self.dist = dist if dist.is_available() and dist.is_initialized() else None
+        self.world = self.dist.get_world_size(group) if self.dist else 1
+        self.rank = self.dist.get_rank(group) if self.dist else 0
+        self.M, self.K = A.M, A.K
+        rp = A.row_ptr.cpu() if hasattr(A.row_ptr, "cpu") else A.row_ptr
+        self.bounds = partition_rows(rp, self.world, align_rows=align_rows) if self.world > 1 else np.array([0, A.M], dtype=np.uint64)
+        self.r0, self.r1 = int(self.bounds[self.rank]), int(self.bounds[self.rank + 1])
+        mine = A.row_slice(self.r0, self.r1) if self.world > 1 else A
+        if hasattr(mine, "cpu"):
+            mine = mine.cpu()
+        self.rows = mine
+        self.plan = Plan.from_csr(mine, path=path, host_only=host_only, **plan_kw)
+
+    # ---- B already in every rank's memory --------------------------------------------------------
+    def spmm(self, B, Cout=None, stream=None):
+        """Rows [r0, r1) of A @ B; B is a K x N CUDA tensor resident on this rank."""
+        return self.plan.spmm(B, Cout, stream)
+
+    # ---- B on one rank ---------------------------------------------------------------------------
+    def spmm_from_root(self, B, N: int, root: int = 0, Cout=None, *, max_windows: int = 4, min_cols: int = 32,
+                       product: Optional[Callable] = None, device=None):
+        """Rows [r0, r1) of A @ B where B (K x N) is given on rank `root` only (None elsewhere).
+
+        B is sent window-major (each column window a contiguous K x w block), all broadcasts are
+        queued at once, and the product of window w is queued behind the arrival of window w only.
+        Returns (C, windows): C is this rank's (r1-r0) x N block, `windows` the received K x w
+        blocks (kept so that a caller can reuse B without a second transfer).
+
+        `product(Bw, Cw)` computes Cw = A_rows @ Bw; default: this rank's plan on the GPU.  Tests on
+        CPU ranks pass a CPU product of their own.
+        """
+        import torch
+
+        if product is None:
+            product = lambda Bw, Cw: self.plan.spmm(Bw, Cw)  # noqa: E731
+        wins = column_windows(N, max_windows, min_cols)
+        if self.rank == root:
+            if B is None or tuple(B.shape) != (self.K, N):
+                raise ValueError("the root rank must pass B with shape (K, N)")
+            device = B.device
+        elif device is None:
+            raise ValueError("ranks other than the root must say on which device B is to be received")
+        if Cout is None:
+            Cout = torch.empty((self.r1 - self.r0, N), dtype=torch.float32, device=device)
+        blocks, works = [], []
+        for c0, c1 in wins:
+            blk = B[:, c0:c1].contiguous() if self.rank == root else torch.empty((self.K, c1 - c0), dtype=torch.float32, device=device)
+            blocks.append(blk)
+            if self.world > 1:
+                works.append(self.dist.broadcast(blk, src=self._global_rank(root), group=self.group, async_op=True))
+        for i, (c0, c1) in enumerate(wins):
+            if works:
+                works[i].wait()  # CUDA: the current stream waits for window i only; the host does not block
+            product(blocks[i], Cout[:, c0:c1])
+        return Cout, blocks
+
+    def _global_rank(self, group_rank: int) -> int:
+        if self.dist is None or self.group is None:
+            return group_rank
+        return self.dist.get_global_rank(self.group, group_rank)

@@ -68,6 +68,66 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
+def _worker_windows(rank, world, port, out_dir):
+    """ShardedSpmm.spmm_from_root on CPU ranks: B on the last rank only, broadcast in column windows,
+    each window multiplied as it arrives (by the CPU oracle standing in for the device product)."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from cutespmm_ae_b200 import generators as g
+        from cutespmm_ae_b200.sharded import ShardedSpmm, column_windows
+
+        A = g.stencil9(24)
+        N, root = 80, world - 1
+        sh = ShardedSpmm(A, host_only=True)
+        assert (sh.world, sh.rank) == (world, rank)
+        assert sh.r0 % 16 == 0 and int(sh.bounds[0]) == 0 and int(sh.bounds[-1]) == A.M
+        assert column_windows(N, 4, 32) == [(0, 64), (64, 80)]
+        calls = []
+
+        def product(Bw, Cw):
+            calls.append(tuple(Bw.shape))
+            Cw.copy_(torch.from_numpy(oracle.spmm_csr(sh.rows.row_ptr, sh.rows.cols, sh.rows.vals, Bw.numpy(), sh.rows.M, sh.rows.K)))
+
+        B = g.dense_operand(A.K, N, 91) if rank == root else None
+        C_mine, blocks = sh.spmm_from_root(B, N, root=root, product=product, device=torch.device("cpu"))
+        assert calls == [(A.K, 64), (A.K, 16)]
+        assert [tuple(b.shape) for b in blocks] == calls and all(b.is_contiguous() for b in blocks)
+        torch.save({"r0": sh.r0, "r1": sh.r1, "C": C_mine, "B": torch.cat(blocks, dim=1)}, Path(out_dir) / f"win{rank}.pt")
+        dist.barrier()
+        if rank == 0:
+            parts = [torch.load(Path(out_dir) / f"win{r}.pt") for r in range(world)]
+            Bfull = parts[root]["B"].numpy()
+            assert all(np.array_equal(p["B"].numpy(), Bfull) for p in parts)  # every rank received all of B
+            full = oracle.spmm_csr(A.row_ptr, A.cols, A.vals, Bfull, A.M, A.K)
+            got = np.concatenate([p["C"].numpy() for p in parts], axis=0)
+            assert [p["r0"] for p in parts[1:]] == [p["r1"] for p in parts[:-1]]
+            assert np.array_equal(full.view(np.uint32), got.view(np.uint32))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_row_sharding_over_gloo_ranks(tmp_path, world):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_windowed_broadcast_pipeline_over_gloo_ranks(tmp_path, world):
+    mp.spawn(_worker_windows, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+
+
+def test_column_windows():
+    from cutespmm_ae_b200.sharded import column_windows
+
+    assert column_windows(128, 4, 32) == [(0, 32), (32, 64), (64, 96), (96, 128)]
+    assert column_windows(128, 2, 64) == [(0, 64), (64, 128)]
+    assert column_windows(24, 4, 32) == [(0, 24)]
+    assert column_windows(100, 4, 32) == [(0, 64), (64, 100)]
+    assert column_windows(0) == []
+    for N in range(1, 300, 7):
+        w = column_windows(N, 4, 32)
+        assert w[0][0] == 0 and w[-1][1] == N and all(a[1] == b[0] for a, b in zip(w, w[1:])) and len(w) <= 4
