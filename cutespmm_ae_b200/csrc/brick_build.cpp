@@ -1,10 +1,11 @@
 // Packs the panels routed to the tensor-core kernel into the flat brick stream described in
 // plan.hpp.  The role of the block/brick writer in the reference (data.cu:212-296) with a different
 // layout: a brick spans 8 active columns (the K extent of mma.m16n8k8 / one tcgen05 K step), every
-// record is self-describing (map, panel, end-of-panel flag) and starts on a 16-byte boundary so one
-// TMA bulk copy fetches it, and the column list is a separate array the producer lanes read
-// coalesced.  Values are stored unrounded (the kernel rounds to tf32 like the reference's
-// cvt.rna, kernel.cu:28-29), so the format is lossless.
+// record is self-describing (map, panel, end-of-panel flag), has a fixed size and starts on a 16-byte
+// boundary so one TMA bulk copy fetches it, holds the brick's values already in MMA fragment order,
+// and the column list is a separate array the producer lanes read coalesced.  Values are stored
+// unrounded (the kernel rounds to tf32 like the reference's cvt.rna, kernel.cu:28-29), so the
+// format is lossless.
 #include "plan.hpp"
 
 #include <algorithm>
@@ -58,18 +59,17 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
             for (uint32_t bit = 0; bit < 128; ++bit)
                 if (present[(size_t)b * 128 + bit]) head[bit >> 5] |= 1u << (bit & 31);
             p.brick_recs.insert(p.brick_recs.end(), head, head + kBrickRecHeaderWords);
-            uint32_t cnt = 0;
-            for (uint32_t bit = 0; bit < 128; ++bit) {
-                if (!present[(size_t)b * 128 + bit]) continue;
-                uint32_t vb;
-                std::memcpy(&vb, &img[(size_t)b * 128 + bit], 4);
-                p.brick_recs.push_back(vb);
-                ++cnt;
-            }
-            for (; cnt % 4; ++cnt) p.brick_recs.push_back(0u);
+            const size_t base = p.brick_recs.size();
+            p.brick_recs.resize(base + 128, 0u);
+            for (uint32_t bit = 0; bit < 128; ++bit)
+                if (present[(size_t)b * 128 + bit])
+                    std::memcpy(&p.brick_recs[base + brick_frag_index(bit / kBrickCols, bit % kBrickCols)], &img[(size_t)b * 128 + bit], 4);
             ++p.num_bricks;
         }
-        for (uint32_t b = nbricks; b < nslots; ++b) p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));  // empty slots
+        for (uint32_t b = nbricks; b < nslots; ++b) {  // empty slots
+            p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));
+            p.brick_recs.resize(p.brick_recs.size() + kBrickRecWords, 0u);
+        }
         p.panel_last_brick.push_back((uint32_t)(p.brick_rec_off.size() - (nslots - nbricks)));
     }
     p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));

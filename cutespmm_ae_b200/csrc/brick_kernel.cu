@@ -2,16 +2,18 @@
 // contraction (zeros included) costs less than gathering a row of B per nonzero.
 //
 // It takes the place of SpMM<NUM_WARPS,ILP_LEVEL> + COMPUTE<ILP> (reference kernel.cu:16-288).
-// What is kept: 16-row panels, active-column compaction, occupancy bitmaps expanded into MMA
-// A-fragments by popcount (kernel.cu:20-27), TF32 inputs rounded to nearest (cvt.rna,
+// What is kept: 16-row panels, active-column compaction, TF32 inputs rounded to nearest (cvt.rna,
 // kernel.cu:28-35) with fp32 accumulation.  What is different:
+//   * a brick's values are stored already in MMA fragment order, zeros included (544-byte records),
+//     instead of a bitmap plus packed values expanded by popcounts (kernel.cu:20-27): the kernel is
+//     bound by instruction latency, not by bytes, and the expansion was a sixth of its instructions;
 //   * every warp is an autonomous pipeline over its own sequence of panels (panels are dealt
 //     round-robin over the warps of the grid); it owns a ring of kStages shared-memory stages and
 //     one mbarrier per stage.  The reference
 //     drains a depth-2 cp.async pipeline and runs __syncthreads after every block of 16 columns
 //     (kernel.cu:220-222); here no two warps ever wait for each other;
 //   * the eight gathered rows of B of a brick arrive by two TMA gather4 loads (four rows of the slab
-//     each, through a tensor map over B), the brick's record (bitmap + values) by a bulk copy; the
+//     each, through a tensor map over B), the brick's record by a bulk copy; the
 //     copies for brick k + kStages - 1 are issued before brick k is computed, across panel
 //     boundaries, so the gather latency is hidden without occupancy;
 //   * a brick is 16 x 8 and maps onto mma.m16n8k8 (the reference issues m16n8k4 on 16 x 4 bricks);
@@ -40,7 +42,7 @@ namespace {
 #define BRICK_STAGES 3
 #endif
 constexpr int kStages = BRICK_STAGES;
-constexpr int kRecWords = kBrickRecHeaderWords + 128;  // header + a full brick of values
+constexpr int kRecWords = kBrickRecWords;  // header + a full brick of values
 
 template <int NT> struct StageLayout {
     static constexpr int kSlab = 8 * NT;         // columns of B / C a warp covers
@@ -83,16 +85,11 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
 
     // ---- producer state --------------------------------------------------------------------------
     // Metadata travels in groups of 4 brick slots: lane 2j+h (lanes 0..7) holds columns 4h..4h+3 of
-    // slot j, lanes 8..11 hold the record offsets.  A panel starts on a group boundary.  Loaded ahead
-    // of use: the next group of the current panel, the first group of the warp's next panel, and the
-    // slot range of the panel after that.
+    // slot j (records need none: slot k's record is at word k * kRecWords).  A panel starts on a group
+    // boundary.  Loaded ahead of use: the next group of the current panel, the first group of the
+    // warp's next panel, and the slot range of the panel after that.
     auto load_cols = [&](uint32_t g) {
         return lane < 8 ? __ldg(reinterpret_cast<const uint4 *>(a.cols + (size_t)g * 32) + lane) : make_uint4(0, 0, 0, 0);
-    };
-    // lane 8+j holds the record offsets of slot j of the group and of the slot after it (as one 64-bit value)
-    auto load_offs = [&](uint32_t g) {
-        const uint32_t j = (uint32_t)lane - 8u;
-        return j < 4u ? ((uint64_t)__ldg(a.rec_off + (size_t)g * 4 + j + 1) << 32) | __ldg(a.rec_off + (size_t)g * 4 + j) : 0ull;
     };
     auto load_range = [&](uint32_t o, uint32_t &k0, uint32_t &k1) {
         k0 = k1 = 0;
@@ -105,12 +102,10 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
     load_range(ord, pk, pk_end);
     uint32_t G = pk >> 2;
     uint4 mc_cur = load_cols(G), mc_nxt = load_cols(G + 1);
-    uint64_t mo_cur = load_offs(G), mo_nxt = load_offs(G + 1);
     uint32_t n_k0, n_k1, nn_k0, nn_k1;  // slot ranges of the next panel and the one after (k0 == k1: none)
     load_range(ord + W, n_k0, n_k1);
     load_range(ord + 2 * W, nn_k0, nn_k1);
     uint4 n_mc = load_cols(n_k0 >> 2);
-    uint64_t n_mo = load_offs(n_k0 >> 2);
     uint32_t p_ord = ord;            // panel ordinal of the producer cursor
     uint32_t issued = 0, done = 0;   // bricks issued / consumed by this warp so far
     int is = 0, ds = 0;              // ring positions of the next brick to issue / to consume
@@ -122,19 +117,16 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
         if ((k >> 2) != G) {
             ++G;
             mc_cur = mc_nxt;
-            mo_cur = mo_nxt;
             mc_nxt = load_cols(G + 1);
-            mo_nxt = load_offs(G + 1);
         }
         const int s = is;
         is = (is + 1 == kStages) ? 0 : is + 1;
-        // the lanes that own slot k & 3 start its copies straight from their registers: lane 8+j the
-        // record, lanes 2j and 2j+1 one gather4 load of four rows of B each
+        // lane 8 starts the copy of the record; lanes 2j and 2j+1, which hold the columns of slot j = k & 3,
+        // start one gather4 load of four rows of B each straight from their registers
         const uint32_t j = k & 3;
-        if ((uint32_t)lane == 8u + j) {
-            const uint32_t o0 = (uint32_t)mo_cur, rec_bytes = ((uint32_t)(mo_cur >> 32) - o0) * 16u;
-            ptx::mbar_expect_tx(&full[s], (uint32_t)L::kBBytes + rec_bytes);
-            ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)o0 * 4, rec_bytes, &full[s]);
+        if (lane == 8) {
+            ptx::mbar_expect_tx(&full[s], (uint32_t)L::kBBytes + kRecWords * 4u);
+            ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)k * kRecWords, kRecWords * 4u, &full[s]);
         }
         if ((uint32_t)(lane >> 1) == j)
             ptx::tma_gather4(reinterpret_cast<unsigned char *>(stage_b(s)) + (lane & 1) * L::kHalfBytes, &tmap_b, (int)n0, (int)mc_cur.x,
@@ -146,25 +138,18 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
             pk_end = n_k1;
             G = pk >> 2;
             mc_cur = n_mc;
-            mo_cur = n_mo;
             n_k0 = nn_k0;
             n_k1 = nn_k1;
             if (pk < pk_end) {
                 mc_nxt = load_cols(G + 1);
-                mo_nxt = load_offs(G + 1);
                 n_mc = load_cols(n_k0 >> 2);
-                n_mo = load_offs(n_k0 >> 2);
                 load_range(p_ord + 2 * W, nn_k0, nn_k1);
             }
         }
     };
 
-    // lane-constant pieces of the A-fragment expansion (mma.m16n8k8 row-major A: a0 = A[g][t],
-    // a1 = A[g+8][t], a2 = A[g][t+4], a3 = A[g+8][t+4]; map bit = row*8 + col)
+    // mma.m16n8k8 row-major A: lane (g,t) holds a0 = A[g][t], a1 = A[g+8][t], a2 = A[g][t+4], a3 = A[g+8][t+4]
     const int g = lane >> 2, t = lane & 3;
-    const bool upper_word = (g >> 2) != 0;  // rows 4..7 (and 12..15) live in the odd words
-    const uint32_t bit0 = (g & 3) * 8 + t, bit2 = bit0 + 4;
-    const uint32_t below0 = (1u << bit0) - 1u, below2 = (1u << bit2) - 1u;
 
     float acc[NT][4];
 #pragma unroll
@@ -186,17 +171,13 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
             dpar ^= 1u;
         }
         const uint32_t *rec = stage_rec(s);
-        const uint4 map = *reinterpret_cast<const uint4 *>(rec);
         const uint2 info = *reinterpret_cast<const uint2 *>(rec + 4);
-        const float *vals = reinterpret_cast<const float *>(rec + kBrickRecHeaderWords);
-        const uint32_t c1 = __popc(map.x), c2 = c1 + __popc(map.y), c3 = c2 + __popc(map.z);
-        const uint32_t wl = upper_word ? map.y : map.x, wh = upper_word ? map.w : map.z;
-        const uint32_t base_l = upper_word ? c1 : 0u, base_h = upper_word ? c3 : c2;
+        const float4 a4 = *reinterpret_cast<const float4 *>(rec + kBrickRecHeaderWords + 4 * lane);  // this lane's fragment, zeros included
         uint32_t af[4];
-        af[0] = ptx::f32_to_tf32_rna(((wl >> bit0) & 1u) ? vals[base_l + __popc(wl & below0)] : 0.f);
-        af[1] = ptx::f32_to_tf32_rna(((wh >> bit0) & 1u) ? vals[base_h + __popc(wh & below0)] : 0.f);
-        af[2] = ptx::f32_to_tf32_rna(((wl >> bit2) & 1u) ? vals[base_l + __popc(wl & below2)] : 0.f);
-        af[3] = ptx::f32_to_tf32_rna(((wh >> bit2) & 1u) ? vals[base_h + __popc(wh & below2)] : 0.f);
+        af[0] = ptx::f32_to_tf32_rna(a4.x);
+        af[1] = ptx::f32_to_tf32_rna(a4.y);
+        af[2] = ptx::f32_to_tf32_rna(a4.z);
+        af[3] = ptx::f32_to_tf32_rna(a4.w);
         const float *b_lo = stage_b(s) + t * L::kStride + g, *b_hi = b_lo + 4 * L::kStride;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {

@@ -52,7 +52,7 @@ struct cutespmm_plan {
     // device arrays
     void *d_row_ptr = nullptr, *d_pairs = nullptr, *d_tiles = nullptr, *d_chunks = nullptr, *d_long_rows = nullptr;
     void *d_tiles_all = nullptr, *d_chunks_all = nullptr, *d_long_rows_all = nullptr;
-    void *d_bcols = nullptr, *d_brecs = nullptr, *d_brec_off = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
+    void *d_bcols = nullptr, *d_brecs = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
     void *d_scols = nullptr, *d_srecs = nullptr, *d_srec_off = nullptr, *d_sfirst = nullptr, *d_slast = nullptr, *d_sids = nullptr;
     float *d_scratch = nullptr;
     uint32_t *d_status = nullptr;
@@ -72,7 +72,7 @@ struct cutespmm_plan {
         cudaGetDevice(&cur);
         if (cur != device) cudaSetDevice(device);
         for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
-                        d_bcols, d_brecs, d_brec_off, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
+                        d_bcols, d_brecs, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
                         d_slast, d_sids, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
         for (cudaEvent_t ev : {ev_entry, ev_done})
@@ -176,12 +176,10 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
     UP(h.long_rows_all, p->d_long_rows_all)
     if (h.num_bricks) {
         // the producer lanes prefetch a group (4 brick slots) beyond the one in use: keep that readable
-        std::vector<uint32_t> bc(h.brick_cols), ro(h.brick_rec_off);
+        std::vector<uint32_t> bc(h.brick_cols);
         bc.resize(bc.size() + 96, 0u);
-        ro.resize(ro.size() + 16, ro.back());
         UP(bc, p->d_bcols)
         UP(h.brick_recs, p->d_brecs)
-        UP(ro, p->d_brec_off)
         UP(h.panel_first_brick, p->d_panel_first)
         UP(h.panel_last_brick, p->d_panel_last)
     }
@@ -286,7 +284,6 @@ static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb
     BrickArgs a{};
     a.cols = static_cast<const uint32_t *>(p->d_bcols);
     a.recs = static_cast<const uint32_t *>(p->d_brecs);
-    a.rec_off = static_cast<const uint32_t *>(p->d_brec_off);
     a.panel_first = static_cast<const uint32_t *>(p->d_panel_first);
     a.panel_last = static_cast<const uint32_t *>(p->d_panel_last);
     a.num_bricks = (uint32_t)p->host.num_bricks;

@@ -33,8 +33,7 @@ int rows_kernel_count(const RowsArgs &a);
 constexpr int kBrickWarps = BRICK_WARPS;  // warps per block; each is an independent pipeline over its own brick range
 struct BrickArgs {
     const uint32_t *cols;         // 8 columns per brick slot (+ readable slack of a few groups behind the end)
-    const uint32_t *recs;         // brick records (map, flags, panel, values)
-    const uint32_t *rec_off;      // per brick slot (+1) record offsets in 16-byte units (+ slack)
+    const uint32_t *recs;         // brick records (map, flags, panel, values in fragment order): slot k at word k * kBrickRecWords
     const uint32_t *panel_first;  // per brick panel: slot of its first brick (a multiple of 4)
     const uint32_t *panel_last;   // per brick panel: one past the slot of its last brick
     uint32_t num_bricks, num_panels;

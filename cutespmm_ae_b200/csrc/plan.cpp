@@ -239,17 +239,15 @@ void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float
                 rows[r].push_back({p.pairs[j].col, v});
             }
     }
-    for (uint64_t k = 0; k + 1 < p.brick_rec_off.size(); ++k) {
-        if (p.brick_rec_off[k + 1] == p.brick_rec_off[k]) continue;  // empty slot
+    for (uint64_t i = 0; i < p.panel_first_brick.size(); ++i)
+    for (uint64_t k = p.panel_first_brick[i]; k < p.panel_last_brick[i]; ++k) {  // the panel's bricks (not its empty slots)
         const uint32_t *rec = &p.brick_recs[(size_t)p.brick_rec_off[k] * 4];
         const uint32_t panel = rec[5];
-        uint32_t cnt = 0;
         for (uint32_t bit = 0; bit < 128; ++bit) {
             if (!((rec[bit >> 5] >> (bit & 31)) & 1u)) continue;
             float v;
-            std::memcpy(&v, &rec[kBrickRecHeaderWords + cnt], 4);
+            std::memcpy(&v, &rec[kBrickRecHeaderWords + brick_frag_index(bit / kBrickCols, bit % kBrickCols)], 4);
             rows[(size_t)panel * kPanelRows + bit / kBrickCols].push_back({p.brick_cols[k * kBrickCols + bit % kBrickCols], v});
-            ++cnt;
         }
     }
     for (uint64_t t = 0; t + 1 < p.slab_rec_off.size(); ++t) {

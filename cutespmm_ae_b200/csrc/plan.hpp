@@ -50,8 +50,18 @@ struct LongRow {
 //     word  4     bit 0: last brick of its panel
 //     word  5     panel index (rows 16*panel .. 16*panel+15)
 //     words 6-7   0
-//     words 8..   the stored values (fp32) in map-bit order, padded with zeros to a multiple of 4
+//     words 8-135 the whole 16 x 8 brick (fp32, unrounded), zeros included, in the order the MMA wants it: word
+//                 8 + 4*lane + i is A-fragment register i of that lane (brick_frag_index below), so a lane expands
+//                 nothing: it loads its four values with one 128-bit read
+// Every slot has a record of kBrickRecWords words (empty slots: zeros), brick k at word k * kBrickRecWords.
+// (A packed record -- map plus the stored values only, expanded by popcounts as the reference does,
+// kernel.cu:20-27 -- is a quarter of the size but was measured 5-11 % slower: the expansion is 50 dependent
+// instructions per brick in a kernel that is bound by instruction latency, not by bytes.)
 constexpr uint32_t kBrickRecHeaderWords = 8;
+constexpr uint32_t kBrickRecWords = kBrickRecHeaderWords + 128;
+// mma.m16n8k8 row-major A fragment: lane (g = lane / 4, t = lane % 4) holds a0 = A[g][t], a1 = A[g+8][t],
+// a2 = A[g][t+4], a3 = A[g+8][t+4].  Position of element (row r, column c) of a brick in the dense record.
+constexpr uint32_t brick_frag_index(uint32_t r, uint32_t c) { return ((r & 7u) * 4u + (c & 3u)) * 4u + (r >> 3) + 2u * (c >> 2); }
 constexpr uint32_t kSlabRows = 128;      // rows of a slab panel (the M of one tcgen05.mma)
 constexpr uint32_t kSlabMaxVals = 192;   // values one step record may hold (bounds the shared-memory stage)
 constexpr uint32_t kSlabMaxRows = 32;    // rows one step record may list (one builder lane each)
