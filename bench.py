@@ -334,25 +334,32 @@ def run_ours(args):
     if plan.device_status() != 0:
         raise SystemExit(f"device status word is {plan.device_status()}: a bounded wait ran out")
 
-    # B on rank 0 only: broadcast in column windows with the products queued behind their windows
-    pipelined_ms = None
+    # B on rank 0 only: broadcast (whole, or in two column windows with each product queued behind its window), then the product
+    from_root = None
     if dist:
         n_p = min(args.steps, 5)
         Cp = torch.empty_like(C)
-        shard.spmm_from_root(B if rank == 0 else None, N, root=0, Cout=Cp, max_windows=2, min_cols=64, device=dev)  # warm-up
-        torch.cuda.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n_p):
-            shard.spmm_from_root(B if rank == 0 else None, N, root=0, Cout=Cp, max_windows=2, min_cols=64, device=dev)
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / n_p], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        pipelined_ms = float(t.item())
-        if not torch.allclose(Cp, C, rtol=1e-3, atol=1e-3):
-            raise SystemExit("the windowed product differs from the one-piece product")
+        by_windows = {}
+        for nwin in (1, 2):
+            kw = dict(root=0, Cout=Cp, max_windows=nwin, min_cols=64, device=dev)
+            shard.spmm_from_root(B if rank == 0 else None, N, **kw)  # warm-up
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n_p):
+                shard.spmm_from_root(B if rank == 0 else None, N, **kw)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / n_p], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            by_windows[nwin] = float(t.item())
+            if not torch.allclose(Cp, C, rtol=1e-3, atol=1e-3):
+                raise SystemExit("the product behind the broadcast differs from the resident-B product")
+        best = min(by_windows, key=by_windows.get)
+        from_root = {"ms_per_step": round(by_windows[best], 3), "windows": best, "unit": "GFLOP/s",
+                     "ms_by_windows": {str(k): round(v, 3) for k, v in by_windows.items()}}
+        shard._recv.clear()
         del Cp
 
     # end to end through the host-buffer entry point: pinned host B in, host C out, every step
@@ -405,9 +412,9 @@ def run_ours(args):
     if bcast_ms is not None:
         line["bcast_ms"] = round(bcast_ms, 3)
         line["bcast_bytes"] = K * N * 4
-        # B starting on rank 0 only: broadcast in two column windows, each window's product behind its arrival
-        line["from_root"] = {"ms_per_step": round(pipelined_ms, 3), "value": round(flops / (pipelined_ms * 1e-3) / 1e9, 2),
-                             "unit": "GFLOP/s", "unpipelined_ms": round(bcast_ms + ms_per_step, 3)}
+        # B starting on rank 0 only: the whole job including the broadcast
+        from_root["value"] = round(flops / (from_root["ms_per_step"] * 1e-3) / 1e9, 2)
+        line["from_root"] = from_root
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(mine, N, b_seed, b_dist)
     if rank == 0:

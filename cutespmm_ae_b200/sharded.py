@@ -60,6 +60,7 @@ class ShardedSpmm:
             mine = mine.cpu()
         self.rows = mine
         self.plan = Plan.from_csr(mine, path=path, host_only=host_only, **plan_kw)
+        self._recv = {}  # receive buffers of spmm_from_root, by (window, width, device)
 
     # ---- B already in every rank's memory --------------------------------------------------------
     def spmm(self, B, Cout=None, stream=None):
@@ -67,14 +68,18 @@ class ShardedSpmm:
         return self.plan.spmm(B, Cout, stream)
 
     # ---- B on one rank ---------------------------------------------------------------------------
-    def spmm_from_root(self, B, N: int, root: int = 0, Cout=None, *, max_windows: int = 4, min_cols: int = 32,
+    def spmm_from_root(self, B, N: int, root: int = 0, Cout=None, *, max_windows: int = 1, min_cols: int = 64,
                        product: Optional[Callable] = None, device=None):
         """Rows [r0, r1) of A @ B where B (K x N) is given on rank `root` only (None elsewhere).
 
         B is sent window-major (each column window a contiguous K x w block), all broadcasts are
         queued at once, and the product of window w is queued behind the arrival of window w only.
         Returns (C, windows): C is this rank's (r1-r0) x N block, `windows` the received K x w
-        blocks (kept so that a caller can reuse B without a second transfer).
+        blocks (kept so that a caller can reuse B without a second transfer; they are buffers of
+        this object, overwritten by the next call).  One window (the default) is a plain broadcast
+        followed by the product; more windows pay when the transfer is long against the product
+        (measured on two GPUs over NVLink it is not: 268 MB arrive in 0.47 ms, and two half-width
+        products cost more than one full-width product).
 
         `product(Bw, Cw)` computes Cw = A_rows @ Bw; default: this rank's plan on the GPU.  Tests on
         CPU ranks pass a CPU product of their own.
@@ -93,8 +98,16 @@ class ShardedSpmm:
         if Cout is None:
             Cout = torch.empty((self.r1 - self.r0, N), dtype=torch.float32, device=device)
         blocks, works = [], []
-        for c0, c1 in wins:
-            blk = B[:, c0:c1].contiguous() if self.rank == root else torch.empty((self.K, c1 - c0), dtype=torch.float32, device=device)
+        for i, (c0, c1) in enumerate(wins):
+            if self.rank == root and len(wins) == 1 and B.is_contiguous():
+                blk = B  # one window: B goes as it is
+            else:
+                key = (i, c1 - c0, str(device))
+                blk = self._recv.get(key)
+                if blk is None:
+                    blk = self._recv[key] = torch.empty((self.K, c1 - c0), dtype=torch.float32, device=device)
+                if self.rank == root:
+                    blk.copy_(B[:, c0:c1])
             blocks.append(blk)
             if self.world > 1:
                 works.append(self.dist.broadcast(blk, src=self._global_rank(root), group=self.group, async_op=True))

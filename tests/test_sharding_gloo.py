@@ -92,9 +92,12 @@ def _worker_windows(rank, world, port, out_dir):
             Cw.copy_(torch.from_numpy(oracle.spmm_csr(sh.rows.row_ptr, sh.rows.cols, sh.rows.vals, Bw.numpy(), sh.rows.M, sh.rows.K)))
 
         B = g.dense_operand(A.K, N, 91) if rank == root else None
-        C_mine, blocks = sh.spmm_from_root(B, N, root=root, product=product, device=torch.device("cpu"))
+        C_mine, blocks = sh.spmm_from_root(B, N, root=root, max_windows=4, min_cols=32, product=product, device=torch.device("cpu"))
         assert calls == [(A.K, 64), (A.K, 16)]
         assert [tuple(b.shape) for b in blocks] == calls and all(b.is_contiguous() for b in blocks)
+        C_mine = C_mine.clone()
+        C_one, one = sh.spmm_from_root(B, N, root=root, product=product, device=torch.device("cpu"))  # default: one window
+        assert len(one) == 1 and tuple(one[0].shape) == (A.K, N) and torch.equal(C_one, C_mine)
         torch.save({"r0": sh.r0, "r1": sh.r1, "C": C_mine, "B": torch.cat(blocks, dim=1)}, Path(out_dir) / f"win{rank}.pt")
         dist.barrier()
         if rank == 0:
