@@ -58,6 +58,7 @@ def _load() -> C.CDLL:
         "cutespmm_plan_create": (C.c_int, [C.POINTER(vp), C.c_uint64, C.c_uint64, vp, vp, vp, C.POINTER(Options)]),
         "cutespmm_plan_create_u32": (C.c_int, [C.POINTER(vp), C.c_uint32, C.c_uint32, vp, vp, vp, C.POINTER(Options)]),
         "cutespmm_plan_build_host": (C.c_int, [C.POINTER(vp), C.c_uint64, C.c_uint64, vp, vp, vp, C.POINTER(Options)]),
+        "cutespmm_plan_create_device": (C.c_int, [C.POINTER(vp), C.c_uint64, C.c_uint64, vp, vp, vp, C.POINTER(Options), vp]),
         "cutespmm_plan_destroy": (C.c_int, [vp]),
         "cutespmm_plan_info": (C.c_int, [vp, C.POINTER(PlanInfo)]),
         "cutespmm_plan_blocked_row_ptr": (C.c_int, [vp, vp]),
@@ -116,6 +117,28 @@ class Plan:
     def from_csr(cls, A, **kw) -> "Plan":
         """From a generators.CsrMatrix (or anything with M, K, row_ptr, cols, vals)."""
         return cls(A.M, A.K, A.row_ptr, A.cols, A.vals, **kw)
+
+    @classmethod
+    def from_device_csr(cls, M: int, K: int, row_ptr, cols, vals, *, path: int = PATH_AUTO, split_nnz: int = 0,
+                        tile_nnz: int = 0, stream=None) -> "Plan":
+        """From CSR tensors that live on the GPU (row_ptr: M+1 int32, cols: nnz int32, vals: nnz float32): the
+        nonzeros are packed on the device (cutespmm_plan_create_device); the plan runs on the row kernel."""
+        import torch
+
+        for t, dt in ((row_ptr, torch.int32), (cols, torch.int32), (vals, torch.float32)):
+            if not t.is_cuda or t.dtype != dt or not t.is_contiguous():
+                raise ValueError("row_ptr/cols must be contiguous CUDA int32 tensors, vals a contiguous CUDA float32 tensor")
+        if row_ptr.numel() != M + 1 or cols.numel() != vals.numel():
+            raise ValueError("row_ptr must have M+1 entries; cols and vals the same length")
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, 0.0, 0)
+        st = (stream or torch.cuda.current_stream(vals.device)).cuda_stream
+        _check(lib.cutespmm_plan_create_device(C.byref(self._h), M, K, row_ptr.data_ptr(), cols.data_ptr(), vals.data_ptr(),
+                                               C.byref(opts), st))
+        self.M, self.K = M, K
+        self.nnz = self.info()["nnz"]
+        return self
 
     def close(self) -> None:
         if getattr(self, "_h", None) and self._h.value and lib is not None:  # lib is None at interpreter shutdown

@@ -20,7 +20,7 @@ LIBDIR = HERE / "lib"
 # side with the default one (kernel tuning experiments); unset in normal use.
 LIB = LIBDIR / os.environ.get("CUTESPMM_LIBNAME", "libcutespmm.so")
 EXTRA = os.environ.get("CUTESPMM_DEFINES", "").split()
-SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "slab_kernel.cu", "plan.cpp", "brick_build.cpp", "slab_build.cpp", "mtx_io.cpp"]
+SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "slab_kernel.cu", "device_build.cu", "plan.cpp", "brick_build.cpp", "slab_build.cpp", "mtx_io.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",

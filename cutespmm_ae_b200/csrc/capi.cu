@@ -207,6 +207,82 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
     return CUTESPMM_OK;
 }
 
+int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint32_t *rowPtr_dev, const uint32_t *cols_dev,
+                                const float *vals_dev, const cutespmm_options_t *opts, void *stream)
+{
+    if (!plan) return fail(CUTESPMM_EINVAL, "plan is NULL");
+    *plan = nullptr;
+    if (!rowPtr_dev) return fail(CUTESPMM_EINVAL, "rowPtr is NULL");
+    if (M >= (1ull << 32) - kPanelRows || K >= (1ull << 32)) return fail(CUTESPMM_EUNSUPPORTED, "M and K must be below 2^32");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice (libcutespmm needs a CUDA device; there is no CPU path)");
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) return fail_cuda(e, "cudaGetDeviceProperties");
+    if (prop.major < 10)
+        return fail(CUTESPMM_EUNSUPPORTED, "this library is built for sm_100a (B200) only; found compute capability " +
+                                               std::to_string(prop.major) + "." + std::to_string(prop.minor));
+    // the row pointers come to the host (4 bytes per row): tiles, chunks and the fix-up list are cut from them alone
+    std::vector<uint32_t> rp;
+    try {
+        rp.resize(M + 1);
+    } catch (const std::bad_alloc &) {
+        return fail(CUTESPMM_ENOMEM, "host allocation failed");
+    }
+    if ((e = cudaMemcpyAsync(rp.data(), rowPtr_dev, (M + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(s)) != cudaSuccess)
+        return fail_cuda(e, "reading the row pointers");
+    cutespmm_plan *p = new (std::nothrow) cutespmm_plan();
+    if (!p) return fail(CUTESPMM_ENOMEM, "host allocation failed");
+    std::string err;
+    int st;
+    try {
+        st = build_rows_plan_from_row_ptr(p->host, M, K, std::move(rp), opts, err);
+    } catch (const std::bad_alloc &) {
+        st = CUTESPMM_ENOMEM;
+        err = "host allocation failed while building the plan";
+    }
+    if (st != CUTESPMM_OK) { delete p; return fail(st, err); }
+    HostPlan &h = p->host;
+    if (h.nnz && (!cols_dev || !vals_dev)) { delete p; return fail(CUTESPMM_EINVAL, "cols/vals is NULL"); }
+    p->device = dev;
+    p->sm_count = prop.multiProcessorCount;
+    p->on_device = true;
+    uint64_t &by = p->device_bytes;
+    auto bail = [&](cudaError_t ce, const char *what) { delete p; return fail_cuda(ce, what); };
+    // row pointers: device-to-device, with the slack the tile copies may read behind the end
+    if ((e = cudaMalloc(&p->d_row_ptr, (M + 1 + 8) * sizeof(uint32_t))) != cudaSuccess) return bail(e, "row pointers");
+    by += (M + 1 + 8) * sizeof(uint32_t);
+    const uint32_t tail[8] = {h.row_ptr[M], h.row_ptr[M], h.row_ptr[M], h.row_ptr[M], h.row_ptr[M], h.row_ptr[M], h.row_ptr[M], h.row_ptr[M]};
+    if ((e = cudaMemcpyAsync(p->d_row_ptr, rowPtr_dev, (M + 1) * sizeof(uint32_t), cudaMemcpyDeviceToDevice, s)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(static_cast<uint32_t *>(p->d_row_ptr) + M + 1, tail, sizeof(tail), cudaMemcpyHostToDevice, s)) != cudaSuccess)
+        return bail(e, "row pointers");
+    if ((e = cudaMalloc(&p->d_status, 256)) != cudaSuccess || (e = cudaMemsetAsync(p->d_status, 0, 256, s)) != cudaSuccess)
+        return bail(e, "status word");
+    by += 256;
+    // nonzeros: packed on the device; the second status word collects the column-range check
+    if ((e = cudaMalloc(&p->d_pairs, (h.nnz + 2) * sizeof(Pair))) != cudaSuccess) return bail(e, "packed nonzeros");
+    by += (h.nnz + 2) * sizeof(Pair);
+    if ((e = launch_pack_pairs(cols_dev, vals_dev, p->d_pairs, h.nnz, (uint32_t)K, p->d_status + 1, p->sm_count, s)) != cudaSuccess)
+        return bail(e, "packing the nonzeros");
+    if ((e = upload(h.tiles, &p->d_tiles, by)) != cudaSuccess || (e = upload(h.chunks, &p->d_chunks, by)) != cudaSuccess ||
+        (e = upload(h.long_rows, &p->d_long_rows, by)) != cudaSuccess)
+        return bail(e, "uploading the work lists");
+    const uint64_t scratch = (uint64_t)h.chunks.size() * kScratchCols * sizeof(float);
+    if (scratch) {
+        if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) return bail(e, "scratch");
+        by += scratch;
+    }
+    uint32_t bad = 0;
+    if ((e = cudaMemcpyAsync(&bad, p->d_status + 1, sizeof(bad), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+        (e = cudaStreamSynchronize(s)) != cudaSuccess)
+        return bail(e, "packing the nonzeros");
+    if (bad) { delete p; return fail(CUTESPMM_EINVAL, "column index out of range (>= K)"); }
+    *plan = p;
+    return CUTESPMM_OK;
+}
+
 int cutespmm_plan_create_u32(cutespmm_plan_t **plan, uint32_t M, uint32_t K, const uint32_t *rowPtr,
                              const uint32_t *cols, const float *vals, const cutespmm_options_t *opts)
 {
@@ -240,21 +316,39 @@ int cutespmm_plan_info(const cutespmm_plan_t *p, cutespmm_plan_info_t *info)
     return CUTESPMM_OK;
 }
 
+static const char *kNoViews = "a plan built on the device has no panel views: the column analysis runs in the host builder only";
+
 int cutespmm_plan_blocked_row_ptr(const cutespmm_plan_t *p, uint32_t *out)
 {
     if (!p || !out) return fail(CUTESPMM_EINVAL, "null argument");
+    if (p->host.device_built) return fail(CUTESPMM_EUNSUPPORTED, kNoViews);
     std::memcpy(out, p->host.blocked_row_ptr.data(), p->host.blocked_row_ptr.size() * sizeof(uint32_t));
     return CUTESPMM_OK;
 }
 int cutespmm_plan_active_cols(const cutespmm_plan_t *p, uint32_t *out)
 {
     if (!p || !out) return fail(CUTESPMM_EINVAL, "null argument");
+    if (p->host.device_built) return fail(CUTESPMM_EUNSUPPORTED, kNoViews);
     std::memcpy(out, p->host.active_cols.data(), p->host.active_cols.size() * sizeof(uint32_t));
     return CUTESPMM_OK;
 }
 int cutespmm_plan_decode_csr(const cutespmm_plan_t *p, uint64_t *rowPtr, uint32_t *cols, float *vals)
 {
     if (!p || !rowPtr || (p->host.nnz && (!cols || !vals))) return fail(CUTESPMM_EINVAL, "null argument");
+    if (p->host.device_built) {  // the pairs live on the device only, in CSR order
+        const HostPlan &h = p->host;
+        for (uint64_t r = 0; r <= h.M; ++r) rowPtr[r] = h.row_ptr[r];
+        std::vector<Pair> pr(h.nnz);
+        if (h.nnz) {
+            cudaError_t e = cudaMemcpy(pr.data(), p->d_pairs, h.nnz * sizeof(Pair), cudaMemcpyDeviceToHost);
+            if (e != cudaSuccess) return fail_cuda(e, "reading the packed nonzeros back");
+        }
+        for (uint64_t j = 0; j < h.nnz; ++j) {
+            cols[j] = pr[j].col;
+            std::memcpy(&vals[j], &pr[j].val_bits, 4);
+        }
+        return CUTESPMM_OK;
+    }
     decode_host_plan(p->host, rowPtr, cols, vals);
     return CUTESPMM_OK;
 }
@@ -273,6 +367,7 @@ static RowsArgs rows_args(const cutespmm_plan *p, bool all_rows, const float *B,
     a.num_chunks = (uint32_t)(all_rows ? h.chunks_all.size() : h.chunks.size());
     a.num_long_rows = (uint32_t)(all_rows ? h.long_rows_all.size() : h.long_rows.size());
     a.split_nnz = h.opts.split_nnz;
+    a.avg_row_nnz = (uint32_t)(h.nnz / std::max<uint64_t>(h.M, 1));
     a.B = B; a.C = C; a.scratch = p->d_scratch;
     a.ldb = ldb; a.ldc = ldc; a.ld_scratch = kScratchCols;
     a.N = N;

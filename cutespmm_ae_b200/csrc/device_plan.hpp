@@ -14,6 +14,7 @@ struct RowsArgs {
     const void *chunks;        // num_chunks x {row, j0, j1, slot}
     const void *long_rows;     // num_long_rows x {row, slot0, slot1, -}
     uint32_t num_tiles, num_chunks, num_long_rows, split_nnz;
+    uint32_t avg_row_nnz;      // nonzeros per row of the whole matrix (picks the kernel's tuning)
     const float *B;            // K x N window, leading dimension ldb
     float *C;                  // M x N window, leading dimension ldc
     float *scratch;            // partial sums, leading dimension ld_scratch
@@ -67,5 +68,9 @@ struct SlabArgs {
 };
 cudaError_t launch_slab(const SlabArgs &a, int sm_count, cudaStream_t s);
 bool slab_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const void *C);
+
+// pairs[j] = (cols[j], bits of vals[j]) for j < nnz, two zero pairs behind; *bad |= 1 when a column is >= K
+cudaError_t launch_pack_pairs(const uint32_t *cols, const float *vals, void *pairs, uint64_t nnz, uint32_t K, uint32_t *bad, int sm_count,
+                              cudaStream_t s);
 
 }  // namespace cutespmm

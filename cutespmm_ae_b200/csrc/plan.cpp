@@ -137,6 +137,31 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
     }
 }
 
+int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vector<uint32_t> &&row_ptr,
+                                 const cutespmm_options_t *opts, std::string &err)
+{
+    if (M >= (1ull << 32) - kPanelRows || K >= (1ull << 32)) { err = "M and K must be below 2^32"; return CUTESPMM_EUNSUPPORTED; }
+    if (row_ptr.size() != M + 1) { err = "rowPtr must have M+1 entries"; return CUTESPMM_EINVAL; }
+    if (row_ptr[0] != 0) { err = "rowPtr[0] must be 0"; return CUTESPMM_EINVAL; }
+    if (opts && opts->path != CUTESPMM_PATH_AUTO && opts->path != CUTESPMM_PATH_ROWS) {
+        err = "a plan built on the device runs on the row kernel only (path auto or rows)";
+        return CUTESPMM_EUNSUPPORTED;
+    }
+    fill_default_options(p.opts, opts);
+    p.opts.path = CUTESPMM_PATH_ROWS;
+    int bad = 0;
+#pragma omp parallel for schedule(static) reduction(| : bad)
+    for (int64_t r = 0; r < (int64_t)M; ++r) bad |= row_ptr[r + 1] < row_ptr[r];
+    if (bad) { err = "rowPtr is not non-decreasing"; return CUTESPMM_EINVAL; }
+    p.M = M; p.K = K; p.nnz = row_ptr[M];
+    p.row_ptr = std::move(row_ptr);
+    p.device_built = true;
+    p.row_path.assign(p.num_panels(), 0);
+    p.slab_path.assign((M + kSlabRows - 1) / kSlabRows, 0);
+    build_tiles(p, false, p.tiles, p.chunks, p.long_rows);
+    return CUTESPMM_OK;
+}
+
 int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
                     const float *vals, const cutespmm_options_t *opts, std::string &err)
 {

@@ -71,6 +71,7 @@ constexpr uint32_t kSlabRecMaxWords = kSlabRecHeaderWords + kSlabMaxRows + kSlab
 struct HostPlan {
     uint64_t M = 0, K = 0, nnz = 0;
     cutespmm_options_t opts{};
+    bool device_built = false;  // the nonzeros were packed on the device; the host holds row pointers and work lists only
 
     // ---- row kernel ----
     std::vector<uint32_t> row_ptr;       // M+1, offsets into pairs
@@ -123,6 +124,12 @@ struct HostPlan {
 // on failure `err` holds the message.
 int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
                     const float *vals, const cutespmm_options_t *opts, std::string &err);
+
+// The row-kernel part of a plan from the row pointers alone (tiles, chunks of long rows, fix-up list): what a plan
+// needs on the host when the nonzeros themselves stay on the device.  p.pairs stays empty and p.device_built is
+// set: the HRPB views and the host-side decode are not available for such a plan.
+int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vector<uint32_t> &&row_ptr,
+                                 const cutespmm_options_t *opts, std::string &err);
 
 // Rebuilds CSR from the packed arrays (rows-kernel part from pairs, brick part from maps + values).
 void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float *vals);

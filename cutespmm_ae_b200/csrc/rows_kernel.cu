@@ -24,11 +24,11 @@ namespace cutespmm {
 
 namespace {
 
-// Two tunings of the row kernel, chosen per launch (measured on R-MAT 2^20 and the 512x512 stencil at N = 128):
+// Two tunings of the row kernel, chosen per launch (measured on R-MAT graphs and the 512x512 stencil at N = 128):
 //   DEEP = false  4 rows of B in flight per warp, 6 blocks (48 warps) per SM: more warps hide the gather latency
-//                 better than more loads per warp once the grid is several waves of tiles long;
-//   DEEP = true   8 rows in flight, 4 blocks per SM: fewer dependent steps per row, better when the whole job
-//                 is a single wave of tiles and the time is a handful of latencies.
+//                 better than more loads per warp when rows are short and the grid is several waves of tiles long;
+//   DEEP = true   8 rows in flight, 4 blocks per SM: fewer dependent steps per row, better for long rows and when
+//                 the whole job is a single wave of tiles and the time is a handful of latencies.
 #ifndef ROWS_SHALLOW_BLOCKS
 #define ROWS_SHALLOW_BLOCKS 6
 #endif
@@ -312,7 +312,10 @@ cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s)
     const bool v4 = !((pb | pc | ps) & 15) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 3);
     const bool v2 = !((pb | pc | ps) & 7) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 1);
     const uint32_t N = a.N;
-    const bool deep = (uint64_t)a.num_tiles <= (uint64_t)sm_count * 6;  // at most one resident wave of tiles
+    // deep: at most one resident wave of tiles, or long rows (measured on shards of R-MAT 2^24: 300 nonzeros per row
+    // 2.19 vs 2.38 ms, 21 per row 1.88 vs 1.93 ms in favour of deep; 15 per row (R-MAT 2^20) 0.645 vs 0.611 ms and
+    // 3.4 per row 1.50 vs 1.48 ms in favour of shallow)
+    const bool deep = (uint64_t)a.num_tiles <= (uint64_t)sm_count * 6 || a.avg_row_nnz >= 20;
 #define CUTESPMM_GO(VEC, CH)                                                                   \
     do {                                                                                       \
         const uint32_t w = 32 * VEC * CH, slabs = (N + w - 1) / w;                             \

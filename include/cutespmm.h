@@ -107,6 +107,18 @@ int cutespmm_plan_create_u32(cutespmm_plan_t **plan, uint32_t M, uint32_t K, con
 int cutespmm_plan_build_host(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint64_t *rowPtr,
                              const uint32_t *cols, const float *vals, const cutespmm_options_t *opts);
 
+/* A plan for a matrix that already lives on the device (rowPtr: M+1 x u32, cols: nnz x u32, vals: nnz x f32, all
+ * device pointers): the nonzeros are packed by a kernel and never visit the host; only the row pointers do, because
+ * the work lists are cut from them.  The reference preprocesses on the host only (data.cu:80-335) and its caller
+ * uploads the result (data.cu:318-333); this is the entry point for a caller that has no host copy.  The plan runs
+ * on the row kernel (opts->path auto or rows; brick and slab need the host builder's column analysis and are refused
+ * with CUTESPMM_EUNSUPPORTED); rows need not be sorted.  The panel views (blocked_row_ptr, active_cols) are not
+ * available for such a plan; plan_decode_csr reads the packed nonzeros back.  Work is queued on `stream`, which is
+ * synchronised before the call returns (the column-range check is read back). */
+int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint32_t *rowPtr_dev,
+                                const uint32_t *cols_dev, const float *vals_dev, const cutespmm_options_t *opts,
+                                void *stream);
+
 int cutespmm_plan_destroy(cutespmm_plan_t *plan);
 int cutespmm_plan_info(const cutespmm_plan_t *plan, cutespmm_plan_info_t *info);
 
