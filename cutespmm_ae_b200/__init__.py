@@ -235,7 +235,7 @@ def spmm_csr_noalloc(M: int, K: int, row_ptr, cols, vals, B, Cout, stream=None):
     return Cout
 
 
-def partition_rows(row_ptr, nparts: int, align_rows: int = 16, row_cost: int = 4) -> np.ndarray:
+def partition_rows(row_ptr, nparts: int, align_rows: int = 16, row_cost: int = 2) -> np.ndarray:
     """nnz-balanced contiguous row ranges, boundaries multiples of `align_rows`; returns nparts+1 bounds."""
     rp = _np(row_ptr, np.uint64)
     out = np.empty(nparts + 1, dtype=np.uint64)

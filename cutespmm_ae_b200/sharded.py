@@ -42,9 +42,14 @@ class ShardedSpmm:
     rank passes the same matrix (or its own way of producing the same rows).  `group` is a
     torch.distributed process group (None: the default group; a single process works without one).
     `host_only=True` builds the plan without touching CUDA (tests of the host logic on CPU ranks).
+    `row_cost`: what a row costs in units of one nonzero when the rows are cut into ranges of equal cost.  At
+    N = 128 a row is one 512-byte store of C plus the claim of the row, a nonzero one 512-byte gather; measured on
+    the eight shards of R-MAT 2^24, 2 balances them within 9 % (1.83 .. 2.00 ms), 4 leaves the hub-heavy shard at
+    2.18 ms and 1 the many-rows shard at 2.12 ms.
     """
 
-    def __init__(self, A, group=None, *, path: int = PATH_AUTO, host_only: bool = False, align_rows: int = 16, **plan_kw):
+    def __init__(self, A, group=None, *, path: int = PATH_AUTO, host_only: bool = False, align_rows: int = 16, row_cost: int = 2,
+                 **plan_kw):
         import torch.distributed as dist
 
         self.group = group
@@ -53,7 +58,7 @@ class ShardedSpmm:
         self.rank = self.dist.get_rank(group) if self.dist else 0
         self.M, self.K = A.M, A.K
         rp = A.row_ptr.cpu() if hasattr(A.row_ptr, "cpu") else A.row_ptr
-        self.bounds = partition_rows(rp, self.world, align_rows=align_rows) if self.world > 1 else np.array([0, A.M], dtype=np.uint64)
+        self.bounds = partition_rows(rp, self.world, align_rows=align_rows, row_cost=row_cost) if self.world > 1 else np.array([0, A.M], dtype=np.uint64)
         self.r0, self.r1 = int(self.bounds[self.rank]), int(self.bounds[self.rank + 1])
         mine = A.row_slice(self.r0, self.r1) if self.world > 1 else A
         if hasattr(mine, "cpu"):
