@@ -23,56 +23,61 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
     p.num_bricks = 0;
     p.brick_panels = 0;
     const uint64_t P = p.num_panels();
-    uint64_t acol_off = 0;
-    std::vector<float> img;
-    std::vector<uint8_t> present;
+    // pass 1: which panels, how many slots each (records have a fixed size, so every offset follows from the counts)
+    std::vector<uint64_t> acol_off(P + 1, 0);
+    std::vector<uint32_t> which;  // panels routed to the brick kernel, ascending
     for (uint64_t q = 0; q < P; ++q) {
+        acol_off[q + 1] = acol_off[q] + (uint64_t)((panel_ncols[q] + kBlockCols - 1) / kBlockCols) * kBlockCols;
+        if (p.row_path[q] == 1 && panel_ncols[q] != 0) which.push_back((uint32_t)q);
+    }
+    p.brick_panels = which.size();
+    p.panel_first_brick.resize(which.size());
+    p.panel_last_brick.resize(which.size());
+    uint64_t slots = 0;
+    for (size_t i = 0; i < which.size(); ++i) {
+        const uint32_t nbricks = (panel_ncols[which[i]] + kBrickCols - 1) / kBrickCols;
+        p.panel_first_brick[i] = (uint32_t)slots;  // a multiple of 4
+        p.panel_last_brick[i] = (uint32_t)(slots + nbricks);
+        p.num_bricks += nbricks;
+        slots += (nbricks + 3) / 4 * 4;  // groups of 4 slots start on a panel boundary; the surplus slots stay empty
+    }
+    p.brick_cols.assign(slots * kBrickCols, 0u);
+    p.brick_recs.assign(slots * kBrickRecWords, 0u);  // empty slots: zero records
+    p.brick_rec_off.resize(slots + 1);
+    for (uint64_t k = 0; k <= slots; ++k) p.brick_rec_off[k] = (uint32_t)(k * (kBrickRecWords / 4));
+    // pass 2: every panel writes its own slots
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t i = 0; i < (int64_t)which.size(); ++i) {
+        const uint64_t q = which[i];
         const uint32_t nc = panel_ncols[q];
-        const uint64_t my_off = acol_off;
-        acol_off += (uint64_t)((nc + kBlockCols - 1) / kBlockCols) * kBlockCols;
-        if (p.row_path[q] != 1 || nc == 0) continue;
-        ++p.brick_panels;
-        p.panel_first_brick.push_back((uint32_t)p.brick_rec_off.size());  // slot index, a multiple of 4
-        const uint32_t *acols = &p.active_cols[my_off];
+        const uint32_t *acols = &p.active_cols[acol_off[q]];
         const uint64_t r0 = q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
-        const uint32_t nbricks = (nc + kBrickCols - 1) / kBrickCols;
-        const uint32_t nslots = (nbricks + 3) / 4 * 4;  // the panel's brick slots: groups of 4 start on a panel boundary
-        for (uint32_t c = 0; c < nslots * kBrickCols; ++c) p.brick_cols.push_back(acols[std::min(c, nc - 1)]);
-        img.assign((size_t)nbricks * 128, 0.0f);
-        present.assign((size_t)nbricks * 128, 0);
+        const uint32_t first = p.panel_first_brick[i], nbricks = p.panel_last_brick[i] - first;
+        const uint32_t nslots = (nbricks + 3) / 4 * 4;
+        for (uint32_t c = 0; c < nslots * kBrickCols; ++c) p.brick_cols[(size_t)first * kBrickCols + c] = acols[std::min(c, nc - 1)];
+        for (uint32_t b = 0; b < nbricks; ++b) {
+            uint32_t *rec = &p.brick_recs[(size_t)(first + b) * kBrickRecWords];
+            rec[4] = b + 1 == nbricks ? 1u : 0u;
+            rec[5] = (uint32_t)q;
+        }
         for (uint64_t r = r0; r < r1; ++r) {
             const uint32_t *cursor = acols;
             for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; ++j) {
                 const uint32_t col = p.pairs[j].col;  // ascending inside the row
                 cursor = std::lower_bound(cursor, acols + nc, col);
                 const uint32_t lc = (uint32_t)(cursor - acols);
-                float v;
+                uint32_t *rec = &p.brick_recs[(size_t)(first + lc / kBrickCols) * kBrickRecWords];
+                const uint32_t bit = (uint32_t)(r - r0) * kBrickCols + lc % kBrickCols;
+                float v, acc;
                 std::memcpy(&v, &p.pairs[j].val_bits, 4);
-                const size_t at = (size_t)(lc / kBrickCols) * 128 + (r - r0) * kBrickCols + lc % kBrickCols;
-                img[at] += v;  // duplicates of one (row, column) merge here
-                present[at] = 1;
+                uint32_t *slot = &rec[kBrickRecHeaderWords + brick_frag_index(bit / kBrickCols, bit % kBrickCols)];
+                std::memcpy(&acc, slot, 4);
+                acc = (rec[bit >> 5] >> (bit & 31)) & 1u ? acc + v : v;  // duplicates of one (row, column) merge here
+                std::memcpy(slot, &acc, 4);
+                rec[bit >> 5] |= 1u << (bit & 31);
             }
         }
-        for (uint32_t b = 0; b < nbricks; ++b) {
-            p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));
-            uint32_t head[kBrickRecHeaderWords] = {0, 0, 0, 0, b + 1 == nbricks ? 1u : 0u, (uint32_t)q, 0, 0};
-            for (uint32_t bit = 0; bit < 128; ++bit)
-                if (present[(size_t)b * 128 + bit]) head[bit >> 5] |= 1u << (bit & 31);
-            p.brick_recs.insert(p.brick_recs.end(), head, head + kBrickRecHeaderWords);
-            const size_t base = p.brick_recs.size();
-            p.brick_recs.resize(base + 128, 0u);
-            for (uint32_t bit = 0; bit < 128; ++bit)
-                if (present[(size_t)b * 128 + bit])
-                    std::memcpy(&p.brick_recs[base + brick_frag_index(bit / kBrickCols, bit % kBrickCols)], &img[(size_t)b * 128 + bit], 4);
-            ++p.num_bricks;
-        }
-        for (uint32_t b = nbricks; b < nslots; ++b) {  // empty slots
-            p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));
-            p.brick_recs.resize(p.brick_recs.size() + kBrickRecWords, 0u);
-        }
-        p.panel_last_brick.push_back((uint32_t)(p.brick_rec_off.size() - (nslots - nbricks)));
     }
-    p.brick_rec_off.push_back((uint32_t)(p.brick_recs.size() / 4));
 }
 
 }  // namespace cutespmm
