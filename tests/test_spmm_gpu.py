@@ -172,12 +172,13 @@ def test_execution_errors_are_status_codes():
     assert cs.lib.cutespmm_spmm(p._h, B.data_ptr() + 2, 16, B.data_ptr(), 16, 16, None) == -1  # misaligned
 
 
-def test_full_size_properties_without_cpu_product():
+def test_full_size_properties_without_cpu_product(oracle_mod):
     """At the size where the CPU product takes too long: linearity in B and the column-sum identity
-    1^T (A B) = (A^T 1)^T B, both checked on the device in fp64."""
+    1^T (A B) = (A^T 1)^T B, both checked on the device in fp64, and a sample of rows (2^16 random rows plus every
+    row with more than 4096 nonzeros) against the CPU oracle.  The plan is built from the device-resident CSR."""
     A = g.rmat(22, 8, seed=1005, values="uniform", device="cuda")
     N = 128
-    p = cs.Plan.from_csr(A)
+    p = cs.Plan.from_device_csr(A.M, A.K, A.row_ptr.to(torch.int32), A.cols.to(torch.int32), A.vals)
     B1 = g.dense_operand(A.K, N, 81, device="cuda")
     B2 = g.dense_operand(A.K, N, 82, device="cuda")
     C1, C2, C12 = p.spmm(B1), p.spmm(B2), p.spmm(B1 + B2)
@@ -189,3 +190,8 @@ def test_full_size_properties_without_cpu_product():
     expect = colsum @ B1.double()
     got = C1.double().sum(0)
     assert float((got - expect).norm() / expect.norm()) < 1e-5
+    deg = (A.row_ptr[1:] - A.row_ptr[:-1]).cpu()
+    gen = torch.Generator().manual_seed(7)
+    which = torch.unique(torch.cat([torch.randint(0, A.M, (1 << 16,), generator=gen), torch.nonzero(deg > 4096).flatten()]))
+    want = oracle_mod.spmm_csr_rows(A.row_ptr.cpu(), A.cols.cpu(), A.vals.cpu(), B1.cpu().numpy(), which.numpy())
+    assert oracle_mod.rel_fro(want, C1[which.cuda()].cpu().numpy()) <= REL_FRO_TOL_FP32
