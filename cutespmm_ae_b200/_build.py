@@ -16,12 +16,19 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBDIR = HERE / "lib"
-# CUTESPMM_LIBNAME / CUTESPMM_DEFINES: build and load an alternative variant of the library side by
-# side with the default one (kernel tuning experiments); unset in normal use.
-LIB = LIBDIR / os.environ.get("CUTESPMM_LIBNAME", "libcutespmm.so")
-EXTRA = os.environ.get("CUTESPMM_DEFINES", "").split()
+LIB = LIBDIR / "libcutespmm.so"
 SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "slab_kernel.cu", "device_build.cu", "plan.cpp", "brick_build.cpp", "slab_build.cpp", "mtx_io.cpp"]
-NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+def _find_nvcc() -> str:
+    import shutil
+
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    return "nvcc"
+
+
+NVCC = _find_nvcc()
+CUDA_HOME = Path(os.environ.get("CUDA_HOME") or Path(NVCC).resolve().parent.parent)  # headers and libcudart for C++ hosts
 FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -40,7 +47,7 @@ def _stamp() -> str:
         if f.is_file():
             h.update(f.name.encode())
             h.update(f.read_bytes())
-    h.update(" ".join(FLAGS + EXTRA).encode())
+    h.update(" ".join(FLAGS).encode())
     return h.hexdigest()
 
 
@@ -56,7 +63,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     stamp = _stamp()
     if not force and LIB.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
         return LIB
-    cmd = [NVCC, *FLAGS, *EXTRA, "-o", str(LIB), *map(str, _sources())]
+    cmd = [NVCC, *FLAGS, "-o", str(LIB), *map(str, _sources())]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

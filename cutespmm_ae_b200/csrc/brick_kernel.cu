@@ -38,10 +38,7 @@ namespace cutespmm {
 
 namespace {
 
-#ifndef BRICK_STAGES
-#define BRICK_STAGES 3
-#endif
-constexpr int kStages = BRICK_STAGES;
+constexpr int kStages = 3;
 constexpr int kRecWords = kBrickRecWords;  // header + a full brick of values
 
 template <int NT> struct StageLayout {
@@ -205,18 +202,14 @@ template <int NT, bool ROUND_B> cudaError_t launch_brick_t(const BrickArgs &a, i
 {
     using L = StageLayout<NT>;
     constexpr int smem = kBrickWarps * L::kWarpBytes;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(spmm_brick_kernel<NT, ROUND_B>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    cudaError_t e = allow_dynamic_smem<spmm_brick_kernel<NT, ROUND_B>>(smem);
+    if (e != cudaSuccess) return e;
     const uint32_t slabs = a.N / L::kSlab;
     uint32_t blocks = (a.num_panels + kBrickWarps - 1) / kBrickWarps;
     if (blocks > (uint32_t)sm_count) blocks = (uint32_t)sm_count;  // one resident block per SM, persistent
     // B as a 2-D tensor; the box is the slab plus the 8 columns of padding that give the shared-memory stride
     CUtensorMap tmap;
-    cudaError_t e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, L::kStride, CU_TENSOR_MAP_SWIZZLE_NONE);
+    e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, L::kStride, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (e != cudaSuccess) return e;
     spmm_brick_kernel<NT, ROUND_B><<<dim3(blocks, slabs), kBrickWarps * 32, smem, s>>>(tmap, a);
     return cudaGetLastError();

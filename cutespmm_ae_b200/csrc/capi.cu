@@ -451,6 +451,10 @@ int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float 
     if ((reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 3) return fail(CUTESPMM_EINVAL, "B and C must be 4-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (p->host.M == 0) return CUTESPMM_OK;
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != p->device)
+        return fail(CUTESPMM_EINVAL, "the current CUDA device (" + std::to_string(cur) + ") is not the one the plan was created on (" +
+                                         std::to_string(p->device) + "): call cudaSetDevice first");
     for (uint32_t n0 = 0; n0 < N; n0 += kScratchCols) {
         const uint32_t nw = N - n0 < kScratchCols ? N - n0 : kScratchCols;
         cudaError_t e;
@@ -568,6 +572,8 @@ int cutespmm_plan_device_status(const cutespmm_plan_t *p, uint32_t *status)
     if (!p->on_device) return CUTESPMM_OK;
     cudaError_t e = cudaMemcpy(status, p->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail_cuda(e, "reading the status word");
+    // clear on read: a reported timeout does not stick to the launches that follow
+    if (*status && (e = cudaMemset(p->d_status, 0, sizeof(uint32_t))) != cudaSuccess) return fail_cuda(e, "clearing the status word");
     return CUTESPMM_OK;
 }
 

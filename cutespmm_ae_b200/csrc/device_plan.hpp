@@ -6,6 +6,23 @@
 
 namespace cutespmm {
 
+// Opts a kernel in to more than 48 KB of dynamic shared memory.  The attribute belongs to the (function, device)
+// pair, so it is set once per device ordinal: a process that drives several GPUs configures each of them.
+// (The kernel is a template argument, not a function argument: the table below must be one per kernel, and two
+// instantiations of a kernel template share a function-pointer type.)
+template <auto Kernel> cudaError_t allow_dynamic_smem(int bytes)
+{
+    constexpr int kMaxDevices = 64;
+    static bool done[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < kMaxDevices && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < kMaxDevices) done[dev] = true;
+    return e;
+}
+
 // Arguments of the row-gather kernel and of the fix-up kernel that follows it.
 struct RowsArgs {
     const uint32_t *row_ptr;   // M+1 offsets into pairs
@@ -28,10 +45,7 @@ cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
 int rows_kernel_count(const RowsArgs &a);
 
 // Arguments of the tensor-core brick kernel.
-#ifndef BRICK_WARPS
-#define BRICK_WARPS 15
-#endif
-constexpr int kBrickWarps = BRICK_WARPS;  // warps per block; each is an independent pipeline over its own brick range
+constexpr int kBrickWarps = 15;  // warps per block; each is an independent pipeline over its own brick range
 struct BrickArgs {
     const uint32_t *cols;         // 8 columns per brick slot (+ readable slack of a few groups behind the end)
     const uint32_t *recs;         // brick records (map, flags, panel, values in fragment order): slot k at word k * kBrickRecWords

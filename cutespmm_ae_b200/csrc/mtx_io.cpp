@@ -20,30 +20,56 @@ struct cutespmm_mtx {
     std::vector<float> vals;
 };
 
+namespace cutespmm {
+void set_last_error(const std::string &msg);  // capi.cu
+}
+
 namespace {
-thread_local std::string g_mtx_error;
 struct Entry {
     uint32_t r, c;
     float v;
 };
+
+int fail(int status, const std::string &path, const std::string &what)
+{
+    cutespmm::set_last_error("MatrixMarket file " + path + ": " + what);
+    return status;
+}
+
+// Parses an unsigned decimal that must start (after blanks) before `line_end`; never reads into the next line.
+bool parse_uint(const char *&p, const char *line_end, unsigned long &out)
+{
+    while (p < line_end && (*p == ' ' || *p == '\t')) ++p;
+    if (p >= line_end || *p < '0' || *p > '9') return false;
+    unsigned long v = 0;
+    while (p < line_end && *p >= '0' && *p <= '9') {
+        if (v > (~0ul - 9) / 10) return false;
+        v = v * 10 + (unsigned long)(*p++ - '0');
+    }
+    out = v;
+    return true;
+}
 }  // namespace
 
 extern "C" {
 
 int cutespmm_mtx_open(cutespmm_mtx_t **out, const char *path, int pattern_only)
 {
-    if (!out || !path) return CUTESPMM_EINVAL;
+    if (!out || !path) {
+        cutespmm::set_last_error("cutespmm_mtx_open: null argument");
+        return CUTESPMM_EINVAL;
+    }
     *out = nullptr;
     FILE *f = std::fopen(path, "rb");
-    if (!f) return CUTESPMM_EIO;
+    if (!f) return fail(CUTESPMM_EIO, path, std::string("cannot open: ") + std::strerror(errno));
     std::fseek(f, 0, SEEK_END);
     const long size = std::ftell(f);
     std::fseek(f, 0, SEEK_SET);
-    if (size <= 0) { std::fclose(f); return CUTESPMM_EIO; }
+    if (size <= 0) { std::fclose(f); return fail(CUTESPMM_EIO, path, "empty or unreadable"); }
     std::string buf((size_t)size, '\0');
     const size_t got = std::fread(&buf[0], 1, (size_t)size, f);
     std::fclose(f);
-    if (got != (size_t)size) return CUTESPMM_EIO;
+    if (got != (size_t)size) return fail(CUTESPMM_EIO, path, "short read");
 
     const char *p = buf.c_str(), *end = p + buf.size();
     auto next_line = [&](const char *q) { while (q < end && *q != '\n') ++q; return q < end ? q + 1 : end; };
@@ -51,26 +77,40 @@ int cutespmm_mtx_open(cutespmm_mtx_t **out, const char *path, int pattern_only)
     const char *l1 = next_line(p);
     const bool symmetric = std::string(p, l1).find("symmetric") != std::string::npos;
     p = l1;
-    while (p < end && *p == '%') p = next_line(p);
-    if (p >= end) return CUTESPMM_EIO;
-    char *q = nullptr;
-    const unsigned long m0 = std::strtoul(p, &q, 10);
-    const unsigned long k0 = std::strtoul(q, &q, 10);
-    if (m0 == 0 || k0 == 0 || m0 >= (1ul << 32) - 16 || k0 >= (1ul << 32) - 16) return CUTESPMM_EIO;
-    p = next_line(q);
+    size_t line_no = 2;
+    while (p < end && *p == '%') { p = next_line(p); ++line_no; }
+    if (p >= end) return fail(CUTESPMM_EIO, path, "no size line");
+    unsigned long m0 = 0, k0 = 0;
+    {
+        const char *size_end = next_line(p), *q = p;
+        if (!parse_uint(q, size_end, m0) || !parse_uint(q, size_end, k0) || m0 == 0 || k0 == 0 || m0 >= (1ul << 32) - 16 ||
+            k0 >= (1ul << 32) - 16)
+            return fail(CUTESPMM_EIO, path, "bad size line (line " + std::to_string(line_no) + ")");
+        p = size_end;
+    }
 
     cutespmm_mtx *m = new (std::nothrow) cutespmm_mtx();
-    if (!m) return CUTESPMM_ENOMEM;
+    if (!m) return fail(CUTESPMM_ENOMEM, path, "host allocation failed");
     m->M = (uint32_t)((m0 - 1) / 16 + 1) * 16;
     m->K = (uint32_t)((k0 - 1) / 16 + 1) * 16;
     std::vector<Entry> ents;
     while (p < end) {
         const char *line_end = next_line(p);
+        ++line_no;
         while (p < line_end && (*p == ' ' || *p == '\t' || *p == '\r')) ++p;
         if (p >= line_end || *p == '\n' || *p == '%') { p = line_end; continue; }
-        const unsigned long r = std::strtoul(p, &q, 10);
-        const unsigned long c = std::strtoul(q, &q, 10);
-        if (r == 0 || c == 0 || r > m0 || c > k0) { delete m; return CUTESPMM_EIO; }
+        unsigned long r = 0, c = 0;
+        const char *q = p;
+        if (!parse_uint(q, line_end, r) || !parse_uint(q, line_end, c)) {
+            delete m;
+            return fail(CUTESPMM_EIO, path, "line " + std::to_string(line_no) + ": expected a row and a column index");
+        }
+        // a mirrored entry (c, r) must lie inside the declared matrix too
+        if (r == 0 || c == 0 || r > m0 || c > k0 || (symmetric && (c > m0 || r > k0))) {
+            delete m;
+            return fail(CUTESPMM_EIO, path, "line " + std::to_string(line_no) + ": index outside the " + std::to_string(m0) + " x " +
+                                                std::to_string(k0) + " matrix" + (symmetric ? " (or its mirror image is)" : ""));
+        }
         float v = 1.0f;
         if (!pattern_only) {
             const char *t = q;

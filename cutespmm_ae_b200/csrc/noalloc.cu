@@ -50,10 +50,25 @@ __device__ __forceinline__ uint64_t chunk_slot(uint32_t start, bool first_of_row
     return 2ull * (start / kSplit) + (first_of_row ? 1u : 0u);
 }
 
-// acc[i] += sum over nonzeros [j0, j1) of vals[j] * B[cols[j]][n0 + lane + 32 i]
+// Nonzero positions [j0, j1) of row r, forced into [0, nnz] and into order: every position the kernels derive a
+// scratch slot or an array index from is then below the `nnz` the host sized its checks with, whatever rowPtr holds.
+struct Range {
+    uint32_t j0, j1;
+};
+__device__ __forceinline__ Range row_range(const uint32_t *__restrict__ rowPtr, uint64_t r, uint32_t nnz)
+{
+    Range g;
+    g.j0 = min(__ldg(rowPtr + r), nnz);
+    g.j1 = min(max(__ldg(rowPtr + r + 1), g.j0), nnz);
+    return g;
+}
+
+// acc[i] += sum over nonzeros [j0, j1) of vals[j] * B[cols[j]][n0 + lane + 32 i].  A nonzero whose column is not
+// below K is left out (B has no such row); the call cannot report it without reading something back.
 __device__ __forceinline__ void accumulate(float (&acc)[4], const uint32_t *__restrict__ cols,
                                            const float *__restrict__ vals, uint32_t j0, uint32_t j1,
-                                           const float *__restrict__ B, uint64_t ldb, uint32_t n0, uint32_t N, int lane)
+                                           const float *__restrict__ B, uint64_t ldb, uint32_t n0, uint32_t N, uint32_t K,
+                                           int lane)
 {
     for (uint32_t j = j0; j < j1; j += 32) {
         const uint32_t n = min(32u, j1 - j);
@@ -66,6 +81,7 @@ __device__ __forceinline__ void accumulate(float (&acc)[4], const uint32_t *__re
         for (uint32_t k = 0; k < n; ++k) {
             const uint32_t ck = __shfl_sync(kFull, c, k);
             const float vk = __shfl_sync(kFull, v, k);
+            if (ck >= K) continue;  // uniform across the warp
             const float *row = B + (uint64_t)ck * ldb + n0 + lane;
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -78,6 +94,7 @@ __device__ __forceinline__ void accumulate(float (&acc)[4], const uint32_t *__re
 __global__ void __launch_bounds__(kWarps * 32) noalloc_rows_kernel(const uint32_t *__restrict__ rowPtr,
                                                                    const uint32_t *__restrict__ cols,
                                                                    const float *__restrict__ vals, uint32_t M,
+                                                                   uint32_t K, uint32_t nnz,
                                                                    const float *__restrict__ B, uint64_t ldb,
                                                                    float *__restrict__ C, uint64_t ldc, uint32_t N)
 {
@@ -85,10 +102,11 @@ __global__ void __launch_bounds__(kWarps * 32) noalloc_rows_kernel(const uint32_
     const uint32_t n0 = blockIdx.y * kSlab;
     const uint64_t nw = (uint64_t)gridDim.x * kWarps;
     for (uint64_t r = (uint64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < M; r += nw) {
-        const uint32_t j0 = __ldg(rowPtr + r), j1 = __ldg(rowPtr + r + 1);
+        const Range rg = row_range(rowPtr, r, nnz);
+        const uint32_t j0 = rg.j0, j1 = rg.j1;
         if (j1 - j0 > kSplit) continue;  // written by the fix-up kernel
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        accumulate(acc, cols, vals, j0, j1, B, ldb, n0, N, lane);
+        accumulate(acc, cols, vals, j0, j1, B, ldb, n0, N, K, lane);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
             if (n0 + lane + 32 * i < N) C[r * ldc + n0 + lane + 32 * i] = acc[i];
@@ -101,7 +119,7 @@ __global__ void __launch_bounds__(kWarps * 32) noalloc_rows_kernel(const uint32_
 __global__ void __launch_bounds__(kWarps * 32) noalloc_chunks_kernel(const uint32_t *__restrict__ rowPtr,
                                                                      const uint32_t *__restrict__ cols,
                                                                      const float *__restrict__ vals, uint32_t M,
-                                                                     uint32_t nnz, const float *__restrict__ B,
+                                                                     uint32_t K, uint32_t nnz, const float *__restrict__ B,
                                                                      uint64_t ldb, float *__restrict__ scratch,
                                                                      uint32_t lds, uint32_t N)
 {
@@ -118,7 +136,8 @@ __global__ void __launch_bounds__(kWarps * 32) noalloc_chunks_kernel(const uint3
             if (__ldg(rowPtr + mid) <= p0) lo = mid; else hi = mid;
         }
         for (uint32_t r = lo; r < M; ++r) {
-            const uint32_t j0 = __ldg(rowPtr + r), j1 = __ldg(rowPtr + r + 1);
+            const Range rg = row_range(rowPtr, r, nnz);
+            const uint32_t j0 = rg.j0, j1 = rg.j1;
             if (j0 >= p1) break;
             if (j1 - j0 <= kSplit) continue;
             // chunk starts of row r are j0, j0 + kSplit, ...; the one (if any) inside [p0, p1)
@@ -126,7 +145,7 @@ __global__ void __launch_bounds__(kWarps * 32) noalloc_chunks_kernel(const uint3
             const uint32_t start = j0 + i * kSplit;  // cannot wrap: start < j1 is checked before use below
             if (start < p0 || start >= p1 || start >= j1) continue;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            accumulate(acc, cols, vals, start, min(j1, start + kSplit), B, ldb, n0, N, lane);
+            accumulate(acc, cols, vals, start, min(j1, start + kSplit), B, ldb, n0, N, K, lane);
             float *out = scratch + chunk_slot(start, i == 0) * lds + n0 + lane;
 #pragma unroll
             for (int k = 0; k < 4; ++k)
@@ -137,14 +156,15 @@ __global__ void __launch_bounds__(kWarps * 32) noalloc_chunks_kernel(const uint3
 
 // C[row] of every long row = its chunks' partial sums, added in chunk order.
 __global__ void __launch_bounds__(kWarps * 32) noalloc_fixup_kernel(const uint32_t *__restrict__ rowPtr, uint32_t M,
-                                                                    const float *__restrict__ scratch, uint32_t lds,
+                                                                    uint32_t nnz, const float *__restrict__ scratch, uint32_t lds,
                                                                     float *__restrict__ C, uint64_t ldc, uint32_t N)
 {
     const int lane = threadIdx.x & 31;
     const uint32_t n0 = blockIdx.y * kSlab;
     const uint64_t nw = (uint64_t)gridDim.x * kWarps;
     for (uint64_t r = (uint64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < M; r += nw) {
-        const uint32_t j0 = __ldg(rowPtr + r), j1 = __ldg(rowPtr + r + 1);
+        const Range rg = row_range(rowPtr, r, nnz);
+        const uint32_t j0 = rg.j0, j1 = rg.j1;
         if (j1 - j0 <= kSplit) continue;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (uint32_t start = j0, i = 0; start < j1; start += kSplit, ++i) {
@@ -181,7 +201,6 @@ extern "C" int cutespmm_spmm_csr_noalloc(uint32_t M, uint32_t K, uint32_t nnz, c
                                          const uint32_t *cols_dev, const float *vals_dev, const float *B_dev,
                                          uint64_t ldb, float *C_dev, uint64_t ldc, uint32_t N, void *stream)
 {
-    (void)K;
     if (N == 0 || M == 0) return CUTESPMM_OK;
     if (!rowPtr_dev || !C_dev || (nnz && (!cols_dev || !vals_dev || !B_dev)))
         return fail(CUTESPMM_EINVAL, "cutespmm_spmm_csr_noalloc: null pointer");
@@ -224,13 +243,13 @@ extern "C" int cutespmm_spmm_csr_noalloc(uint32_t M, uint32_t K, uint32_t nnz, c
         const uint64_t b = (items + kWarps - 1) / kWarps;
         return (uint32_t)(b < 1 ? 1 : (b > max_blocks ? max_blocks : b));
     };
-    noalloc_rows_kernel<<<dim3(blocks_for(M), slabs), kWarps * 32, 0, s>>>(rowPtr_dev, cols_dev, vals_dev, M, B_dev, ldb,
-                                                                           C_dev, ldc, N);
+    noalloc_rows_kernel<<<dim3(blocks_for(M), slabs), kWarps * 32, 0, s>>>(rowPtr_dev, cols_dev, vals_dev, M, K, nnz, B_dev,
+                                                                           ldb, C_dev, ldc, N);
     if (nnz > kSplit) {  // a long row needs more than kSplit nonzeros
         noalloc_chunks_kernel<<<dim3(blocks_for((nnz + kSplit - 1) / kSplit), slabs), kWarps * 32, 0, s>>>(
-            rowPtr_dev, cols_dev, vals_dev, M, nnz, B_dev, ldb, setup.scratch, lds, N);
-        noalloc_fixup_kernel<<<dim3(blocks_for(M), slabs), kWarps * 32, 0, s>>>(rowPtr_dev, M, setup.scratch, lds, C_dev,
-                                                                                ldc, N);
+            rowPtr_dev, cols_dev, vals_dev, M, K, nnz, B_dev, ldb, setup.scratch, lds, N);
+        noalloc_fixup_kernel<<<dim3(blocks_for(M), slabs), kWarps * 32, 0, s>>>(rowPtr_dev, M, nnz, setup.scratch, lds,
+                                                                                C_dev, ldc, N);
     }
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(CUTESPMM_ECUDA, std::string("cutespmm_spmm_csr_noalloc launch: ") + cudaGetErrorString(e));

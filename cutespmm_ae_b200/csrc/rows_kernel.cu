@@ -29,12 +29,9 @@ namespace {
 //                 better than more loads per warp when rows are short and the grid is several waves of tiles long;
 //   DEEP = true   8 rows in flight, 4 blocks per SM: fewer dependent steps per row, better for long rows and when
 //                 the whole job is a single wave of tiles and the time is a handful of latencies.
-#ifndef ROWS_SHALLOW_BLOCKS
-#define ROWS_SHALLOW_BLOCKS 6
-#endif
 template <bool DEEP> struct Tuning {
     static constexpr int kUnroll = DEEP ? 8 : 4;
-    static constexpr int kMinBlocks = DEEP ? 4 : ROWS_SHALLOW_BLOCKS;
+    static constexpr int kMinBlocks = DEEP ? 4 : 6;
 };
 constexpr int kWarps = 8;
 constexpr int kStages = 3;  // tiles in flight per block (TMA bulk copies into shared memory)

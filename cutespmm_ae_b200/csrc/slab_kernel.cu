@@ -35,24 +35,13 @@ namespace cutespmm {
 
 namespace {
 
-#ifndef SLAB_STAGES
-#define SLAB_STAGES 8   // steps of B in flight per block; a multiple of 4 (see static_assert)
-#endif
-#ifndef SLAB_META_SLOTS
-#define SLAB_META_SLOTS 64
-#endif
-#ifndef SLAB_BLOCKS_PER_SM
-#define SLAB_BLOCKS_PER_SM 3u
-#endif
-constexpr int kStages = SLAB_STAGES;
+constexpr int kStages = 8;  // steps of B in flight per block; a multiple of 4 (see static_assert)
+constexpr unsigned kBlocksPerSm = 3;  // shared memory and tensor memory (128 of 512 columns each) allow this many per SM
 // A stage is always refilled by the same producer warp and its step built by the same builder warp: a
 // warp is in order on its own stages, so the one-bit phase parity of a barrier can never be two
 // phases stale.
 static_assert(kStages % 4 == 0, "stage i % kStages must belong to producer / builder warp i % 4");
-#ifndef SLAB_ATILES
-#define SLAB_ATILES 4    // A operand tiles per block; a multiple of 4: step i uses tile i % SLAB_ATILES, built by warp i & 3
-#endif
-constexpr int kATiles = SLAB_ATILES;
+constexpr int kATiles = 4;  // A operand tiles per block; a multiple of 4: step i uses tile i % kATiles, built by warp i & 3
 // kATiles <= kStages: a builder waits for the MMA of step i - kATiles on that step's stage barrier, which must not
 // have been reused in between (the one-bit phase parity cannot tell two phases apart).
 static_assert(kATiles % 4 == 0 && kATiles <= kStages, "A tiles are owned by builder warps in turn");
@@ -69,7 +58,7 @@ constexpr int kStageBytes = 4096 + 1024;
 constexpr int kOffATiles = kStages * kStageBytes;
 constexpr int kOffDirty = 4096;               // inside an A tile: the K-major operand tile, then the rows that hold values (count, row numbers)
 constexpr int kATileBytes = 4096 + 128;
-constexpr int kMetaSlots = SLAB_META_SLOTS;   // step slots whose metadata one buffer holds
+constexpr int kMetaSlots = 64;   // step slots whose metadata one buffer holds
 constexpr int kMetaBytes = kMetaSlots * 32 + (kMetaSlots + 4) * 4;  // columns, then record offsets (+ next, padded)
 constexpr int kOffMeta = kOffATiles + kATiles * kATileBytes;
 constexpr int kOffBars = kOffMeta + 2 * kMetaBytes;
@@ -137,7 +126,7 @@ constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((
 
 namespace {
 
-__global__ void __launch_bounds__(kThreads, SLAB_BLOCKS_PER_SM) spmm_slab_kernel(const __grid_constant__ CUtensorMap tmap_b, SlabArgs a)
+__global__ void __launch_bounds__(kThreads, kBlocksPerSm) spmm_slab_kernel(const __grid_constant__ CUtensorMap tmap_b, SlabArgs a)
 {
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -395,17 +384,13 @@ bool slab_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const 
 cudaError_t launch_slab(const SlabArgs &a, int sm_count, cudaStream_t s)
 {
     if (a.num_panels == 0) return cudaSuccess;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(spmm_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    cudaError_t e = allow_dynamic_smem<spmm_slab_kernel>(kSmemBytes);
+    if (e != cudaSuccess) return e;
     // B as a 2-D tensor (columns innermost); one gather4 brings 4 rows x 32 columns = a 4 x 128-byte atom
     CUtensorMap tmap;
-    cudaError_t e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (e != cudaSuccess) return e;
-    uint32_t blocks = (uint32_t)sm_count * SLAB_BLOCKS_PER_SM;  // shared memory and tensor memory (128 of 512 columns each) allow this many per SM
+    uint32_t blocks = (uint32_t)sm_count * kBlocksPerSm;
     if (blocks > a.num_panels) blocks = a.num_panels;
     spmm_slab_kernel<<<dim3(blocks, a.N / kN), kThreads, kSmemBytes, s>>>(tmap, a);
     return cudaGetLastError();

@@ -137,7 +137,8 @@ int cutespmm_plan_decode_csr(const cutespmm_plan_t *plan, uint64_t *rowPtr, uint
  * Replaces SPMM_TC::run (spmm.cu:823-839) and the kernel SpMM<NUM_WARPS,ILP_LEVEL>
  * (kernel.cu:119-288).  B: K x N device, row-major, leading dimension ldb >= N; C: M x N device,
  * ldc >= N.  Every row of C is written (rows without nonzeros become 0), so C needs no memset
- * (the reference relies on run.cu:43,49).  Any N >= 1. */
+ * (the reference relies on run.cu:43,49).  Any N >= 1.  The plan's device must be the current one
+ * (CUTESPMM_EINVAL otherwise): a host that drives several GPUs calls cudaSetDevice before each plan. */
 int cutespmm_spmm(const cutespmm_plan_t *plan, const float *B_dev, uint64_t ldb, float *C_dev,
                   uint64_t ldc, uint32_t N, void *stream);
 
@@ -178,8 +179,9 @@ int cutespmm_spmm_csr_noalloc(uint32_t M, uint32_t K, uint32_t nnz, const uint32
 /* Number of kernels one cutespmm_spmm call launches for this plan and N. */
 int cutespmm_spmm_launch_count(const cutespmm_plan_t *plan, uint32_t N);
 
-/* Status word the kernels of this plan write on a failed bounded wait (0 = none).  Synchronises
- * nothing: call after the stream has been synchronised. */
+/* Status word the kernels of this plan write on a failed bounded wait (0 = none; 1 row kernel, 2 brick
+ * kernel, 3 slab kernel).  Orders nothing: call after the stream has been synchronised.  A non-zero
+ * word is cleared by the read, so it describes the launches since the previous read. */
 int cutespmm_plan_device_status(const cutespmm_plan_t *plan, uint32_t *status);
 
 /* ---- sharding ------------------------------------------------------------------------------

@@ -16,14 +16,37 @@ LIB_PATH = HERE / "liboracle.so"
 REF_PATH = HERE / "_ref" / "libcutespmm_ref.so"
 REF_LOADERS_PATH = HERE / "_ref" / "libcutespmm_ref_loaders.so"
 
-__all__ = ["build", "spmm_coo", "spmm_csr", "spmm_csr_rows", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
+__all__ = ["build", "reference_root", "spmm_coo", "spmm_csr", "spmm_csr_rows", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
 
 
-def build(ref_root: str | None = "/root/reference") -> None:
-    """Compiles liboracle.so (gcc) and, if the reference tree is present, oracle/_ref."""
+def reference_root() -> Path | None:
+    """Where a checkout of the reference project lies: $CUTESPMM_REF, else a directory named
+    "reference" beside this repository.  None when there is none (a machine that only runs the tests)."""
+    import os
+
+    for cand in (os.environ.get("CUTESPMM_REF"), HERE.parent.parent / "reference"):
+        if cand and (Path(cand) / "data.cu").exists():
+            return Path(cand)
+    return None
+
+
+def _nvcc() -> str:
+    import os
+    import shutil
+
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    return "nvcc"
+
+
+def build(ref_root="auto") -> None:
+    """Compiles liboracle.so (gcc) and, if a reference checkout is found (reference_root(), or the
+    path given), oracle/_ref.  ref_root=None builds the oracle alone."""
     subprocess.run(["make", "-s", "-C", str(HERE)], check=True)
-    if ref_root and (Path(ref_root) / "data.cu").exists():
-        subprocess.run(["make", "-s", "-C", str(HERE), "ref", f"REF={ref_root}"], check=True)
+    root = reference_root() if ref_root == "auto" else (Path(ref_root) if ref_root else None)
+    if root and (root / "data.cu").exists():
+        subprocess.run(["make", "-s", "-C", str(HERE), "ref", f"REF={root}", f"NVCC={_nvcc()}"], check=True)
 
 
 _lib = None

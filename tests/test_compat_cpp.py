@@ -10,7 +10,7 @@ import cutespmm_ae_b200 as cs
 import oracle
 from conftest import GOLDEN, ROOT
 
-CUDA = Path("/usr/local/cuda")
+CUDA = cs._build.CUDA_HOME
 
 
 def build_driver(tmp: Path) -> Path:

@@ -1,11 +1,10 @@
 """Regression sweep over the MatrixMarket files the reference project ships (its ae_matrices/ folder), on the
 CPU: the loader, the plan's packed format and the reference-compatible views on real sparsity patterns.
 
-Opt-in by presence: runs only where a copy of the reference tree is mounted (CUTESPMM_REF or /root/reference)
-and its host routines have been compiled into oracle/_ref; skipped everywhere else.  Nothing of those files
+Opt-in by presence: runs only where a checkout of the reference project is found (oracle.reference_root():
+$CUTESPMM_REF, or a directory named "reference" beside this repository) and its host routines have been compiled into oracle/_ref; skipped everywhere else.  Nothing of those files
 is stored in this repository.
 """
-import os
 from pathlib import Path
 
 import numpy as np
@@ -15,9 +14,11 @@ import cutespmm_ae_b200 as cs
 
 
 def _matrix_files():
-    for root in (os.environ.get("CUTESPMM_REF"), "/root/reference"):
-        if root and (Path(root) / "ae_matrices").is_dir():
-            return sorted(Path(root, "ae_matrices").glob("*/*.mtx"))
+    import oracle
+
+    root = oracle.reference_root()
+    if root and (root / "ae_matrices").is_dir():
+        return sorted((root / "ae_matrices").glob("*/*.mtx"))
     return []
 
 

@@ -37,7 +37,7 @@ def test_golden_fixtures(oracle_mod, name, path):
                                          ("elasticity40", [32, 64, 128, 256]), ("rmat20", [128])])
 def test_named_workloads_match_oracle(oracle_mod, workload, Ns, path):
     if path == cs.PATH_SLAB and workload == "rmat20":
-        pytest.skip("forcing a power-law graph through the dense 128-row path is covered at 2^10 nodes (slab_try sizes); here it only costs time")
+        pytest.skip("forcing a power-law graph through the dense 128-row path is covered at 2^11 nodes (test_slab_path_on_a_small_power_law_graph_and_rounding_modes); here it only costs time")
     w = g.WORKLOADS[workload]
     A = w["make"]()
     p = cs.Plan.from_csr(A, path=path)
