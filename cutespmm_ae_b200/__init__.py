@@ -22,9 +22,12 @@ import numpy as np
 
 from . import _build
 
-__all__ = ["CuteSpmmError", "Plan", "MtxReader", "partition_rows", "spmm_csr_noalloc", "lib", "PATH_AUTO", "PATH_ROWS", "PATH_BRICK", "PATH_SLAB"]
+__all__ = ["CuteSpmmError", "Plan", "Comm", "MtxReader", "partition_rows", "spmm_csr_noalloc", "lib", "PATH_AUTO", "PATH_ROWS",
+           "PATH_BRICK", "PATH_SLAB", "B_RESIDENT", "B_FROM_ROOT", "B_ROW_SHARDED"]
 
 PATH_AUTO, PATH_ROWS, PATH_BRICK, PATH_SLAB = 0, 1, 2, 3
+B_RESIDENT, B_FROM_ROOT, B_ROW_SHARDED = 0, 1, 2  # cutespmm_b_mode_t
+COMM_ID_BYTES = 128
 
 
 class CuteSpmmError(RuntimeError):
@@ -70,6 +73,17 @@ def _load() -> C.CDLL:
         "cutespmm_spmm_csr_noalloc": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, vp, vp, vp, vp, C.c_uint64, vp,
                                                 C.c_uint64, C.c_uint32, vp]),
         "cutespmm_plan_device_status": (C.c_int, [vp, u32p]),
+        "cutespmm_comm_unique_id": (C.c_int, [vp]),
+        "cutespmm_comm_create": (C.c_int, [C.POINTER(vp), C.c_int, C.c_int, vp]),
+        "cutespmm_comm_create_all": (C.c_int, [C.POINTER(vp), C.c_int, C.POINTER(C.c_int)]),
+        "cutespmm_comm_adopt": (C.c_int, [C.POINTER(vp), vp, C.c_int, C.c_int]),
+        "cutespmm_comm_create_stub": (C.c_int, [C.POINTER(vp), C.c_int, C.c_int]),
+        "cutespmm_comm_stub_log": (C.c_int, [vp, C.c_uint32, vp, vp, vp, u32p]),
+        "cutespmm_comm_info": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+        "cutespmm_comm_destroy": (C.c_int, [vp]),
+        "cutespmm_spmm_sharded": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, C.c_uint64, vp, vp, C.c_uint64, C.c_uint32, vp]),
+        "cutespmm_spmm_sharded_host": (C.c_int, [vp, vp, vp, C.c_uint64, vp, vp, C.c_uint64, C.c_uint32, vp, f32p, f32p]),
+        "cutespmm_sharded_transfers": (C.c_int, [vp, C.c_int, C.c_int, C.c_uint64, C.c_uint64, vp, C.c_uint32, vp, vp, vp, u32p]),
         "cutespmm_partition_rows": (C.c_int, [C.c_uint64, vp, C.c_uint32, C.c_uint32, C.c_uint32, vp]),
         "cutespmm_mtx_open": (C.c_int, [C.POINTER(vp), C.c_char_p, C.c_int]),
         "cutespmm_mtx_dims": (C.c_int, [vp, u32p, u32p, u32p]),
@@ -215,6 +229,115 @@ class Plan:
                                       tc.stride(0) if self.M > 1 else max(N, 1), N, st, C.byref(ms)))
         return Cout, ms.value
 
+    def spmm_sharded(self, comm: "Comm", B, Cout=None, *, b_mode: int = B_RESIDENT, root: int = 0, b_bounds=None, stream=None):
+        """This rank's rows of A @ B through cutespmm_spmm_sharded: B (K x N, contiguous, on this rank's GPU) is
+        completed in place by the exchange `b_mode` names (B_FROM_ROOT: broadcast from `root`; B_ROW_SHARDED: this
+        rank holds rows [b_bounds[rank], b_bounds[rank+1]) and the others arrive by all-gather), then multiplied."""
+        import torch
+
+        if not B.is_cuda or B.dtype != torch.float32 or B.dim() != 2 or B.shape[0] != self.K or not B.is_contiguous():
+            raise ValueError("B must be a contiguous K x N CUDA fp32 tensor")
+        N = B.shape[1]
+        if Cout is None:
+            Cout = torch.empty((self.M, N), dtype=torch.float32, device=B.device)
+        if not Cout.is_cuda or Cout.dtype != torch.float32 or Cout.shape != (self.M, N) or Cout.stride(1) != 1:
+            raise ValueError("C must be an M x N CUDA fp32 tensor with unit column stride")
+        bb = None if b_bounds is None else _np(b_bounds, np.uint64)
+        if bb is not None and bb.shape[0] != comm.nranks + 1:
+            raise ValueError("b_bounds must have nranks+1 entries")
+        st = (stream or torch.cuda.current_stream(B.device)).cuda_stream
+        _check(lib.cutespmm_spmm_sharded(self._h, comm._h, b_mode, root, B.data_ptr(), max(N, 1), None if bb is None else bb.ctypes.data,
+                                         Cout.data_ptr(), Cout.stride(0) if self.M > 1 else max(N, 1), N, st))
+        return Cout
+
+    def spmm_sharded_host(self, comm, B_rows, b_bounds, Cout=None, stream=None):
+        """Host buffers in and out with several ranks (cutespmm_spmm_sharded_host): `B_rows` is this rank's slice of B
+        only, rows [b_bounds[rank], b_bounds[rank+1]) as a CPU fp32 tensor (pinned for full copy bandwidth); every rank
+        uploads its slice over its own PCIe link and the slices are exchanged over NVLink.  Returns
+        (C rows of this rank, kernel_ms, exchange_ms)."""
+        import torch
+
+        bb = _np(b_bounds, np.uint64)
+        nranks, rank = (comm.nranks, comm.rank) if comm is not None else (1, 0)
+        if bb.shape[0] != nranks + 1:
+            raise ValueError("b_bounds must have nranks+1 entries")
+        rows = int(bb[rank + 1] - bb[rank])
+        tb = B_rows
+        if tb.is_cuda or tb.dtype != torch.float32 or tb.dim() != 2 or tb.stride(1) != 1 or tb.shape[0] != rows:
+            raise ValueError(f"B_rows must be a {rows} x N CPU fp32 tensor with unit column stride")
+        N = tb.shape[1]
+        if Cout is None:
+            Cout = torch.empty((self.M, N), dtype=torch.float32)
+        if Cout.is_cuda or Cout.dtype != torch.float32 or tuple(Cout.shape) != (self.M, N) or Cout.stride(1) != 1:
+            raise ValueError("C must be an M x N CPU fp32 tensor with unit column stride")
+        kms, xms = C.c_float(0.0), C.c_float(0.0)
+        st = stream.cuda_stream if stream is not None else None
+        _check(lib.cutespmm_spmm_sharded_host(self._h, comm._h if comm is not None else None, tb.data_ptr(),
+                                              tb.stride(0) if rows > 1 else max(N, 1), bb.ctypes.data, Cout.data_ptr(),
+                                              Cout.stride(0) if self.M > 1 else max(N, 1), N, st, C.byref(kms), C.byref(xms)))
+        return Cout, kms.value, xms.value
+
+
+class Comm:
+    """A communicator of the library (cutespmm_comm_*): NCCL underneath, opened at run time.  One per rank; the
+    rank's CUDA device must be current when it is created.
+
+    `Comm.from_torch(group)` builds one for every rank of a torch.distributed group (the id travels through the
+    group); `Comm.stub(nranks, rank)` records transfers instead of sending them (tests without GPUs)."""
+
+    def __init__(self, handle, nranks: int, rank: int):
+        self._h, self.nranks, self.rank = handle, nranks, rank
+
+    @classmethod
+    def create(cls, nranks: int, rank: int, unique_id: bytes) -> "Comm":
+        h = C.c_void_p()
+        buf = C.create_string_buffer(bytes(unique_id), COMM_ID_BYTES)
+        _check(lib.cutespmm_comm_create(C.byref(h), nranks, rank, buf))
+        return cls(h, nranks, rank)
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(COMM_ID_BYTES)
+        _check(lib.cutespmm_comm_unique_id(buf))
+        return buf.raw
+
+    @classmethod
+    def from_torch(cls, group=None) -> "Comm":
+        import torch.distributed as dist
+
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [cls.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls.create(world, rank, box[0])
+
+    @classmethod
+    def stub(cls, nranks: int, rank: int) -> "Comm":
+        h = C.c_void_p()
+        _check(lib.cutespmm_comm_create_stub(C.byref(h), nranks, rank))
+        return cls(h, nranks, rank)
+
+    def transfers(self, b_mode: int, K: int, N: int, b_bounds=None, root: int = 0):
+        """[(root, element offset, element count)] of the exchange of one contiguous K x N block of B."""
+        bb = None if b_bounds is None else _np(b_bounds, np.uint64)
+        cap = self.nranks + 1
+        roots, offs, cnts, n = np.zeros(cap, np.int32), np.zeros(cap, np.uint64), np.zeros(cap, np.uint64), C.c_uint32()
+        _check(lib.cutespmm_sharded_transfers(self._h, b_mode, root, K, N, None if bb is None else bb.ctypes.data, cap,
+                                              roots.ctypes.data, offs.ctypes.data, cnts.ctypes.data, C.byref(n)))
+        return [(int(roots[i]), int(offs[i]), int(cnts[i])) for i in range(n.value)]
+
+    def stub_log(self):
+        cap = 4096
+        roots, offs, cnts, n = np.zeros(cap, np.int32), np.zeros(cap, np.uint64), np.zeros(cap, np.uint64), C.c_uint32()
+        _check(lib.cutespmm_comm_stub_log(self._h, cap, roots.ctypes.data, offs.ctypes.data, cnts.ctypes.data, C.byref(n)))
+        return [(int(roots[i]), int(offs[i]), int(cnts[i])) for i in range(min(n.value, cap))]
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) and self._h.value and lib is not None:
+            lib.cutespmm_comm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
 
 def spmm_csr_noalloc(M: int, K: int, row_ptr, cols, vals, B, Cout, stream=None):
     """C = A @ B from CSR tensors that already live on the GPU (row_ptr/cols int32, vals/B/C fp32),
@@ -225,9 +348,20 @@ def spmm_csr_noalloc(M: int, K: int, row_ptr, cols, vals, B, Cout, stream=None):
     for t, dt in ((row_ptr, torch.int32), (cols, torch.int32), (vals, torch.float32), (B, torch.float32), (Cout, torch.float32)):
         if not t.is_cuda or t.dtype != dt:
             raise ValueError("all operands must be CUDA tensors: row_ptr/cols int32, vals/B/C float32")
+    if B.dim() != 2 or Cout.dim() != 2:
+        raise ValueError("B and C must be 2-D")
     if not (row_ptr.is_contiguous() and cols.is_contiguous() and vals.is_contiguous()) or B.stride(1) != 1 or Cout.stride(1) != 1:
         raise ValueError("CSR arrays must be contiguous; B and C need unit column stride")
     N = B.shape[1]
+    # the call itself cannot see the sizes of the buffers behind the pointers: check them here, as Plan.spmm does
+    if row_ptr.numel() != M + 1 or cols.numel() != vals.numel():
+        raise ValueError("row_ptr must have M+1 entries; cols and vals the same length")
+    if B.shape[0] != K:
+        raise ValueError(f"B has {B.shape[0]} rows, A has {K} columns")
+    if tuple(Cout.shape) != (M, N):
+        raise ValueError(f"C must be {M} x {N}, got {tuple(Cout.shape)}")
+    if len({t.device for t in (row_ptr, cols, vals, B, Cout)}) != 1:
+        raise ValueError("all operands must live on one device")
     st = (stream or torch.cuda.current_stream(B.device)).cuda_stream
     _check(lib.cutespmm_spmm_csr_noalloc(M, K, cols.numel(), row_ptr.data_ptr(), cols.data_ptr(), vals.data_ptr(), B.data_ptr(),
                                          B.stride(0) if K > 1 else max(N, 1), Cout.data_ptr(),

@@ -17,7 +17,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBDIR = HERE / "lib"
 LIB = LIBDIR / "libcutespmm.so"
-SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "slab_kernel.cu", "device_build.cu", "plan.cpp", "brick_build.cpp", "slab_build.cpp", "mtx_io.cpp"]
+SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "slab_kernel.cu", "device_build.cu", "sharded.cu", "plan.cpp", "brick_build.cpp", "slab_build.cpp", "mtx_io.cpp"]
 def _find_nvcc() -> str:
     import shutil
 
@@ -33,7 +33,7 @@ FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-Xcompiler", "-fPIC,-fopenmp,-O3,-Wall,-Wno-unknown-pragmas",
-    "-shared", "-lgomp",
+    "-shared", "-lgomp", "-ldl",
 ]
 
 

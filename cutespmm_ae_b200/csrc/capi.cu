@@ -9,7 +9,9 @@
 #include <vector>
 
 #include "device_plan.hpp"
+#include "nvtx.hpp"
 #include "plan.hpp"
+#include "plan_object.hpp"
 
 using namespace cutespmm;
 
@@ -18,19 +20,21 @@ thread_local std::string g_last_error;
 }
 namespace cutespmm {
 void set_last_error(const std::string &msg) { g_last_error = msg; }
-}
-namespace {
-
-int fail(int status, const std::string &msg)
+int fail_status(int status, const std::string &msg)
 {
     g_last_error = msg;
     return status;
 }
-int fail_cuda(cudaError_t e, const char *what)
+int fail_cuda_status(cudaError_t e, const char *what)
 {
     g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
     return e == cudaErrorMemoryAllocation ? CUTESPMM_ENOMEM : CUTESPMM_ECUDA;
 }
+}
+namespace {
+
+int fail(int status, const std::string &msg) { return fail_status(status, msg); }
+int fail_cuda(cudaError_t e, const char *what) { return fail_cuda_status(e, what); }
 
 template <class T> cudaError_t upload(const std::vector<T> &h, void **d, uint64_t &bytes)
 {
@@ -42,49 +46,6 @@ template <class T> cudaError_t upload(const std::vector<T> &h, void **d, uint64_
     return cudaMemcpy(*d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice);
 }
 }  // namespace
-
-struct cutespmm_plan {
-    HostPlan host;
-    bool on_device = false;
-    int device = -1;
-    int sm_count = 0;
-    uint64_t device_bytes = 0;
-    // device arrays
-    void *d_row_ptr = nullptr, *d_pairs = nullptr, *d_tiles = nullptr, *d_chunks = nullptr, *d_long_rows = nullptr;
-    void *d_tiles_all = nullptr, *d_chunks_all = nullptr, *d_long_rows_all = nullptr;
-    void *d_bcols = nullptr, *d_brecs = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
-    void *d_scols = nullptr, *d_srecs = nullptr, *d_srec_off = nullptr, *d_sfirst = nullptr, *d_slast = nullptr, *d_sids = nullptr;
-    float *d_scratch = nullptr;
-    uint32_t *d_status = nullptr;
-    // staging for the host-buffer call
-    float *d_B = nullptr, *d_C = nullptr;
-    uint64_t staged_B = 0, staged_C = 0;
-    // the host-buffer call pipelines column windows: copy-in, product and copy-out each on a stream of their own
-    static constexpr int kMaxWindows = 4;
-    cudaStream_t s_in = nullptr, s_out = nullptr;
-    cudaEvent_t ev_entry = nullptr, ev_done = nullptr;
-    cudaEvent_t ev_in[kMaxWindows] = {}, ev_k0[kMaxWindows] = {}, ev_k1[kMaxWindows] = {};
-
-    ~cutespmm_plan()
-    {
-        if (!on_device) return;
-        int cur = -1;
-        cudaGetDevice(&cur);
-        if (cur != device) cudaSetDevice(device);
-        for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
-                        d_bcols, d_brecs, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
-                        d_slast, d_sids, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
-            if (p) cudaFree(p);
-        for (cudaEvent_t ev : {ev_entry, ev_done})
-            if (ev) cudaEventDestroy(ev);
-        for (int w = 0; w < kMaxWindows; ++w)
-            for (cudaEvent_t ev : {ev_in[w], ev_k0[w], ev_k1[w]})
-                if (ev) cudaEventDestroy(ev);
-        if (s_in) cudaStreamDestroy(s_in);
-        if (s_out) cudaStreamDestroy(s_out);
-        if (cur != device && cur >= 0) cudaSetDevice(cur);
-    }
-};
 
 extern "C" {
 
@@ -98,6 +59,7 @@ const char *cutespmm_status_string(int status)
         case CUTESPMM_EUNSUPPORTED: return "unsupported";
         case CUTESPMM_EIO: return "I/O error";
         case CUTESPMM_ETIMEOUT: return "device-side wait timed out";
+        case CUTESPMM_ECOMM: return "communication library error";
         default: return "unknown status";
     }
 }
@@ -146,6 +108,7 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
     if (prop.major < 10)
         return fail(CUTESPMM_EUNSUPPORTED, "this library is built for sm_100a (B200) only; found compute capability " +
                                                std::to_string(prop.major) + "." + std::to_string(prop.minor));
+    NvtxRange range("cutespmm: plan creation");
     int st = build_common(plan, M, K, rowPtr, cols, vals, opts);
     if (st != CUTESPMM_OK) return st;
     cutespmm_plan *p = *plan;
@@ -215,6 +178,7 @@ int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, 
     if (!rowPtr_dev) return fail(CUTESPMM_EINVAL, "rowPtr is NULL");
     if (M >= (1ull << 32) - kPanelRows || K >= (1ull << 32)) return fail(CUTESPMM_EUNSUPPORTED, "M and K must be below 2^32");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    NvtxRange range("cutespmm: plan creation (device CSR)");
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice (libcutespmm needs a CUDA device; there is no CPU path)");
@@ -474,94 +438,6 @@ int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float 
         if ((e = launch_rows(ra, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "row kernel launch");
         if ((e = launch_fixup(ra, s)) != cudaSuccess) return fail_cuda(e, "fix-up kernel launch");
     }
-    return CUTESPMM_OK;
-}
-
-int cutespmm_spmm_host(cutespmm_plan_t *p, const float *B_host, uint64_t ldb, float *C_host, uint64_t ldc, uint32_t N,
-                       void *stream, float *kernel_ms)
-{
-    if (!p) return fail(CUTESPMM_EINVAL, "plan is NULL");
-    if (!p->on_device) return fail(CUTESPMM_EUNSUPPORTED, "host-only plan cannot execute");
-    if (N == 0) return CUTESPMM_OK;
-    if (!B_host || !C_host) return fail(CUTESPMM_EINVAL, "null host buffer");
-    if (ldb < N || ldc < N) return fail(CUTESPMM_EINVAL, "leading dimension smaller than N");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t e;
-    // Column windows are independent products (C[:, w] = A * B[:, w]), so the call is a pipeline over them:
-    // while window w is multiplied and copied out, window w+1 is already coming in; the two copy directions
-    // run on different engines.  Small operands go in one piece.
-    const uint64_t M = p->host.M, K = p->host.K;
-    uint32_t nw = 1;
-    if ((uint64_t)N * std::max(M, K) * sizeof(float) >= (8u << 20)) nw = std::max(1u, std::min<uint32_t>(cutespmm_plan::kMaxWindows, N / 64));
-    // window width: a multiple of 64 columns (the last may be narrower); strided copies of rows shorter than 256 bytes
-    // were measured at 2/3 of the link rate, 256-byte rows at the full rate
-    const uint32_t wcols = ((N + nw - 1) / nw + 63) / 64 * 64;
-    nw = (N + wcols - 1) / wcols;
-    const uint64_t ldd = nw == 1 ? (uint64_t)(N + 3) / 4 * 4 : wcols;  // device leading dimension: rows start 16-byte aligned
-    const uint64_t needB = (uint64_t)nw * K * ldd * sizeof(float), needC = (uint64_t)nw * M * ldd * sizeof(float);
-    if (needB > p->staged_B) {
-        if (p->d_B) cudaFree(p->d_B);
-        p->d_B = nullptr; p->staged_B = 0;
-        if ((e = cudaMalloc(&p->d_B, needB)) != cudaSuccess) return fail_cuda(e, "staging buffer for B");
-        p->staged_B = needB;
-    }
-    if (needC > p->staged_C) {
-        if (p->d_C) cudaFree(p->d_C);
-        p->d_C = nullptr; p->staged_C = 0;
-        if ((e = cudaMalloc(&p->d_C, needC)) != cudaSuccess) return fail_cuda(e, "staging buffer for C");
-        p->staged_C = needC;
-    }
-    if (!p->s_in) {
-        if ((e = cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking)) != cudaSuccess ||
-            (e = cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking)) != cudaSuccess)
-            return fail_cuda(e, "cudaStreamCreate");
-        if ((e = cudaEventCreateWithFlags(&p->ev_entry, cudaEventDisableTiming)) != cudaSuccess ||
-            (e = cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming)) != cudaSuccess)
-            return fail_cuda(e, "cudaEventCreate");
-        for (int w = 0; w < cutespmm_plan::kMaxWindows; ++w)
-            if ((e = cudaEventCreateWithFlags(&p->ev_in[w], cudaEventDisableTiming)) != cudaSuccess ||
-                (e = cudaEventCreate(&p->ev_k0[w])) != cudaSuccess || (e = cudaEventCreate(&p->ev_k1[w])) != cudaSuccess)
-                return fail_cuda(e, "cudaEventCreate");
-    }
-    // whatever the caller queued on `stream` comes first
-    cudaEventRecord(p->ev_entry, s);
-    cudaStreamWaitEvent(p->s_in, p->ev_entry, 0);
-    for (uint32_t w = 0; w < nw; ++w) {
-        const uint32_t c0 = w * wcols, cw = std::min(wcols, N - c0);
-        float *dB = p->d_B + (uint64_t)w * K * ldd, *dC = p->d_C + (uint64_t)w * M * ldd;
-        if (K && (e = cudaMemcpy2DAsync(dB, ldd * sizeof(float), B_host + c0, ldb * sizeof(float), (size_t)cw * sizeof(float), K,
-                                        cudaMemcpyHostToDevice, p->s_in)) != cudaSuccess)
-            return fail_cuda(e, "copy of B to the device");
-        cudaEventRecord(p->ev_in[w], p->s_in);
-        cudaStreamWaitEvent(s, p->ev_in[w], 0);
-        cudaEventRecord(p->ev_k0[w], s);
-        int st = cutespmm_spmm(p, dB, ldd, dC, ldd, cw, s);
-        if (st != CUTESPMM_OK) {
-            cudaStreamSynchronize(p->s_in);
-            cudaStreamSynchronize(p->s_out);
-            cudaStreamSynchronize(s);
-            return st;
-        }
-        cudaEventRecord(p->ev_k1[w], s);
-        cudaStreamWaitEvent(p->s_out, p->ev_k1[w], 0);
-        if (M && (e = cudaMemcpy2DAsync(C_host + c0, ldc * sizeof(float), dC, ldd * sizeof(float), (size_t)cw * sizeof(float), M,
-                                        cudaMemcpyDeviceToHost, p->s_out)) != cudaSuccess)
-            return fail_cuda(e, "copy of C to the host");
-    }
-    cudaEventRecord(p->ev_done, p->s_out);
-    cudaStreamWaitEvent(s, p->ev_done, 0);  // later work on `stream` sees the finished call
-    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return fail_cuda(e, "SpMM execution");
-    if (kernel_ms) {
-        *kernel_ms = 0.f;
-        for (uint32_t w = 0; w < nw; ++w) {
-            float ms = 0.f;
-            cudaEventElapsedTime(&ms, p->ev_k0[w], p->ev_k1[w]);
-            *kernel_ms += ms;
-        }
-    }
-    uint32_t dev_status = 0;
-    cutespmm_plan_device_status(p, &dev_status);
-    if (dev_status) return fail(CUTESPMM_ETIMEOUT, "a device-side wait ran out (status " + std::to_string(dev_status) + ")");
     return CUTESPMM_OK;
 }
 

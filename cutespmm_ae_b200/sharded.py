@@ -5,12 +5,18 @@ per-row term, 16-row aligned: `cutespmm_partition_rows`), every rank builds a pl
 only, and C stays row-sharded: rank p owns rows [bounds[p], bounds[p+1]).  The one exchange of the
 path is B, which every rank needs in its own memory.  Two ways to run a product:
 
-* `spmm(B)`           B is already replicated (iterative solvers, the layers of a GNN after the
-                      first): purely local, no collective.
-* `spmm_from_root(B)` B lives on one rank.  It travels by broadcast in column windows, and the
-                      product of a window starts as soon as that window has arrived, so the
-                      multiplication overlaps the tail of the transfer (column windows of B are
-                      independent products: C[:, w] = A @ B[:, w]).
+* `spmm(B)`              B is already replicated (iterative solvers, the layers of a GNN after the
+                         first): purely local, no collective.
+* `spmm_from_root(B)`    B lives on one rank and reaches the others by broadcast.
+* `spmm_row_sharded(B)`  every rank holds a row range of B in place inside its K x N buffer (the C
+                         of a previous sharded product): one all-gather, then the product.
+* `spmm_host(B_rows)`    host buffers: every rank uploads only its own slice of B over its own PCIe
+                         link, the slices are exchanged over NVLink, C rows go back to the host.
+
+On GPU ranks these are calls of the library's C entry points (cutespmm_spmm_sharded,
+cutespmm_spmm_sharded_host) over the library's own communicator (cutespmm_comm_*, NCCL underneath);
+this class only adds the partition and the plan.  On CPU ranks (tests of the host logic under gloo)
+`spmm_from_root` runs the same schedule over torch.distributed with a caller-supplied product.
 
 The reference has no multi-GPU path; its single-GPU driver loop (run.cu:38-53) is what a rank runs
 on its shard.  No kernel reads another GPU's memory: B comes into local memory first (NCCL).
@@ -21,7 +27,7 @@ from typing import Callable, Optional
 
 import numpy as np
 
-from . import PATH_AUTO, Plan, partition_rows
+from . import B_FROM_ROOT, B_ROW_SHARDED, PATH_AUTO, Comm, Plan, partition_rows
 
 
 def column_windows(N: int, max_windows: int = 4, min_cols: int = 32) -> list[tuple[int, int]]:
@@ -66,11 +72,43 @@ class ShardedSpmm:
         self.rows = mine
         self.plan = Plan.from_csr(mine, path=path, host_only=host_only, **plan_kw)
         self._recv = {}  # receive buffers of spmm_from_root, by (window, width, device)
+        self._comm = None
+
+    @property
+    def comm(self) -> Comm:
+        """The library communicator of this rank (created on first use; collective: every rank must ask for it)."""
+        if self._comm is None:
+            if self.world == 1:
+                raise RuntimeError("a single rank needs no communicator")
+            self._comm = Comm.from_torch(self.group)
+        return self._comm
+
+    def even_row_bounds(self) -> np.ndarray:
+        """Row bounds of B cut into `world` slices of equal size (the last takes the remainder): equal slices travel
+        as one in-place all-gather."""
+        step = -(-self.K // self.world)
+        return np.minimum(np.arange(self.world + 1, dtype=np.uint64) * np.uint64(step), np.uint64(self.K))
 
     # ---- B already in every rank's memory --------------------------------------------------------
     def spmm(self, B, Cout=None, stream=None):
         """Rows [r0, r1) of A @ B; B is a K x N CUDA tensor resident on this rank."""
         return self.plan.spmm(B, Cout, stream)
+
+    # ---- B row-sharded over the ranks --------------------------------------------------------------
+    def spmm_row_sharded(self, B, b_bounds, Cout=None, stream=None):
+        """Rows [r0, r1) of A @ B where this rank's K x N buffer B holds rows [b_bounds[rank], b_bounds[rank+1]) and
+        the rest arrives by one all-gather in place (cutespmm_spmm_sharded, CUTESPMM_B_ROW_SHARDED)."""
+        if self.world == 1:
+            return self.plan.spmm(B, Cout, stream)
+        return self.plan.spmm_sharded(self.comm, B, Cout, b_mode=B_ROW_SHARDED, b_bounds=b_bounds, stream=stream)
+
+    # ---- host buffers ------------------------------------------------------------------------------
+    def spmm_host(self, B_rows, b_bounds=None, Cout=None, stream=None):
+        """Host in, host out: B_rows is this rank's slice of B (rows [b_bounds[rank], b_bounds[rank+1]), default
+        even_row_bounds()); returns (C rows of this rank on the host, kernel_ms, exchange_ms)."""
+        if b_bounds is None:
+            b_bounds = self.even_row_bounds()
+        return self.plan.spmm_sharded_host(self.comm if self.world > 1 else None, B_rows, b_bounds, Cout, stream)
 
     # ---- B on one rank ---------------------------------------------------------------------------
     def spmm_from_root(self, B, N: int, root: int = 0, Cout=None, *, max_windows: int = 1, min_cols: int = 64,
@@ -91,6 +129,21 @@ class ShardedSpmm:
         """
         import torch
 
+        if product is None and self.world > 1 and max_windows == 1:
+            # GPU ranks, one window: the library's own broadcast + product (cutespmm_spmm_sharded)
+            if self.rank == root:
+                if B is None or tuple(B.shape) != (self.K, N):
+                    raise ValueError("the root rank must pass B with shape (K, N)")
+                buf = B if B.is_contiguous() else B.contiguous()
+            else:
+                if device is None:
+                    raise ValueError("ranks other than the root must say on which device B is to be received")
+                key = (0, N, str(device))
+                buf = self._recv.get(key)
+                if buf is None:
+                    buf = self._recv[key] = torch.empty((self.K, N), dtype=torch.float32, device=device)
+            Cout = self.plan.spmm_sharded(self.comm, buf, Cout, b_mode=B_FROM_ROOT, root=root)
+            return Cout, [buf]
         if product is None:
             product = lambda Bw, Cw: self.plan.spmm(Bw, Cw)  # noqa: E731
         wins = column_windows(N, max_windows, min_cols)

@@ -38,7 +38,8 @@ typedef enum {
     CUTESPMM_ECUDA = -3,        /* a CUDA runtime call or kernel launch failed (no device, ...) */
     CUTESPMM_EUNSUPPORTED = -4, /* valid request outside what this build handles */
     CUTESPMM_EIO = -5,          /* file could not be read or parsed */
-    CUTESPMM_ETIMEOUT = -6      /* a bounded device-side wait ran out (reported through the plan's status word) */
+    CUTESPMM_ETIMEOUT = -6,     /* a bounded device-side wait ran out (reported through the plan's status word) */
+    CUTESPMM_ECOMM = -7         /* the communication library is missing or one of its calls failed */
 } cutespmm_status_t;
 
 /* Which kernel family executes a plan. */
@@ -191,6 +192,68 @@ int cutespmm_plan_device_status(const cutespmm_plan_t *plan, uint32_t *status);
  * bounds[nparts] = M.  Each rank then builds a plan over its own rows and C stays row-sharded. */
 int cutespmm_partition_rows(uint64_t M, const uint64_t *rowPtr, uint32_t nparts, uint32_t align_rows,
                             uint32_t row_cost, uint64_t *bounds);
+
+/* ---- communicator and sharded execution ----------------------------------------------------
+ * No counterpart in the reference (its driver, run.cu:8-72, runs one GPU).  Row panels are
+ * independent, so a large matrix is cut by cutespmm_partition_rows, every rank (one GPU each: a
+ * process, or a thread of one process) creates a plan over its own rows, and C stays row-sharded.
+ * The one exchange of the path is B, which every rank needs in its own device memory; it travels
+ * over NVLink through NCCL, which the library loads at run time (libnccl.so.2; no link dependency)
+ * the first time a communicator is created.  No kernel of this library reads another GPU's memory.
+ *
+ * A communicator belongs to the CUDA device that was current when it was created; collective calls
+ * on it must come from one thread at a time, in the same order on every rank. */
+typedef struct cutespmm_comm cutespmm_comm_t;
+#define CUTESPMM_COMM_ID_BYTES 128
+/* Rank 0 obtains an id and hands it to the other ranks by any means (a file, MPI, a TCP store). */
+int cutespmm_comm_unique_id(void *id_out /* CUTESPMM_COMM_ID_BYTES */);
+/* One process per GPU: every rank calls this with the same id; collective. */
+int cutespmm_comm_create(cutespmm_comm_t **comm, int nranks, int rank, const void *id);
+/* One process, several GPUs: creates ndev communicators at once, comms[i] on devices[i] (NULL: 0..ndev-1). */
+int cutespmm_comm_create_all(cutespmm_comm_t **comms, int ndev, const int *devices);
+/* Wraps an ncclComm_t the caller already has (not destroyed by cutespmm_comm_destroy). */
+int cutespmm_comm_adopt(cutespmm_comm_t **comm, void *nccl_comm, int nranks, int rank);
+/* A communicator without a transport: collectives are recorded instead of executed.  For testing the
+ * bookkeeping of the sharded calls on a machine without GPUs (see cutespmm_sharded_transfers). */
+int cutespmm_comm_create_stub(cutespmm_comm_t **comm, int nranks, int rank);
+/* The transfers a stub communicator was asked for since the last call of this function (same fields as
+ * cutespmm_sharded_transfers); the record is emptied. */
+int cutespmm_comm_stub_log(cutespmm_comm_t *comm, uint32_t max, int *roots, uint64_t *offsets, uint64_t *counts, uint32_t *n);
+int cutespmm_comm_info(const cutespmm_comm_t *comm, int *nranks, int *rank);
+int cutespmm_comm_destroy(cutespmm_comm_t *comm);
+
+/* How B reaches every rank's memory before the product. */
+typedef enum {
+    CUTESPMM_B_RESIDENT = 0,    /* B_dev already holds all K rows on every rank: no exchange */
+    CUTESPMM_B_FROM_ROOT = 1,   /* rank `root` holds B; one broadcast fills B_dev on the others */
+    CUTESPMM_B_ROW_SHARDED = 2  /* rank r holds rows [b_bounds[r], b_bounds[r+1]) in place inside its K x N
+                                   buffer B_dev (the C of a previous sharded product, a layer's output):
+                                   one all-gather in place (equal slices) or one broadcast per slice */
+} cutespmm_b_mode_t;
+
+/* This rank's rows of C = A * B.  plan: built over this rank's rows; B_dev: K x N on this rank, rows
+ * contiguous (ldb == N) unless the mode is RESIDENT; b_bounds: nranks+1 row bounds of B (ROW_SHARDED
+ * only, else NULL); C_dev: this rank's rows of C.  The exchange and the product are queued on `stream`
+ * and the call returns without waiting. */
+int cutespmm_spmm_sharded(const cutespmm_plan_t *plan, cutespmm_comm_t *comm, int b_mode, int root, float *B_dev,
+                          uint64_t ldb, const uint64_t *b_bounds, float *C_dev, uint64_t ldc, uint32_t N, void *stream);
+
+/* The same from host buffers, in the style of cutespmm_spmm_host: rank r passes only its own slice of
+ * B -- B_host_rows points at row b_bounds[r] of B, rows [b_bounds[r], b_bounds[r+1]) follow with leading
+ * dimension ldb -- so every rank copies K/nranks rows over its own PCIe link, the slices are exchanged
+ * over NVLink, and each rank copies its rows of C back to C_host.  Column windows pipeline copy-in,
+ * exchange, product and copy-out.  comm == NULL (or one rank) with b_bounds == NULL is cutespmm_spmm_host.
+ * Waits for completion.  kernel_ms / exchange_ms (may be NULL): device time of the products / exchanges. */
+int cutespmm_spmm_sharded_host(cutespmm_plan_t *plan, cutespmm_comm_t *comm, const float *B_host_rows, uint64_t ldb,
+                               const uint64_t *b_bounds, float *C_host, uint64_t ldc, uint32_t N, void *stream,
+                               float *kernel_ms, float *exchange_ms);
+
+/* The collectives a sharded call issues for one contiguous K x N block of B, in order: transfer i sends
+ * count[i] floats starting at element offset[i] of the block from rank root[i] to every rank.  Returns the
+ * number of transfers in *n (at most `max` are written).  Pure bookkeeping: works on a stub communicator. */
+int cutespmm_sharded_transfers(const cutespmm_comm_t *comm, int b_mode, int root, uint64_t K, uint64_t N,
+                               const uint64_t *b_bounds, uint32_t max, int *roots, uint64_t *offsets, uint64_t *counts,
+                               uint32_t *n);
 
 /* ---- MatrixMarket loader -------------------------------------------------------------------
  * Replaces MTX_READER (IO.cu:1-88).  pattern_only != 0 reproduces the reference exactly: every

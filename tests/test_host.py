@@ -130,6 +130,27 @@ def test_mtx_reader_keeps_values_when_asked_and_reports_missing_file():
     assert e.value.status == -5
 
 
+def test_mtx_reader_rejects_malformed_files_with_a_message(tmp_path):
+    """Malformed files end in CUTESPMM_EIO with the path and line in the last-error string, never in an
+    out-of-range write: a mirrored entry outside a non-square "symmetric" matrix, and an entry line with one
+    number (which must not borrow the next line's first number)."""
+    f = tmp_path / "sym_nonsquare.mtx"
+    f.write_text("%%MatrixMarket matrix coordinate real symmetric\n3 40 2\n1 1 1.0\n2 35 1.0\n")
+    with pytest.raises(cs.CuteSpmmError) as e:
+        cs.MtxReader(f)
+    assert e.value.status == -5
+    msg = cs.lib.cutespmm_last_error().decode()
+    assert "sym_nonsquare.mtx" in msg and "line 4" in msg
+    f2 = tmp_path / "one_number.mtx"
+    f2.write_text("%%MatrixMarket matrix coordinate pattern general\n4 4 2\n3\n2 2\n")
+    with pytest.raises(cs.CuteSpmmError):
+        cs.MtxReader(f2)
+    assert "line 3" in cs.lib.cutespmm_last_error().decode()
+    with pytest.raises(cs.CuteSpmmError):
+        cs.MtxReader(tmp_path / "missing.mtx")
+    assert "cannot open" in cs.lib.cutespmm_last_error().decode()
+
+
 def test_partition_rows_balances_nnz_and_aligns():
     A = g.rmat(12, 8, seed=5)
     rp = A.row_ptr.numpy().astype(np.uint64)

@@ -134,3 +134,51 @@ def test_column_windows():
     for N in range(1, 300, 7):
         w = column_windows(N, 4, 32)
         assert w[0][0] == 0 and w[-1][1] == N and all(a[1] == b[0] for a, b in zip(w, w[1:])) and len(w) <= 4
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_sharded_entry_point_bookkeeping_with_a_stub_communicator(world):
+    """cutespmm_spmm_sharded / cutespmm_sharded_transfers through the C ABI with a communicator that records its
+    collectives instead of sending them: which rank sends which element range of B, for every exchange mode, and
+    the argument errors -- everything of the multi-GPU entry point that needs no GPU."""
+    import ctypes as C
+
+    import cutespmm_ae_b200 as cs
+    from cutespmm_ae_b200 import generators as g
+
+    A = g.rmat(10, 8, seed=79, values="uniform")
+    K, N = A.K, 24
+    bounds = cs.partition_rows(A.row_ptr, world, align_rows=16)
+    dummy = C.create_string_buffer(64)  # stands for device buffers: a stub communicator and a host-only plan touch neither
+    ptr = C.addressof(dummy)
+    even = np.minimum(np.arange(world + 1, dtype=np.uint64) * np.uint64(-(-K // world)), np.uint64(K))
+    ragged = even.copy()
+    ragged[1] = ragged[0]  # rank 0 holds no rows of B
+    for rank in range(world):
+        comm = cs.Comm.stub(world, rank)
+        mine = A.row_slice(int(bounds[rank]), int(bounds[rank + 1]))
+        plan = cs.Plan.from_csr(mine, host_only=True)
+
+        def call(mode, root=0, bb=None, ldb=N):
+            b = None if bb is None else np.ascontiguousarray(bb, dtype=np.uint64)
+            return cs.lib.cutespmm_spmm_sharded(plan._h, comm._h, mode, root, ptr, ldb, None if b is None else b.ctypes.data, ptr, N, N, None)
+
+        assert call(cs.B_RESIDENT) == 0 and comm.stub_log() == []
+        assert call(cs.B_FROM_ROOT, root=world - 1) == 0
+        assert comm.stub_log() == [(world - 1, 0, K * N)] == comm.transfers(cs.B_FROM_ROOT, K, N, root=world - 1)
+        assert call(cs.B_ROW_SHARDED, bb=even) == 0
+        want = [(r, int(even[r]) * N, int(even[r + 1] - even[r]) * N) for r in range(world) if even[r + 1] > even[r]]
+        assert comm.stub_log() == want == comm.transfers(cs.B_ROW_SHARDED, K, N, even)
+        assert sum(c for _, _, c in want) == K * N  # the slices tile B exactly
+        assert call(cs.B_ROW_SHARDED, bb=ragged) == 0
+        log = comm.stub_log()
+        assert [r for r, _, _ in log] == list(range(1, world)) and sum(c for _, _, c in log) == K * N
+        # errors: strided B cannot be exchanged, bounds must tile [0, K], the root must be a rank, bounds are required
+        assert call(cs.B_FROM_ROOT, ldb=N + 4) == -4
+        bad = even.copy()
+        bad[-1] -= 1
+        assert call(cs.B_ROW_SHARDED, bb=bad) == -1
+        assert call(cs.B_FROM_ROOT, root=world) == -1
+        assert call(cs.B_ROW_SHARDED) == -1
+        assert comm.stub_log() == []
+        comm.close()
