@@ -16,7 +16,7 @@ LIB_PATH = HERE / "liboracle.so"
 REF_PATH = HERE / "_ref" / "libcutespmm_ref.so"
 REF_LOADERS_PATH = HERE / "_ref" / "libcutespmm_ref_loaders.so"
 
-__all__ = ["build", "reference_root", "spmm_coo", "spmm_csr", "spmm_csr_rows", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
+__all__ = ["build", "reference_root", "set_threads", "spmm_coo", "spmm_csr", "spmm_csr_rows", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
 
 
 def reference_root() -> Path | None:
@@ -69,7 +69,18 @@ def _load():
         _lib.oracle_max_rel_err.restype = C.c_float
         _lib.oracle_rel_fro.argtypes = [vp, vp, C.c_uint64]
         _lib.oracle_rel_fro.restype = C.c_double
+        _lib.oracle_set_threads.argtypes = [C.c_int]
+        _lib.oracle_set_threads.restype = None
+        _lib.oracle_max_threads.argtypes = []
+        _lib.oracle_max_threads.restype = C.c_int
     return _lib
+
+
+def set_threads(n: int) -> int:
+    """Sets the OpenMP thread count of the oracle's loops; returns the count in force."""
+    lib = _load()
+    lib.oracle_set_threads(int(n))
+    return int(lib.oracle_max_threads())
 
 
 def _a(x, dt):
@@ -134,6 +145,11 @@ class Ref:
         L.ref_spmm_coo.restype = None
         L.ref_check_gemm_correctness_coo.argtypes = [vp, vp, C.c_uint32, C.c_uint32]
         L.ref_check_gemm_correctness_coo.restype = C.c_float
+        if hasattr(L, "ref_set_threads"):
+            L.ref_set_threads.argtypes = [C.c_int]
+            L.ref_set_threads.restype = None
+            L.ref_max_threads.argtypes = []
+            L.ref_max_threads.restype = C.c_int
         L.ref_mtx_open.argtypes = [C.c_char_p]
         L.ref_mtx_open.restype = vp
         for f in ("ref_mtx_M", "ref_mtx_K", "ref_mtx_nnz", "ref_hrpb_num_panels", "ref_hrpb_num_blocks"):
@@ -147,6 +163,10 @@ class Ref:
         L.ref_hrpb_copy.restype = None
         L.ref_hrpb_stream_words.argtypes = [vp]
         L.ref_hrpb_stream_words.restype = C.c_ulonglong
+
+    def set_threads(self, n: int) -> int:
+        self.lib.ref_set_threads(int(n))
+        return int(self.lib.ref_max_threads())
 
     def spmm_coo(self, rows, cols, vals, B, M, K):
         rows, cols, vals, B = _a(rows, np.uint32), _a(cols, np.uint32), _a(vals, np.float32), _a(B, np.float32)

@@ -34,7 +34,16 @@ static cudaError_t host_memcpy_(void *d, const void *s, size_t n, cudaMemcpyKind
 
 #include "data.cu" /* reference: HRPB, MTX_READER (IO.cu), spmm_coo (inc.h) */
 
+#include <omp.h>
+
 extern "C" {
+
+/* thread count of the reference's OpenMP regions, set by the caller instead of inherited */
+void ref_set_threads(int n)
+{
+    if (n > 0) omp_set_num_threads(n);
+}
+int ref_max_threads(void) { return omp_get_max_threads(); }
 
 /* inc.h:71-83 verbatim */
 void ref_spmm_coo(unsigned int *rows, unsigned int *cols, float *vals, float *B, float *C,

@@ -21,6 +21,29 @@
 #include <math.h>
 #include <stdint.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Thread count of the OpenMP loops below (a launcher may have exported
+ * OMP_NUM_THREADS=1 for its children; a timed CPU baseline states its own). */
+void oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+int oracle_max_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
 
 /* inc.h:71-83  (spmm_coo).  The reference opens an OpenMP region over the N
  * columns for every nonzero; the arithmetic per output element is a plain

@@ -195,3 +195,46 @@ def test_full_size_properties_without_cpu_product(oracle_mod):
     which = torch.unique(torch.cat([torch.randint(0, A.M, (1 << 16,), generator=gen), torch.nonzero(deg > 4096).flatten()]))
     want = oracle_mod.spmm_csr_rows(A.row_ptr.cpu(), A.cols.cpu(), A.vals.cpu(), B1.cpu().numpy(), which.numpy())
     assert oracle_mod.rel_fro(want, C1[which.cuda()].cpu().numpy()) <= REL_FRO_TOL_FP32
+
+
+def test_largest_configuration_at_its_own_size(oracle_mod):
+    """The R-MAT graph with 2^24 nodes at N = 128 on one GPU: B and C hold 2^31 elements each, so every element offset
+    above 2^31 - 1 needs the kernels' 64-bit address arithmetic (the reference computes these offsets in 32 bits,
+    kernel.cu:149,267,281).  Checked: 2^16 random rows plus every row with more than 4096 nonzeros against the CPU
+    oracle, and the column-sum identity 1^T (A B) = (A^T 1)^T B in fp64 as the whole-matrix checksum.  The plan is
+    built from the device-resident CSR."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 60 << 30:
+        pytest.skip("needs about 60 GB of free device memory")
+    w = g.WORKLOADS["rmat24"]
+    A = w["make"](device="cuda")
+    N = w["N"]
+    assert A.M == 1 << 24 and A.M * N == 1 << 31
+    p = cs.Plan.from_device_csr(A.M, A.K, A.row_ptr.to(torch.int32), A.cols.to(torch.int32), A.vals)
+    B = g.dense_operand(A.K, N, w["b_seed"], w["b_dist"], device="cuda")
+    C = torch.full((A.M, N), float("nan"), device="cuda")
+    p.spmm(B, C)
+    torch.cuda.synchronize()
+    assert p.device_status() == 0
+    # whole-matrix checksum, fp64, in row chunks (no 17 GB temporaries)
+    colsum = torch.zeros(A.K, dtype=torch.float64, device="cuda")
+    colsum.index_add_(0, A.cols.long(), A.vals.double())
+    expect = torch.zeros(N, dtype=torch.float64, device="cuda")
+    got = torch.zeros(N, dtype=torch.float64, device="cuda")
+    step = 1 << 20
+    for r in range(0, A.K, step):
+        expect += colsum[r : r + step] @ B[r : r + step].double()
+        got += C[r : r + step].sum(0, dtype=torch.float64)
+    assert float((got - expect).norm() / expect.norm()) < 1e-5
+    # sampled rows against the oracle: random rows over the whole range (high rows: offsets beyond 2^31) + every hub row
+    deg = A.row_ptr[1:] - A.row_ptr[:-1]
+    gen = torch.Generator().manual_seed(11)
+    hubs = torch.nonzero(deg > 4096).flatten().cpu()
+    assert hubs.numel() > 100
+    which = torch.unique(torch.cat([torch.randint(0, A.M, (1 << 16,), generator=gen), hubs, torch.tensor([A.M - 1])]))
+    assert int(which.max()) * N + N - 1 > 2**31 - 2**20  # the top of the offset range is sampled
+    got_rows = C[which.cuda()].cpu().numpy()
+    del C, colsum
+    want = oracle_mod.spmm_csr_rows(A.row_ptr.cpu(), A.cols.cpu(), A.vals.cpu(), B.cpu().numpy(), which.numpy())
+    assert not np.isnan(got_rows).any()
+    assert oracle_mod.rel_fro(want, got_rows) <= REL_FRO_TOL_FP32
