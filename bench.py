@@ -73,7 +73,7 @@ def parse_args():
     ap.add_argument("--no-per-config", action="store_true", help="skip the per_config block (1 GPU)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = chosen by operand size)")
-    ap.add_argument("--reorder", default="none", choices=["none", "hubs", "cluster"], help="plan-time reordering option")
+    ap.add_argument("--reorder", default="none", choices=["none", "cluster"], help="plan-time reordering option")
     return ap.parse_args()
 
 
@@ -312,11 +312,11 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------------
-def build_plan(cs, A_dev, path_name: str, reorder: str):
+def build_plan(cs, A_dev, path_name: str, reorder: str, flags: dict | None = None):
     """A plan over the rows of A_dev (CSR on the GPU), built from the device arrays where the device builder takes the
     request and by the host builder otherwise.  Returns (plan, milliseconds, builder name)."""
     path = {"auto": cs.PATH_AUTO, "rows": cs.PATH_ROWS, "brick": cs.PATH_BRICK, "slab": cs.PATH_SLAB}[path_name]
-    kw = {}
+    kw = dict(flags or {})
     if reorder != "none":
         kw["reorder"] = reorder
     torch.cuda.synchronize()

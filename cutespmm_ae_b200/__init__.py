@@ -26,6 +26,7 @@ __all__ = ["CuteSpmmError", "Plan", "Comm", "MtxReader", "partition_rows", "spmm
            "PATH_BRICK", "PATH_SLAB", "B_RESIDENT", "B_FROM_ROOT", "B_ROW_SHARDED"]
 
 PATH_AUTO, PATH_ROWS, PATH_BRICK, PATH_SLAB = 0, 1, 2, 3
+FLAG_ROUND_B_NEAREST = 1
 B_RESIDENT, B_FROM_ROOT, B_ROW_SHARDED = 0, 1, 2  # cutespmm_b_mode_t
 COMM_ID_BYTES = 128
 
@@ -122,7 +123,7 @@ class Plan:
         rp, cc, vv = _np(row_ptr, np.uint64), _np(cols, np.uint32), _np(vals, np.float32)
         if rp.shape[0] != M + 1:
             raise ValueError("row_ptr must have M+1 entries")
-        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, 1 if round_b_nearest else 0)
+        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, FLAG_ROUND_B_NEAREST if round_b_nearest else 0)
         fn = lib.cutespmm_plan_build_host if host_only else lib.cutespmm_plan_create
         _check(fn(C.byref(self._h), M, K, rp.ctypes.data, cc.ctypes.data, vv.ctypes.data, C.byref(opts)))
         self.M, self.K, self.nnz = M, K, int(rp[-1])
@@ -136,7 +137,8 @@ class Plan:
     def from_device_csr(cls, M: int, K: int, row_ptr, cols, vals, *, path: int = PATH_AUTO, split_nnz: int = 0,
                         tile_nnz: int = 0, stream=None) -> "Plan":
         """From CSR tensors that live on the GPU (row_ptr: M+1 int32, cols: nnz int32, vals: nnz float32): the
-        nonzeros are packed on the device (cutespmm_plan_create_device); the plan runs on the row kernel."""
+        nonzeros are packed, the 16-row panels analysed and the tensor-core bricks written on the device
+        (cutespmm_plan_create_device); path auto, rows or brick."""
         import torch
 
         for t, dt in ((row_ptr, torch.int32), (cols, torch.int32), (vals, torch.float32)):

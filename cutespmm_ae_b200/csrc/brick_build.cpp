@@ -13,23 +13,19 @@
 
 namespace cutespmm {
 
-void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
+// Which panels go to the brick kernel and which slots of the brick stream each of them owns: every offset follows
+// from the per-panel column counts because records have a fixed size.  Fills panel_first_brick / panel_last_brick /
+// num_bricks / brick_panels, returns the number of slots and lists the panels (ascending) in `which`.
+uint64_t layout_brick_slots(HostPlan &p, const std::vector<uint32_t> &panel_ncols, std::vector<uint32_t> &which)
 {
-    p.brick_cols.clear();
-    p.brick_recs.clear();
-    p.brick_rec_off.clear();
     p.panel_first_brick.clear();
     p.panel_last_brick.clear();
     p.num_bricks = 0;
     p.brick_panels = 0;
+    which.clear();
     const uint64_t P = p.num_panels();
-    // pass 1: which panels, how many slots each (records have a fixed size, so every offset follows from the counts)
-    std::vector<uint64_t> acol_off(P + 1, 0);
-    std::vector<uint32_t> which;  // panels routed to the brick kernel, ascending
-    for (uint64_t q = 0; q < P; ++q) {
-        acol_off[q + 1] = acol_off[q] + (uint64_t)((panel_ncols[q] + kBlockCols - 1) / kBlockCols) * kBlockCols;
+    for (uint64_t q = 0; q < P; ++q)
         if (p.row_path[q] == 1 && panel_ncols[q] != 0) which.push_back((uint32_t)q);
-    }
     p.brick_panels = which.size();
     p.panel_first_brick.resize(which.size());
     p.panel_last_brick.resize(which.size());
@@ -41,6 +37,21 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
         p.num_bricks += nbricks;
         slots += (nbricks + 3) / 4 * 4;  // groups of 4 slots start on a panel boundary; the surplus slots stay empty
     }
+    p.brick_slots = slots;
+    return slots;
+}
+
+void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
+{
+    p.brick_cols.clear();
+    p.brick_recs.clear();
+    p.brick_rec_off.clear();
+    const uint64_t P = p.num_panels();
+    std::vector<uint64_t> acol_off(P + 1, 0);
+    for (uint64_t q = 0; q < P; ++q)
+        acol_off[q + 1] = acol_off[q] + (uint64_t)((panel_ncols[q] + kBlockCols - 1) / kBlockCols) * kBlockCols;
+    std::vector<uint32_t> which;  // panels routed to the brick kernel, ascending
+    const uint64_t slots = layout_brick_slots(p, panel_ncols, which);
     p.brick_cols.assign(slots * kBrickCols, 0u);
     p.brick_recs.assign(slots * kBrickRecWords, 0u);  // empty slots: zero records
     p.brick_rec_off.resize(slots + 1);

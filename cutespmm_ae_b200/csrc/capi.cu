@@ -228,12 +228,66 @@ int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, 
     // nonzeros: packed on the device; the second status word collects the column-range check
     if ((e = cudaMalloc(&p->d_pairs, (h.nnz + 2) * sizeof(Pair))) != cudaSuccess) return bail(e, "packed nonzeros");
     by += (h.nnz + 2) * sizeof(Pair);
-    if ((e = launch_pack_pairs(cols_dev, vals_dev, p->d_pairs, h.nnz, (uint32_t)K, p->d_status + 1, p->sm_count, s)) != cudaSuccess)
-        return bail(e, "packing the nonzeros");
+    e = launch_pack_pairs(cols_dev, vals_dev, p->d_pairs, h.nnz, (uint32_t)K, p->d_status + 1, p->sm_count, s);
+    if (e != cudaSuccess) return bail(e, "packing the nonzeros");
+    // panel analysis and brick packing on the device (paths auto and brick); the per-panel column counts visit the host,
+    // where each panel's kernel is chosen and the brick slots and work lists are laid out
+    uint32_t *d_ncols = nullptr, *d_acols = nullptr, *d_which = nullptr;
+    auto drop_temps = [&]() {
+        for (uint32_t *t : {d_ncols, d_acols, d_which})
+            if (t) cudaFree(t);
+        d_ncols = d_acols = d_which = nullptr;
+    };
+    try {
+        if (h.opts.path != CUTESPMM_PATH_ROWS && h.nnz) {
+            const uint64_t P = h.num_panels();
+            std::vector<uint32_t> ncols(P);
+            if ((e = cudaMalloc(&d_ncols, P * sizeof(uint32_t))) != cudaSuccess || (e = cudaMalloc(&d_acols, h.nnz * sizeof(uint32_t))) != cudaSuccess ||
+                (e = launch_panel_columns(static_cast<const uint32_t *>(p->d_row_ptr), p->d_pairs, (uint32_t)M, (uint32_t)P, d_ncols, d_acols,
+                                          p->sm_count, s)) != cudaSuccess ||
+                (e = cudaMemcpyAsync(ncols.data(), d_ncols, P * sizeof(uint32_t), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+                (e = cudaStreamSynchronize(s)) != cudaSuccess) {
+                drop_temps();
+                return bail(e, "panel analysis");
+            }
+            if (h.opts.path == CUTESPMM_PATH_BRICK && std::find(ncols.begin(), ncols.end(), kPanelTooLarge) != ncols.end()) {
+                drop_temps();
+                delete p;
+                return fail(CUTESPMM_EUNSUPPORTED, "path brick on the device: a 16-row panel holds more than " + std::to_string(kDevPanelMax) +
+                                                       " nonzeros; use path auto (such panels run on the row kernel) or the host builder");
+            }
+            finish_device_plan(h, &ncols);
+            if (h.brick_panels) {
+                const uint64_t col_words = h.brick_slots * kBrickCols + 96, rec_words = h.brick_slots * kBrickRecWords;
+                if ((e = cudaMalloc(&p->d_bcols, col_words * 4)) != cudaSuccess || (e = cudaMalloc(&p->d_brecs, rec_words * 4)) != cudaSuccess ||
+                    (e = cudaMemsetAsync(p->d_bcols, 0, col_words * 4, s)) != cudaSuccess || (e = cudaMemsetAsync(p->d_brecs, 0, rec_words * 4, s)) != cudaSuccess ||
+                    (e = cudaMalloc(&d_which, h.brick_panels * sizeof(uint32_t))) != cudaSuccess ||
+                    (e = cudaMemcpyAsync(d_which, h.brick_panel_ids.data(), h.brick_panels * sizeof(uint32_t), cudaMemcpyHostToDevice, s)) != cudaSuccess ||
+                    (e = upload(h.panel_first_brick, &p->d_panel_first, by)) != cudaSuccess || (e = upload(h.panel_last_brick, &p->d_panel_last, by)) != cudaSuccess ||
+                    (e = launch_brick_fill(static_cast<const uint32_t *>(p->d_row_ptr), p->d_pairs, (uint32_t)M, d_which,
+                                           static_cast<const uint32_t *>(p->d_panel_first), static_cast<const uint32_t *>(p->d_panel_last),
+                                           (uint32_t)h.brick_panels, d_ncols, d_acols, static_cast<uint32_t *>(p->d_bcols),
+                                           static_cast<uint32_t *>(p->d_brecs), p->sm_count, s)) != cudaSuccess ||
+                    (e = cudaStreamSynchronize(s)) != cudaSuccess) {
+                    drop_temps();
+                    return bail(e, "brick packing");
+                }
+                by += (col_words + rec_words) * 4;
+            }
+            drop_temps();
+        } else {
+            finish_device_plan(h, nullptr);
+        }
+    } catch (const std::bad_alloc &) {
+        drop_temps();
+        delete p;
+        return fail(CUTESPMM_ENOMEM, "host allocation failed while building the plan");
+    }
     if ((e = upload(h.tiles, &p->d_tiles, by)) != cudaSuccess || (e = upload(h.chunks, &p->d_chunks, by)) != cudaSuccess ||
-        (e = upload(h.long_rows, &p->d_long_rows, by)) != cudaSuccess)
+        (e = upload(h.long_rows, &p->d_long_rows, by)) != cudaSuccess || (e = upload(h.tiles_all, &p->d_tiles_all, by)) != cudaSuccess ||
+        (e = upload(h.chunks_all, &p->d_chunks_all, by)) != cudaSuccess || (e = upload(h.long_rows_all, &p->d_long_rows_all, by)) != cudaSuccess)
         return bail(e, "uploading the work lists");
-    const uint64_t scratch = (uint64_t)h.chunks.size() * kScratchCols * sizeof(float);
+    const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
     if (scratch) {
         if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) return bail(e, "scratch");
         by += scratch;
@@ -280,20 +334,54 @@ int cutespmm_plan_info(const cutespmm_plan_t *p, cutespmm_plan_info_t *info)
     return CUTESPMM_OK;
 }
 
-static const char *kNoViews = "a plan built on the device has no panel views: the column analysis runs in the host builder only";
+static const char *kNoViews =
+    "this plan was built on the device without the panel analysis (path rows, or a panel beyond the device sort): "
+    "the panel views come with path auto / brick, or from the host builder";
+
+static bool device_plan_has_views(const cutespmm_plan *p)
+{
+    return !p->host.device_built || p->host.blocked_row_ptr.size() == p->host.num_panels() + 1;
+}
 
 int cutespmm_plan_blocked_row_ptr(const cutespmm_plan_t *p, uint32_t *out)
 {
     if (!p || !out) return fail(CUTESPMM_EINVAL, "null argument");
-    if (p->host.device_built) return fail(CUTESPMM_EUNSUPPORTED, kNoViews);
+    if (!device_plan_has_views(p)) return fail(CUTESPMM_EUNSUPPORTED, kNoViews);
     std::memcpy(out, p->host.blocked_row_ptr.data(), p->host.blocked_row_ptr.size() * sizeof(uint32_t));
     return CUTESPMM_OK;
 }
 int cutespmm_plan_active_cols(const cutespmm_plan_t *p, uint32_t *out)
 {
     if (!p || !out) return fail(CUTESPMM_EINVAL, "null argument");
-    if (p->host.device_built) return fail(CUTESPMM_EUNSUPPORTED, kNoViews);
-    std::memcpy(out, p->host.active_cols.data(), p->host.active_cols.size() * sizeof(uint32_t));
+    if (!device_plan_has_views(p)) return fail(CUTESPMM_EUNSUPPORTED, kNoViews);
+    const HostPlan &h = p->host;
+    if (!h.device_built) {
+        std::memcpy(out, h.active_cols.data(), h.active_cols.size() * sizeof(uint32_t));
+        return CUTESPMM_OK;
+    }
+    // a device-built plan does not keep the column lists: run the panel analysis again and bring them back
+    const uint64_t P = h.num_panels();
+    if (h.nnz == 0 || P == 0) return CUTESPMM_OK;
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (cur != p->device) cudaSetDevice(p->device);
+    uint32_t *d_ncols = nullptr, *d_acols = nullptr;
+    std::vector<uint32_t> ncols(P), acols(h.nnz);
+    cudaError_t e;
+    if ((e = cudaMalloc(&d_ncols, P * sizeof(uint32_t))) == cudaSuccess && (e = cudaMalloc(&d_acols, h.nnz * sizeof(uint32_t))) == cudaSuccess &&
+        (e = launch_panel_columns(static_cast<const uint32_t *>(p->d_row_ptr), p->d_pairs, (uint32_t)h.M, (uint32_t)P, d_ncols, d_acols, p->sm_count, nullptr)) == cudaSuccess &&
+        (e = cudaMemcpy(ncols.data(), d_ncols, P * sizeof(uint32_t), cudaMemcpyDeviceToHost)) == cudaSuccess)
+        e = cudaMemcpy(acols.data(), d_acols, h.nnz * sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (d_ncols) cudaFree(d_ncols);
+    if (d_acols) cudaFree(d_acols);
+    if (cur != p->device && cur >= 0) cudaSetDevice(cur);
+    if (e != cudaSuccess) return fail_cuda(e, "panel analysis");
+    for (uint64_t q = 0; q < P; ++q) {  // per panel: its columns, zero-padded to a multiple of 16 (data.cu:160,204-209)
+        uint32_t *dst = out + (uint64_t)h.blocked_row_ptr[q] * kBlockCols;
+        const uint32_t width = (h.blocked_row_ptr[q + 1] - h.blocked_row_ptr[q]) * kBlockCols;
+        const uint32_t *src = acols.data() + h.row_ptr[q * kPanelRows];
+        for (uint32_t c = 0; c < width; ++c) dst[c] = c < ncols[q] ? src[c] : 0u;
+    }
     return CUTESPMM_OK;
 }
 int cutespmm_plan_decode_csr(const cutespmm_plan_t *p, uint64_t *rowPtr, uint32_t *cols, float *vals)

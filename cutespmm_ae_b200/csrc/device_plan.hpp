@@ -45,7 +45,6 @@ cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
 int rows_kernel_count(const RowsArgs &a);
 
 // Arguments of the tensor-core brick kernel.
-constexpr int kBrickWarps = 15;  // warps per block; each is an independent pipeline over its own brick range
 struct BrickArgs {
     const uint32_t *cols;         // 8 columns per brick slot (+ readable slack of a few groups behind the end)
     const uint32_t *recs;         // brick records (map, flags, panel, values in fragment order): slot k at word k * kBrickRecWords
@@ -86,5 +85,15 @@ bool slab_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const 
 // pairs[j] = (cols[j], bits of vals[j]) for j < nnz, two zero pairs behind; *bad |= 1 when a column is >= K
 cudaError_t launch_pack_pairs(const uint32_t *cols, const float *vals, void *pairs, uint64_t nnz, uint32_t K, uint32_t *bad, int sm_count,
                               cudaStream_t s);
+// Device side of the panel analysis and of the brick packing (device_build.cu).  kDevPanelMax: nonzeros of a panel the
+// shared-memory sort takes (32 KB of column indices); 16 rows of at most kMaxSplitNnz nonzeros fit, so every panel
+// left out holds a long row and runs on the row kernel whatever its density.
+constexpr uint32_t kDevPanelMax = 8192;
+cudaError_t launch_panel_columns(const uint32_t *row_ptr, const void *pairs, uint32_t M, uint32_t num_panels, uint32_t *ncols,
+                                 uint32_t *acols, int sm_count, cudaStream_t s);
+cudaError_t launch_brick_fill(const uint32_t *row_ptr, const void *pairs, uint32_t M, const uint32_t *which,
+                              const uint32_t *first_slot, const uint32_t *last_slot, uint32_t num_brick_panels, const uint32_t *ncols,
+                              const uint32_t *acols, uint32_t *bcols, uint32_t *brecs, int sm_count, cudaStream_t s);
+
 
 }  // namespace cutespmm

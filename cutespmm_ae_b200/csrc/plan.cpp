@@ -22,6 +22,7 @@
 namespace cutespmm {
 
 void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols);  // brick_build.cpp
+uint64_t layout_brick_slots(HostPlan &p, const std::vector<uint32_t> &panel_ncols, std::vector<uint32_t> &which);
 void build_slab_part(HostPlan &p);                                             // slab_build.cpp
 
 static void fill_default_options(cutespmm_options_t &o, const cutespmm_options_t *in)
@@ -97,6 +98,7 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
     tiles.clear();
     chunks.clear();
     long_rows.clear();
+    std::vector<Tile> row_tiles;
     uint64_t q = 0;
     while (q < P) {
         if (!all_rows && p.row_path[q]) { ++q; continue; }
@@ -106,7 +108,7 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
         uint64_t r = q * kPanelRows;
         uint64_t begin = r, cost = 0;
         auto close = [&](uint64_t end) {
-            if (end > begin) tiles.push_back(Tile{(uint32_t)begin, (uint32_t)end, p.row_ptr[begin], p.row_ptr[end]});
+            if (end > begin) row_tiles.push_back(Tile{(uint32_t)begin, (uint32_t)end, p.row_ptr[begin], p.row_ptr[end]});
             cost = 0;
         };
         for (; r < r_end; ++r) {
@@ -135,6 +137,31 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
         close(r_end);
         q = q1;
     }
+    tiles = std::move(row_tiles);
+}
+
+// Which kernel executes each 16-row panel (row_path: 0 = row kernel, 1 = brick kernel), from the panel's nonzero
+// count, its number of distinct columns and its longest row.  A panel whose column count is kPanelTooLarge was not
+// analysed (the device builder skips panels beyond its shared-memory sort) and stays with the row kernel.
+void choose_panel_paths(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
+{
+    const uint64_t P = p.num_panels();
+    p.row_path.assign(P, 0);
+    if (p.opts.path == CUTESPMM_PATH_ROWS) return;
+#pragma omp parallel for schedule(static)
+    for (int64_t q = 0; q < (int64_t)P; ++q) {
+        const uint64_t r0 = (uint64_t)q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
+        const uint32_t n = p.row_ptr[r1] - p.row_ptr[r0];
+        if (n == 0 || panel_ncols[q] == kPanelTooLarge) continue;  // empty panels: the row kernel writes their zeros
+        if (p.opts.path == CUTESPMM_PATH_BRICK) { p.row_path[q] = 1; continue; }
+        if (p.opts.path == CUTESPMM_PATH_SLAB) continue;  // decided per 128-row panel by the caller
+        // AUTO: fill of the panel's 16 x (8*ceil(ncols/8)) dense image
+        const uint32_t padded = (panel_ncols[q] + kBrickCols - 1) / kBrickCols * kBrickCols;
+        const float fill = (float)n / (float)(kPanelRows * padded);
+        bool long_row = false;
+        for (uint64_t r = r0; r < r1; ++r) long_row |= (p.row_ptr[r + 1] - p.row_ptr[r]) > p.opts.split_nnz;
+        p.row_path[q] = (fill >= p.opts.brick_density && !long_row) ? 1 : 0;
+    }
 }
 
 int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vector<uint32_t> &&row_ptr,
@@ -143,12 +170,12 @@ int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vecto
     if (M >= (1ull << 32) - kPanelRows || K >= (1ull << 32)) { err = "M and K must be below 2^32"; return CUTESPMM_EUNSUPPORTED; }
     if (row_ptr.size() != M + 1) { err = "rowPtr must have M+1 entries"; return CUTESPMM_EINVAL; }
     if (row_ptr[0] != 0) { err = "rowPtr[0] must be 0"; return CUTESPMM_EINVAL; }
-    if (opts && opts->path != CUTESPMM_PATH_AUTO && opts->path != CUTESPMM_PATH_ROWS) {
-        err = "a plan built on the device runs on the row kernel only (path auto or rows)";
+    if (opts && opts->path == CUTESPMM_PATH_SLAB) {
+        err = "the slab path is built by the host builder only (cutespmm_plan_create)";
         return CUTESPMM_EUNSUPPORTED;
     }
+    if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
     fill_default_options(p.opts, opts);
-    p.opts.path = CUTESPMM_PATH_ROWS;
     int bad = 0;
 #pragma omp parallel for schedule(static) reduction(| : bad)
     for (int64_t r = 0; r < (int64_t)M; ++r) bad |= row_ptr[r + 1] < row_ptr[r];
@@ -158,8 +185,27 @@ int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vecto
     p.device_built = true;
     p.row_path.assign(p.num_panels(), 0);
     p.slab_path.assign((M + kSlabRows - 1) / kSlabRows, 0);
-    build_tiles(p, false, p.tiles, p.chunks, p.long_rows);
     return CUTESPMM_OK;
+}
+
+void finish_device_plan(HostPlan &p, const std::vector<uint32_t> *panel_ncols)
+{
+    if (panel_ncols) {
+        choose_panel_paths(p, *panel_ncols);
+        // the HRPB view blockedRowPtr follows from the counts -- unless a panel was left out of the analysis
+        bool complete = true;
+        p.blocked_row_ptr.assign(p.num_panels() + 1, 0);
+        for (uint64_t q = 0; q < p.num_panels(); ++q) {
+            complete &= (*panel_ncols)[q] != kPanelTooLarge;
+            p.blocked_row_ptr[q + 1] = p.blocked_row_ptr[q] + (complete ? ((*panel_ncols)[q] + kBlockCols - 1) / kBlockCols : 0);
+        }
+        if (!complete) p.blocked_row_ptr.clear();
+        std::vector<uint32_t> which;
+        layout_brick_slots(p, *panel_ncols, which);
+        p.brick_panel_ids = std::move(which);
+    }
+    build_tiles(p, false, p.tiles, p.chunks, p.long_rows);
+    if (p.brick_panels) build_tiles(p, true, p.tiles_all, p.chunks_all, p.long_rows_all);
 }
 
 int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
@@ -211,25 +257,7 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
 
     const std::vector<uint32_t> panel_ncols = analyze_panels(p);
 
-    // path per panel
-    const uint64_t P = p.num_panels();
-    p.row_path.assign(P, 0);
-    if (p.opts.path != CUTESPMM_PATH_ROWS) {
-#pragma omp parallel for schedule(static)
-        for (int64_t q = 0; q < (int64_t)P; ++q) {
-            const uint64_t r0 = (uint64_t)q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
-            const uint32_t n = p.row_ptr[r1] - p.row_ptr[r0];
-            if (n == 0) continue;  // empty panels: the row kernel writes their zeros
-            if (p.opts.path == CUTESPMM_PATH_BRICK) { p.row_path[q] = 1; continue; }
-            if (p.opts.path == CUTESPMM_PATH_SLAB) continue;  // decided per 128-row panel below
-            // AUTO: fill of the panel's 16 x (8*ceil(ncols/8)) dense image
-            const uint32_t padded = (panel_ncols[q] + kBrickCols - 1) / kBrickCols * kBrickCols;
-            const float fill = (float)n / (float)(kPanelRows * padded);
-            bool long_row = false;
-            for (uint64_t r = r0; r < r1; ++r) long_row |= (p.row_ptr[r + 1] - p.row_ptr[r]) > p.opts.split_nnz;
-            p.row_path[q] = (fill >= p.opts.brick_density && !long_row) ? 1 : 0;
-        }
-    }
+    choose_panel_paths(p, panel_ncols);
     // 128-row panels for the slab (tcgen05) kernel; their 16-row panels are marked 2
     const uint64_t SP = (p.M + kSlabRows - 1) / kSlabRows;
     p.slab_path.assign(SP, 0);

@@ -34,6 +34,8 @@ struct Tile {
     uint32_t row_begin, row_end, pair_begin, pair_end;
 };
 
+constexpr uint32_t kPanelTooLarge = 0xffffffffu;  // column count of a panel the device builder did not analyse
+
 // A chunk of a long row: nonzeros [j0, j1) of `row`; its partial result is row `slot` of the scratch.
 struct Chunk {
     uint32_t row, j0, j1, slot;
@@ -100,6 +102,8 @@ struct HostPlan {
     std::vector<uint32_t> panel_last_brick;   // per brick panel: one past the slot of its last brick
     uint64_t num_bricks = 0;
     uint64_t brick_panels = 0;
+    std::vector<uint32_t> brick_panel_ids;    // device-built plans: the panel index of every brick panel, ascending
+    uint64_t brick_slots = 0;                 // slots of the brick stream (bricks plus the empty slots that pad panels to groups of 4)
 
     // ---- slab kernel (tcgen05): 128-row panels, one record per step of 8 active columns ----
     // Step t owns columns slab_cols[8t .. 8t+8) and the record at 16-byte unit slab_rec_off[t] of slab_recs:
@@ -130,6 +134,11 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
 // set: the HRPB views and the host-side decode are not available for such a plan.
 int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vector<uint32_t> &&row_ptr,
                                  const cutespmm_options_t *opts, std::string &err);
+
+// Second half of a device-built plan: with the per-panel distinct-column counts (nullptr: row kernel only) chooses
+// each panel's kernel, lays out the brick slots and cuts the work lists.
+void finish_device_plan(HostPlan &p, const std::vector<uint32_t> *panel_ncols);
+void choose_panel_paths(HostPlan &p, const std::vector<uint32_t> &panel_ncols);
 
 // Rebuilds CSR from the packed arrays (rows-kernel part from pairs, brick part from maps + values).
 void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float *vals);

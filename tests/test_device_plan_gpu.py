@@ -1,6 +1,6 @@
-"""cutespmm_plan_create_device: a plan built from CSR arrays that live on the GPU must give the row kernel's
-result bit for bit (same work lists, same kernel), decode to the arrays it was given, and refuse what the
-device builder does not do."""
+"""cutespmm_plan_create_device: a plan built from CSR arrays that live on the GPU must give the host-built plan's
+result bit for bit (same work lists, same packed bricks, same kernels), decode to the arrays it was given, show the
+same panel views as the reference's preprocessing, and refuse what the device builder does not do."""
 import numpy as np
 import pytest
 import torch
@@ -20,7 +20,7 @@ def _dev(A):
 def test_device_built_plan_equals_host_built_rows_plan(oracle_mod, make, N):
     A = make()
     rp, cols, vals = _dev(A)
-    pd = cs.Plan.from_device_csr(A.M, A.K, rp, cols, vals)
+    pd = cs.Plan.from_device_csr(A.M, A.K, rp, cols, vals, path=cs.PATH_ROWS)
     ph = cs.Plan.from_csr(A, path=cs.PATH_ROWS)
     id_, ih = pd.info(), ph.info()
     for k in ("M", "K", "nnz", "num_tiles", "num_long_rows", "num_chunks"):
@@ -60,7 +60,7 @@ def test_device_builder_refusals():
     A = g.stencil9(16)
     rp, cols, vals = _dev(A)
     with pytest.raises(cs.CuteSpmmError) as e:
-        cs.Plan.from_device_csr(A.M, A.K, rp, cols, vals, path=cs.PATH_BRICK)
+        cs.Plan.from_device_csr(A.M, A.K, rp, cols, vals, path=cs.PATH_SLAB)  # the slab format is built on the host only
     assert e.value.status == -4
     bad_cols = cols.clone()
     bad_cols[5] = A.K  # out of range
@@ -72,7 +72,62 @@ def test_device_builder_refusals():
     with pytest.raises(cs.CuteSpmmError) as e:
         cs.Plan.from_device_csr(A.M, A.K, bad_rp, cols, vals)
     assert e.value.status == -1
-    p = cs.Plan.from_device_csr(A.M, A.K, rp, cols, vals)
+    p = cs.Plan.from_device_csr(A.M, A.K, rp, cols, vals, path=cs.PATH_ROWS)  # no panel analysis: no panel views
     with pytest.raises(cs.CuteSpmmError) as e:
         p.blocked_row_ptr()
     assert e.value.status == -4
+    # a panel beyond the device sort: one row of 9000 nonzeros among short ones
+    hrp = torch.zeros(65, dtype=torch.int64)
+    hrp[20:] = 9000
+    hrp[21:] += torch.arange(1, 45) * 3
+    hub = g.CsrMatrix(64, 10000, hrp, torch.cat([torch.arange(9000), torch.arange(132) * 7]).to(torch.int32), torch.ones(9132))
+    with pytest.raises(cs.CuteSpmmError) as e:
+        cs.Plan.from_device_csr(hub.M, hub.K, *_dev(hub), path=cs.PATH_BRICK)
+    assert e.value.status == -4
+    auto = cs.Plan.from_device_csr(hub.M, hub.K, *_dev(hub))  # auto: such a panel simply stays with the row kernel
+    assert auto.info()["num_long_rows"] == 1
+    with pytest.raises(cs.CuteSpmmError):  # ... and the panel views are incomplete
+        auto.blocked_row_ptr()
+
+
+@pytest.mark.parametrize("make,Ns,path", [(lambda: g.stencil9(96), [128, 64, 32, 100], cs.PATH_AUTO),
+                                           (lambda: g.elasticity3d(12, 3, 5), [128, 256], cs.PATH_AUTO),
+                                           (lambda: g.stencil9(512, 512, 1002), [128], cs.PATH_AUTO),
+                                           (lambda: g.uniform_random(777, 555, 9, seed=6), [64], cs.PATH_BRICK),
+                                           (lambda: g.rmat(13, 8, seed=12, values="uniform"), [128], cs.PATH_AUTO)])
+def test_device_built_tensor_core_plan_equals_host_built(oracle_mod, make, Ns, path):
+    """Panel analysis and brick packing on the device: same choice of kernel per panel, same brick stream (bit-identical
+    product), same panel views as the host builder, which is itself pinned to the reference's HRPB."""
+    A = make()
+    pd = cs.Plan.from_device_csr(A.M, A.K, *_dev(A), path=path)
+    ph = cs.Plan.from_csr(A, path=path)
+    id_, ih = pd.info(), ph.info()
+    for k in ("M", "K", "nnz", "num_panels", "num_tiles", "num_long_rows", "num_chunks", "brick_panels", "num_bricks"):
+        assert id_[k] == ih[k], k
+    if path == cs.PATH_BRICK or "stencil" in A.name or "elasticity" in A.name:
+        assert id_["num_bricks"] > 0
+    for N in Ns:
+        B = g.dense_operand(A.K, N, 19, device="cuda")
+        Cd, Ch = pd.spmm(B), ph.spmm(B)
+        torch.cuda.synchronize()
+        assert torch.equal(Cd, Ch), N
+    ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B.cpu().numpy(), A.M, A.K)
+    assert oracle_mod.rel_fro(ref, Cd.cpu().numpy()) <= 1e-3
+    assert pd.device_status() == 0
+    if int((A.row_ptr[1:] - A.row_ptr[:-1]).max()) * 16 <= 8192:  # every panel within the device sort: the views exist
+        assert id_["num_blocks"] == ih["num_blocks"]
+        assert np.array_equal(pd.blocked_row_ptr(), ph.blocked_row_ptr())
+        assert np.array_equal(pd.active_cols(), ph.active_cols())
+
+
+@pytest.mark.parametrize("name", ["stencil_16x16", "elasticity_4", "uniform_256"])
+def test_device_built_views_match_the_reference_preprocessing(name):
+    """blockedRowPtr / activeCols of a device-built plan against what the reference's HRPB produced (golden vectors)."""
+    from conftest import load_golden
+
+    gd = load_golden(name)
+    M, K = int(gd["M"]), int(gd["K"])
+    p = cs.Plan.from_device_csr(M, K, torch.from_numpy(gd["row_ptr"].astype(np.int32)).cuda(), torch.from_numpy(gd["cols"].astype(np.int32)).cuda(),
+                                torch.from_numpy(gd["vals"]).cuda())
+    assert np.array_equal(p.blocked_row_ptr(), gd["blocked_row_ptr"])
+    assert np.array_equal(p.active_cols(), gd["active_cols"])

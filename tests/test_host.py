@@ -163,3 +163,4 @@ def test_partition_rows_balances_nnz_and_aligns():
     # more parts than panels: empty ranges allowed, still monotone
     b = cs.partition_rows(np.array([0, 1, 2], np.uint64), 4, align_rows=16)
     assert b[0] == 0 and b[-1] == 2 and np.all(np.diff(b.astype(np.int64)) >= 0)
+
