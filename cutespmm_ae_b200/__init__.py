@@ -27,6 +27,7 @@ __all__ = ["CuteSpmmError", "Plan", "Comm", "MtxReader", "partition_rows", "spmm
 
 PATH_AUTO, PATH_ROWS, PATH_BRICK, PATH_SLAB = 0, 1, 2, 3
 FLAG_ROUND_B_NEAREST = 1
+REORDER_NONE, REORDER_CLUSTER_ROWS = 0, 1
 B_RESIDENT, B_FROM_ROOT, B_ROW_SHARDED = 0, 1, 2  # cutespmm_b_mode_t
 COMM_ID_BYTES = 128
 
@@ -39,7 +40,8 @@ class CuteSpmmError(RuntimeError):
 
 class Options(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("path", C.c_uint32), ("split_nnz", C.c_uint32),
-                ("tile_nnz", C.c_uint32), ("brick_density", C.c_float), ("flags", C.c_uint32), ("reserved", C.c_uint32 * 2)]
+                ("tile_nnz", C.c_uint32), ("brick_density", C.c_float), ("flags", C.c_uint32), ("reorder", C.c_uint32),
+                ("reserved", C.c_uint32)]
 
 
 class PlanInfo(C.Structure):
@@ -118,12 +120,13 @@ class Plan:
     of SPMM_TC (spmm.cu:691-822).  `host_only=True` builds the plan without touching CUDA."""
 
     def __init__(self, M: int, K: int, row_ptr, cols, vals, *, path: int = PATH_AUTO, split_nnz: int = 0,
-                 tile_nnz: int = 0, brick_density: float = 0.0, round_b_nearest: bool = False, host_only: bool = False):
+                 tile_nnz: int = 0, brick_density: float = 0.0, round_b_nearest: bool = False, reorder: int | str = 0, host_only: bool = False):
         self._h = C.c_void_p()
         rp, cc, vv = _np(row_ptr, np.uint64), _np(cols, np.uint32), _np(vals, np.float32)
         if rp.shape[0] != M + 1:
             raise ValueError("row_ptr must have M+1 entries")
-        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, FLAG_ROUND_B_NEAREST if round_b_nearest else 0)
+        reorder = {"none": REORDER_NONE, "cluster": REORDER_CLUSTER_ROWS}.get(reorder, reorder)
+        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, FLAG_ROUND_B_NEAREST if round_b_nearest else 0, reorder)
         fn = lib.cutespmm_plan_build_host if host_only else lib.cutespmm_plan_create
         _check(fn(C.byref(self._h), M, K, rp.ctypes.data, cc.ctypes.data, vv.ctypes.data, C.byref(opts)))
         self.M, self.K, self.nnz = M, K, int(rp[-1])

@@ -13,10 +13,9 @@
 //     drains a depth-2 cp.async pipeline and runs __syncthreads after every block of 16 columns
 //     (kernel.cu:220-222); here no two warps ever wait for each other;
 //   * the eight gathered rows of B of a brick arrive by two TMA gather4 loads (four rows of the slab
-//     each, through a tensor map over B), the brick's record by 16-byte asynchronous copies of the
-//     lanes (the LSU path: measured, the TMA unit's instruction rate is what bounds this kernel, so
-//     it is kept for the gathers); the copies for brick k + kStages - 1 are issued before brick k is
-//     computed, across panel boundaries, so the gather latency is hidden without occupancy;
+//     each, through a tensor map over B), the brick's record by a bulk copy; the
+//     copies for brick k + kStages - 1 are issued before brick k is computed, across panel
+//     boundaries, so the gather latency is hidden without occupancy;
 //   * a brick is 16 x 8 and maps onto mma.m16n8k8 (the reference issues m16n8k4 on 16 x 4 bricks);
 //     a warp covers the whole 128-column slab (16 accumulator tiles), so a brick is expanded once,
 //     not once per warp of a block;
@@ -42,11 +41,6 @@ namespace {
 constexpr int kStages = 3;
 constexpr int kRecWords = kBrickRecWords;  // header + a full brick of values
 
-// Warps per block (one block per SM): as many independent pipelines as registers and shared memory allow for the
-// slab width -- a narrower slab needs fewer accumulators and smaller stages, and the cost of a brick that does not
-// depend on N (issue, wait, A fragment) is latency that more pipelines hide.
-template <int NT> struct Warps { static constexpr int value = NT >= 16 ? 15 : NT >= 8 ? 20 : 28; };
-
 template <int NT> struct StageLayout {
     static constexpr int kSlab = 8 * NT;         // columns of B / C a warp covers
     static constexpr int kStride = kSlab + 8;    // floats between consecutive B rows in shared memory
@@ -57,16 +51,14 @@ template <int NT> struct StageLayout {
     static constexpr int kWarpBytes = (kStages * kStageBytes + kStages * 8 + 127) / 128 * 128;
     static_assert(kBBytes % 128 == 0 && kHalfBytes % 128 == 0 && (kRecWords * 4) % 16 == 0, "gather4 destinations must be 128-byte aligned");
     static_assert(kStride % 32 == 8, "the B-fragment reads are conflict-free only with this stride");
-    static_assert(Warps<NT>::value * kWarpBytes <= 227 * 1024, "a block's stages must fit the shared memory of an SM");
 };
 
 // ROUND_B: round the elements of B to tf32 to nearest (cvt.rna, what the reference does,
 // kernel.cu:35) instead of letting the tensor core drop the low 13 mantissa bits.
 template <int NT, bool ROUND_B>
-__global__ void __launch_bounds__(Warps<NT>::value * 32, 1) spmm_brick_kernel(const __grid_constant__ CUtensorMap tmap_b, BrickArgs a)
+__global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const __grid_constant__ CUtensorMap tmap_b, BrickArgs a)
 {
     using L = StageLayout<NT>;
-    constexpr int kBrickWarps = Warps<NT>::value;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -83,7 +75,7 @@ __global__ void __launch_bounds__(Warps<NT>::value * 32, 1) spmm_brick_kernel(co
     auto stage_b = [&](int s) { return reinterpret_cast<float *>(mine + s * L::kBBytes); };
     auto stage_rec = [&](int s) { return reinterpret_cast<uint32_t *>(mine + kStages * L::kBBytes + s * (kRecWords * 4)); };
     if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) ptx::mbar_init(&full[s], 1 + 32);  // lane 8's expect-tx arrival + one arrival per lane for its part of the record
+        for (int s = 0; s < kStages; ++s) ptx::mbar_init(&full[s], 1);
         ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -126,18 +118,13 @@ __global__ void __launch_bounds__(Warps<NT>::value * 32, 1) spmm_brick_kernel(co
         }
         const int s = is;
         is = (is + 1 == kStages) ? 0 : is + 1;
-        // every lane copies its 16 bytes of the brick's values (its A fragment) and lanes 0-1 the header; lane 8 announces
-        // the bytes of the B tile; lanes 2j and 2j+1, which hold the columns of slot j = k & 3, start one gather4 load of
-        // four rows of B each straight from their registers
+        // lane 8 starts the copy of the record; lanes 2j and 2j+1, which hold the columns of slot j = k & 3,
+        // start one gather4 load of four rows of B each straight from their registers
         const uint32_t j = k & 3;
-        {
-            const uint32_t *src = a.recs + (size_t)k * kRecWords;
-            uint32_t *dst = stage_rec(s);
-            ptx::cp_async_16(dst + kBrickRecHeaderWords + 4 * lane, src + kBrickRecHeaderWords + 4 * lane);
-            if (lane < 2) ptx::cp_async_16(dst + 4 * lane, src + 4 * lane);
-            ptx::cp_async_arrive(&full[s]);
+        if (lane == 8) {
+            ptx::mbar_expect_tx(&full[s], (uint32_t)L::kBBytes + kRecWords * 4u);
+            ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)k * kRecWords, kRecWords * 4u, &full[s]);
         }
-        if (lane == 8) ptx::mbar_expect_tx(&full[s], (uint32_t)L::kBBytes);
         if ((uint32_t)(lane >> 1) == j)
             ptx::tma_gather4(reinterpret_cast<unsigned char *>(stage_b(s)) + (lane & 1) * L::kHalfBytes, &tmap_b, (int)n0, (int)mc_cur.x,
                              (int)mc_cur.y, (int)mc_cur.z, (int)mc_cur.w, &full[s]);
@@ -198,7 +185,9 @@ __global__ void __launch_bounds__(Warps<NT>::value * 32, 1) spmm_brick_kernel(co
         }
         if (info.x & 1u) {  // last brick of the panel: write its 16 x SLAB tile of C
             const uint64_t r_lo = (uint64_t)info.y * kPanelRows + g, r_hi = r_lo + 8;
-            float *c_lo = a.C + r_lo * a.ldc + n0 + 2 * t, *c_hi = a.C + r_hi * a.ldc + n0 + 2 * t;
+            // a reordered plan writes every row to its place in the caller's C
+            const uint64_t o_lo = a.row_map && r_lo < a.M ? __ldg(a.row_map + r_lo) : r_lo, o_hi = a.row_map && r_hi < a.M ? __ldg(a.row_map + r_hi) : r_hi;
+            float *c_lo = a.C + o_lo * a.ldc + n0 + 2 * t, *c_hi = a.C + o_hi * a.ldc + n0 + 2 * t;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 if (r_lo < a.M) __stcs(reinterpret_cast<float2 *>(c_lo + nt * 8), make_float2(acc[nt][0], acc[nt][1]));
@@ -214,7 +203,6 @@ __global__ void __launch_bounds__(Warps<NT>::value * 32, 1) spmm_brick_kernel(co
 template <int NT, bool ROUND_B> cudaError_t launch_brick_t(const BrickArgs &a, int sm_count, cudaStream_t s)
 {
     using L = StageLayout<NT>;
-    constexpr int kBrickWarps = Warps<NT>::value;
     constexpr int smem = kBrickWarps * L::kWarpBytes;
     cudaError_t e = allow_dynamic_smem<spmm_brick_kernel<NT, ROUND_B>>(smem);
     if (e != cudaSuccess) return e;

@@ -131,6 +131,7 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
         UP(rp, p->d_row_ptr)
         UP(pr, p->d_pairs)
     }
+    UP(h.row_map, p->d_row_map)
     UP(h.tiles, p->d_tiles)
     UP(h.chunks, p->d_chunks)
     UP(h.long_rows, p->d_long_rows)
@@ -424,6 +425,7 @@ static RowsArgs rows_args(const cutespmm_plan *p, bool all_rows, const float *B,
     a.ldb = ldb; a.ldc = ldc; a.ld_scratch = kScratchCols;
     a.N = N;
     a.status = p->d_status;
+    a.row_map = static_cast<const uint32_t *>(p->d_row_map);
     return a;
 }
 static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
@@ -442,6 +444,7 @@ static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb
     a.N = N;
     a.round_b = (p->host.opts.flags & CUTESPMM_FLAG_ROUND_B_NEAREST) ? 1u : 0u;
     a.status = p->d_status;
+    a.row_map = static_cast<const uint32_t *>(p->d_row_map);
     return a;
 }
 

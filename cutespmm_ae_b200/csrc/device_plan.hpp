@@ -38,6 +38,7 @@ struct RowsArgs {
     uint64_t ldb, ldc, ld_scratch;
     uint32_t N;
     uint32_t *status;          // device status word: set to 1 when a bounded wait gives up
+    const uint32_t *row_map;   // reordered plan: row r of the work lists is row row_map[r] of C (nullptr: identity)
 };
 
 cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s);
@@ -45,6 +46,7 @@ cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
 int rows_kernel_count(const RowsArgs &a);
 
 // Arguments of the tensor-core brick kernel.
+constexpr int kBrickWarps = 15;  // warps per block; each is an independent pipeline over its own brick range
 struct BrickArgs {
     const uint32_t *cols;         // 8 columns per brick slot (+ readable slack of a few groups behind the end)
     const uint32_t *recs;         // brick records (map, flags, panel, values in fragment order): slot k at word k * kBrickRecWords
@@ -58,6 +60,7 @@ struct BrickArgs {
     uint32_t N;
     uint32_t round_b;             // 1: round B to tf32 to nearest, 0: truncate
     uint32_t *status;             // device status word: set to 2 when a bounded wait gives up
+    const uint32_t *row_map;      // reordered plan: row r of a panel is row row_map[r] of C (nullptr: identity)
 };
 
 cudaError_t launch_brick(const BrickArgs &a, int sm_count, cudaStream_t s);

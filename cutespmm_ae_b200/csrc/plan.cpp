@@ -116,7 +116,7 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
             if (len > split) {
                 close(r);
                 begin = r + 1;
-                LongRow lr{(uint32_t)r, (uint32_t)chunks.size(), 0, 0};
+                LongRow lr{p.row_map.empty() ? (uint32_t)r : p.row_map[r], (uint32_t)chunks.size(), 0, 0};  // the row of C the sum goes to
                 for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; j += split)
                     chunks.push_back(Chunk{(uint32_t)r, j, std::min<uint32_t>(j + split, p.row_ptr[r + 1]),
                                            (uint32_t)chunks.size()});
@@ -138,6 +138,46 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
         q = q1;
     }
     tiles = std::move(row_tiles);
+}
+
+// CUTESPMM_REORDER_CLUSTER_ROWS: reorders the rows of the plan so that rows with similar column sets are neighbours.
+// Rows are sorted by their first kClusterKeyCols column indices (columns are ascending inside a row), a row with
+// fewer columns before its extensions, ties by original position (stable, so an already good order survives); empty
+// rows go last.  The role of the "find the most similar row" step the reference sketches (inc/CSR.hpp:612-679, an
+// O(rows^2) search) at the cost of one sort.  Rewrites row_ptr / pairs in the new order and records row_map.
+static void cluster_rows(HostPlan &p)
+{
+    constexpr uint32_t kClusterKeyCols = 8;
+    const uint64_t M = p.M;
+    if (M < 2) return;
+    std::vector<uint32_t> order(M);
+    std::iota(order.begin(), order.end(), 0u);
+    const std::vector<uint32_t> &rp = p.row_ptr;
+    const std::vector<Pair> &pr = p.pairs;
+    auto less = [&](uint32_t a, uint32_t b) {
+        const uint32_t la = rp[a + 1] - rp[a], lb = rp[b + 1] - rp[b];
+        if ((la == 0) != (lb == 0)) return lb == 0;  // empty rows last
+        const uint32_t n = std::min(std::min(la, lb), kClusterKeyCols);
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint32_t ca = pr[rp[a] + i].col, cb = pr[rp[b] + i].col;
+            if (ca != cb) return ca < cb;
+        }
+        if (n < kClusterKeyCols && la != lb) return la < lb;
+        return a < b;
+    };
+    std::stable_sort(order.begin(), order.end(), less);
+    bool identity = true;
+    for (uint64_t r = 0; r < M && identity; ++r) identity = order[r] == r;
+    if (identity) return;
+    std::vector<uint32_t> new_rp(M + 1, 0);
+    for (uint64_t r = 0; r < M; ++r) new_rp[r + 1] = new_rp[r] + (rp[order[r] + 1] - rp[order[r]]);
+    std::vector<Pair> new_pairs(p.nnz);
+#pragma omp parallel for schedule(dynamic, 4096)
+    for (int64_t r = 0; r < (int64_t)M; ++r)
+        std::copy(pr.begin() + rp[order[r]], pr.begin() + rp[order[r] + 1], new_pairs.begin() + new_rp[r]);
+    p.row_ptr = std::move(new_rp);
+    p.pairs = std::move(new_pairs);
+    p.row_map = std::move(order);
 }
 
 // Which kernel executes each 16-row panel (row_path: 0 = row kernel, 1 = brick kernel), from the panel's nonzero
@@ -176,6 +216,7 @@ int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vecto
     }
     if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
     fill_default_options(p.opts, opts);
+    if (p.opts.reorder) { err = "row reordering is done by the host builder only (cutespmm_plan_create)"; return CUTESPMM_EUNSUPPORTED; }
     int bad = 0;
 #pragma omp parallel for schedule(static) reduction(| : bad)
     for (int64_t r = 0; r < (int64_t)M; ++r) bad |= row_ptr[r + 1] < row_ptr[r];
@@ -219,6 +260,11 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
     if (nnz && (!cols || !vals)) { err = "cols/vals is NULL"; return CUTESPMM_EINVAL; }
     if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
     fill_default_options(p.opts, opts);
+    if (p.opts.reorder > CUTESPMM_REORDER_CLUSTER_ROWS) { err = "unknown reorder option"; return CUTESPMM_EINVAL; }
+    if (p.opts.path == CUTESPMM_PATH_SLAB && p.opts.reorder) {
+        err = "row reordering is available on the row and brick kernels (path auto, rows or brick)";
+        return CUTESPMM_EUNSUPPORTED;
+    }
     if (p.opts.path == CUTESPMM_PATH_SLAB && (p.opts.flags & CUTESPMM_FLAG_ROUND_B_NEAREST)) {
         err = "the slab path cannot round B to nearest: the copy engine places B in the tensor core's operand layout and no thread touches it";
         return CUTESPMM_EUNSUPPORTED;
@@ -254,6 +300,8 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
                              [](const Pair &a, const Pair &b) { return a.col < b.col; });
     }
     if (bad & 2) { err = "column index out of range (>= K)"; return CUTESPMM_EINVAL; }
+
+    if (p.opts.reorder == CUTESPMM_REORDER_CLUSTER_ROWS) cluster_rows(p);
 
     const std::vector<uint32_t> panel_ncols = analyze_panels(p);
 
@@ -319,6 +367,11 @@ void decode_host_plan(const HostPlan &p, uint64_t *rowPtr, uint32_t *cols, float
                 rows[(size_t)panel * kSlabRows + row].push_back({p.slab_cols[t * 8 + c], v});
             }
         }
+    }
+    if (!p.row_map.empty()) {  // back to the caller's row order
+        std::vector<std::vector<std::pair<uint32_t, float>>> orig(p.M);
+        for (uint64_t r = 0; r < p.M; ++r) orig[p.row_map[r]] = std::move(rows[r]);
+        rows = std::move(orig);
     }
     uint64_t off = 0;
     for (uint64_t r = 0; r < p.M; ++r) {

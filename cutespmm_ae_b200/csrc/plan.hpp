@@ -75,6 +75,10 @@ struct HostPlan {
     cutespmm_options_t opts{};
     bool device_built = false;  // the nonzeros were packed on the device; the host holds row pointers and work lists only
 
+    // ---- row reordering (CUTESPMM_REORDER_CLUSTER_ROWS): row r of everything below is row row_map[r] of the caller's
+    // matrix, and the kernels write its result to that row of C; empty = identity ----
+    std::vector<uint32_t> row_map;
+
     // ---- row kernel ----
     std::vector<uint32_t> row_ptr;       // M+1, offsets into pairs
     std::vector<Pair> pairs;             // nnz

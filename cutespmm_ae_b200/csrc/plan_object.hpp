@@ -19,6 +19,7 @@ struct cutespmm_plan {
     void *d_tiles_all = nullptr, *d_chunks_all = nullptr, *d_long_rows_all = nullptr;
     void *d_bcols = nullptr, *d_brecs = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
     void *d_scols = nullptr, *d_srecs = nullptr, *d_srec_off = nullptr, *d_sfirst = nullptr, *d_slast = nullptr, *d_sids = nullptr;
+    void *d_row_map = nullptr;
     float *d_scratch = nullptr;
     uint32_t *d_status = nullptr;
     // staging for the host-buffer call
@@ -39,7 +40,7 @@ struct cutespmm_plan {
         if (cur != device) cudaSetDevice(device);
         for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
                         d_bcols, d_brecs, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
-                        d_slast, d_sids, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
+                        d_slast, d_sids, d_row_map, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
         for (cudaEvent_t ev : {ev_entry, ev_done})
             if (ev) cudaEventDestroy(ev);

@@ -61,18 +61,6 @@ __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gmem_src, u
                  : "memory");
 }
 
-// 16-byte asynchronous copy global -> shared by the calling thread (the LSU path, not the TMA unit; L1 bypassed).
-__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-// One arrival on `bar` that takes place when every cp.async this thread issued before has landed.  The arrival is
-// not added to the barrier's pending count: the count the barrier was initialised with must include it.
-__device__ __forceinline__ void cp_async_arrive(uint64_t *bar)
-{
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 // TMA gather4: four rows (coordinates y0..y3) of the 2-D tensor described by `tmap`, box-width columns from
 // column x (x * element size must be a multiple of 16 bytes), land as four consecutive rows at smem_dst
 // (128-byte aligned; more for swizzled maps); completion counted on `bar`.

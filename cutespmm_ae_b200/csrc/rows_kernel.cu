@@ -239,7 +239,8 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
                 if (rem > U / 2) row_group<VEC, CH, FULL, U, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
                 else row_group<VEC, CH, FULL, U / 2, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
             }
-            float *out = a.C + (uint64_t)r * a.ldc + col0;
+            const uint32_t r_out = a.row_map ? __ldg(a.row_map + r) : r;  // a reordered plan writes the row to its place in the caller's C
+            float *out = a.C + (uint64_t)r_out * a.ldc + col0;
 #pragma unroll
             for (int ch = 0; ch < CH; ++ch)
                 if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(out + ch * 32 * VEC), acc[ch]);

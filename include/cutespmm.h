@@ -59,6 +59,19 @@ typedef enum {
  * the copy engine places B in the tensor core's operand layout and no thread touches it. */
 #define CUTESPMM_FLAG_ROUND_B_NEAREST 1u
 
+/* Plan-time row reordering.  The reference's harness expects reordered inputs to come from outside (it parses the
+ * names of reordered / split matrix files, gpu_kernels.cu:945-1047, and measures block affinity, :1049-1186) and
+ * its CSR class carries the pairwise row similarity such a stage would use (inc/CSR.hpp:612-679).  Here the stage
+ * is part of the plan: rows are processed in an order that puts rows with similar column sets into the same
+ * 16-row panel -- rows sorted by their leading column indices, the cheap form of "most similar row next" -- so a
+ * matrix whose rows arrive in a poor order still fills tensor-core bricks and shares rows of B inside a panel.  Only
+ * the order of processing changes: B and C keep the caller's row order (every row of C is written to its own
+ * place), and the panel views describe the reordered matrix.  Host builder only. */
+typedef enum {
+    CUTESPMM_REORDER_NONE = 0,
+    CUTESPMM_REORDER_CLUSTER_ROWS = 1
+} cutespmm_reorder_t;
+
 typedef struct {
     uint32_t struct_size; /* sizeof(cutespmm_options_t), for forward compatibility */
     uint32_t path;        /* cutespmm_path_t */
@@ -66,7 +79,8 @@ typedef struct {
     uint32_t tile_nnz;    /* nonzeros a thread block takes per scheduling tile (0 = default) */
     float brick_density;  /* AUTO: panels whose 16x8 bricks are at least this full go to the brick kernel (0 = default) */
     uint32_t flags;       /* CUTESPMM_FLAG_* */
-    uint32_t reserved[2];
+    uint32_t reorder;     /* cutespmm_reorder_t */
+    uint32_t reserved;
 } cutespmm_options_t;
 
 typedef struct {

@@ -164,3 +164,43 @@ def test_partition_rows_balances_nnz_and_aligns():
     b = cs.partition_rows(np.array([0, 1, 2], np.uint64), 4, align_rows=16)
     assert b[0] == 0 and b[-1] == 2 and np.all(np.diff(b.astype(np.int64)) >= 0)
 
+
+
+def _shuffle_rows(A, seed=5):
+    """P*A: the same rows in a random order (columns untouched)."""
+    perm = torch.randperm(A.M, generator=torch.Generator().manual_seed(seed))
+    lens = (A.row_ptr[1:] - A.row_ptr[:-1])[perm]
+    rp = torch.zeros(A.M + 1, dtype=torch.int64)
+    torch.cumsum(lens, 0, out=rp[1:])
+    idx = torch.repeat_interleave(A.row_ptr[:-1][perm] - rp[:-1], lens) + torch.arange(int(rp[-1]))
+    return g.CsrMatrix(A.M, A.K, rp, A.cols[idx], A.vals[idx], A.name + "_shuffled"), perm
+
+
+@pytest.mark.parametrize("path", [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO])
+def test_row_clustering_round_trip_and_effect(path):
+    """CUTESPMM_REORDER_CLUSTER_ROWS changes the order rows are processed in, nothing else: the plan decodes to the
+    caller's matrix in the caller's row order.  On a stencil whose rows were shuffled it brings similar rows back
+    together, so the panels are dense enough for the tensor-core kernel again."""
+    S, _ = _shuffle_rows(g.stencil9(48))
+    for A in (S, g.rmat(10, 8, seed=3, values="uniform"), g.uniform_random(100, 64, 3, seed=8)):
+        p = cs.Plan.from_csr(A, path=path, reorder="cluster", host_only=True)
+        rp, cols, vals = p.decode_csr()
+        assert np.array_equal(rp, A.row_ptr.numpy().astype(np.uint64))
+        assert np.array_equal(cols, A.cols.numpy().astype(np.uint32)) and np.array_equal(vals, A.vals.numpy())
+    if path == cs.PATH_AUTO:
+        plain = cs.Plan.from_csr(S, host_only=True).info()
+        clustered = cs.Plan.from_csr(S, reorder="cluster", host_only=True).info()
+        ordered = cs.Plan.from_csr(g.stencil9(48), host_only=True).info()
+        assert plain["brick_panels"] == 0                    # 16 random rows share no columns: no panel is dense enough
+        assert clustered["brick_panels"] >= 0.9 * ordered["brick_panels"] > 0
+        assert clustered["num_blocks"] < 0.5 * plain["num_blocks"]  # far fewer active-column blocks per panel
+
+
+def test_row_clustering_is_refused_where_it_is_not_built():
+    A = g.stencil9(16)
+    with pytest.raises(cs.CuteSpmmError) as e:
+        cs.Plan.from_csr(A, path=cs.PATH_SLAB, reorder="cluster", host_only=True)
+    assert e.value.status == -4
+    with pytest.raises(cs.CuteSpmmError) as e:
+        cs.Plan.from_csr(A, reorder=7, host_only=True)
+    assert e.value.status == -1
