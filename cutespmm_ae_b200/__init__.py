@@ -66,6 +66,8 @@ def _load() -> C.CDLL:
         "cutespmm_plan_build_host": (C.c_int, [C.POINTER(vp), C.c_uint64, C.c_uint64, vp, vp, vp, C.POINTER(Options)]),
         "cutespmm_plan_create_device": (C.c_int, [C.POINTER(vp), C.c_uint64, C.c_uint64, vp, vp, vp, C.POINTER(Options), vp]),
         "cutespmm_plan_destroy": (C.c_int, [vp]),
+        "cutespmm_plan_save": (C.c_int, [vp, C.c_char_p]),
+        "cutespmm_plan_load": (C.c_int, [C.POINTER(vp), C.c_char_p, C.c_int]),
         "cutespmm_plan_info": (C.c_int, [vp, C.POINTER(PlanInfo)]),
         "cutespmm_plan_blocked_row_ptr": (C.c_int, [vp, vp]),
         "cutespmm_plan_active_cols": (C.c_int, [vp, vp]),
@@ -76,6 +78,7 @@ def _load() -> C.CDLL:
         "cutespmm_spmm_csr_noalloc": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, vp, vp, vp, vp, C.c_uint64, vp,
                                                 C.c_uint64, C.c_uint32, vp]),
         "cutespmm_plan_device_status": (C.c_int, [vp, u32p]),
+        "cutespmm_sddmm": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, C.c_int, vp, vp]),
         "cutespmm_comm_unique_id": (C.c_int, [vp]),
         "cutespmm_comm_create": (C.c_int, [C.POINTER(vp), C.c_int, C.c_int, vp]),
         "cutespmm_comm_create_all": (C.c_int, [C.POINTER(vp), C.c_int, C.POINTER(C.c_int)]),
@@ -159,6 +162,20 @@ class Plan:
         self.nnz = self.info()["nnz"]
         return self
 
+    def save(self, path) -> None:
+        """Writes the plan to `path` (cutespmm_plan_save)."""
+        _check(lib.cutespmm_plan_save(self._h, str(path).encode()))
+
+    @classmethod
+    def load(cls, path, host_only: bool = False) -> "Plan":
+        """A plan saved with `save`, uploaded to the current CUDA device (or host-only)."""
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        _check(lib.cutespmm_plan_load(C.byref(self._h), str(path).encode(), 1 if host_only else 0))
+        i = self.info()
+        self.M, self.K, self.nnz = i["M"], i["K"], i["nnz"]
+        return self
+
     def close(self) -> None:
         if getattr(self, "_h", None) and self._h.value and lib is not None:  # lib is None at interpreter shutdown
             lib.cutespmm_plan_destroy(self._h)
@@ -233,6 +250,26 @@ class Plan:
         _check(lib.cutespmm_spmm_host(self._h, tb.data_ptr(), tb.stride(0) if self.K > 1 else max(N, 1), tc.data_ptr(),
                                       tc.stride(0) if self.M > 1 else max(N, 1), N, st, C.byref(ms)))
         return Cout, ms.value
+
+    def sddmm(self, X, Y, out=None, *, scale_by_values: bool = False, stream=None):
+        """out[j] = (A_j if scale_by_values else 1) * <X[row of j], Y[column of j]> for every stored nonzero j, in the
+        plan's storage order (cutespmm_sddmm).  X: M x N, Y: K x N CUDA fp32 tensors with unit column stride."""
+        import torch
+
+        for t, rows, name in ((X, self.M, "X"), (Y, self.K, "Y")):
+            if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != rows:
+                raise ValueError(f"{name} must be a {rows} x N CUDA fp32 tensor with unit column stride")
+        if X.shape[1] != Y.shape[1]:
+            raise ValueError("X and Y must have the same number of columns")
+        N = X.shape[1]
+        if out is None:
+            out = torch.empty(self.nnz, dtype=torch.float32, device=X.device)
+        if not out.is_cuda or out.dtype != torch.float32 or out.numel() != self.nnz or not out.is_contiguous():
+            raise ValueError("out must be a contiguous CUDA fp32 tensor with one element per nonzero")
+        st = (stream or torch.cuda.current_stream(X.device)).cuda_stream
+        _check(lib.cutespmm_sddmm(self._h, X.data_ptr(), X.stride(0) if self.M > 1 else max(N, 1), Y.data_ptr(),
+                                  Y.stride(0) if self.K > 1 else max(N, 1), N, 1 if scale_by_values else 0, out.data_ptr(), st))
+        return out
 
     def spmm_sharded(self, comm: "Comm", B, Cout=None, *, b_mode: int = B_RESIDENT, root: int = 0, b_bounds=None, stream=None):
         """This rank's rows of A @ B through cutespmm_spmm_sharded: B (K x N, contiguous, on this rank's GPU) is

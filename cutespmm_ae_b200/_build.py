@@ -17,7 +17,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBDIR = HERE / "lib"
 LIB = LIBDIR / "libcutespmm.so"
-SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "slab_kernel.cu", "device_build.cu", "sharded.cu", "plan.cpp", "brick_build.cpp", "slab_build.cpp", "mtx_io.cpp"]
+SOURCES = ["capi.cu", "rows_kernel.cu", "brick_kernel.cu", "noalloc.cu", "slab_kernel.cu", "device_build.cu", "sharded.cu", "sddmm_kernel.cu", "plan_io.cu", "plan.cpp", "brick_build.cpp", "slab_build.cpp", "mtx_io.cpp"]
 def _find_nvcc() -> str:
     import shutil
 

@@ -95,34 +95,32 @@ int cutespmm_plan_build_host(cutespmm_plan_t **plan, uint64_t M, uint64_t K, con
     return build_common(plan, M, K, rowPtr, cols, vals, opts);
 }
 
-int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
-                         const float *vals, const cutespmm_options_t *opts)
+// The current device, checked to be one this library runs on.
+static int usable_device(int *dev, int *sm_count)
 {
-    // fail before the (possibly long) host build when there is no usable device
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
+    cudaError_t e = cudaGetDevice(dev);
     if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice (libcutespmm needs a CUDA device; there is no CPU path)");
     cudaDeviceProp prop;
-    e = cudaGetDeviceProperties(&prop, dev);
+    e = cudaGetDeviceProperties(&prop, *dev);
     if (e != cudaSuccess) return fail_cuda(e, "cudaGetDeviceProperties");
     if (prop.major < 10)
         return fail(CUTESPMM_EUNSUPPORTED, "this library is built for sm_100a (B200) only; found compute capability " +
                                                std::to_string(prop.major) + "." + std::to_string(prop.minor));
-    NvtxRange range("cutespmm: plan creation");
-    int st = build_common(plan, M, K, rowPtr, cols, vals, opts);
-    if (st != CUTESPMM_OK) return st;
-    cutespmm_plan *p = *plan;
+    *sm_count = prop.multiProcessorCount;
+    return CUTESPMM_OK;
+}
+
+// Uploads every array of a complete host-side plan to the current device and reserves scratch and status word.
+static int upload_plan(cutespmm_plan *p, int dev, int sm_count)
+{
     HostPlan &h = p->host;
     p->device = dev;
-    p->sm_count = prop.multiProcessorCount;
+    p->sm_count = sm_count;
     p->on_device = true;
     uint64_t &by = p->device_bytes;
-#define UP(vec, ptr)                                                   \
-    if ((e = upload(vec, &ptr, by)) != cudaSuccess) {                  \
-        delete p;                                                      \
-        *plan = nullptr;                                               \
-        return fail_cuda(e, "uploading " #vec);                        \
-    }
+    cudaError_t e;
+#define UP(vec, ptr) \
+    if ((e = upload(vec, &ptr, by)) != cudaSuccess) return fail_cuda(e, "uploading " #vec);
     {   // bulk copies of a tile start/end on 16-byte boundaries: keep readable slack behind both arrays
         std::vector<uint32_t> rp(h.row_ptr);
         rp.resize(rp.size() + 8, rp.back());
@@ -161,14 +159,41 @@ int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const u
 #undef UP
     const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
     if (scratch) {
-        if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) { delete p; *plan = nullptr; return fail_cuda(e, "scratch"); }
+        if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) return fail_cuda(e, "scratch");
         by += scratch;
     }
-    if ((e = cudaMalloc(&p->d_status, 256)) != cudaSuccess || (e = cudaMemset(p->d_status, 0, 256)) != cudaSuccess) {
-        delete p; *plan = nullptr; return fail_cuda(e, "status word");
-    }
+    if ((e = cudaMalloc(&p->d_status, 256)) != cudaSuccess || (e = cudaMemset(p->d_status, 0, 256)) != cudaSuccess)
+        return fail_cuda(e, "status word");
     by += 256;
     return CUTESPMM_OK;
+}
+
+}  // extern "C"
+
+// for plan_io.cu: a complete host-side plan goes to the current device
+int cutespmm_internal_upload_plan(cutespmm_plan *p)
+{
+    int dev = -1, sms = 0;
+    const int st = usable_device(&dev, &sms);
+    return st != CUTESPMM_OK ? st : upload_plan(p, dev, sms);
+}
+
+extern "C" {
+
+int cutespmm_plan_create(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint64_t *rowPtr, const uint32_t *cols,
+                         const float *vals, const cutespmm_options_t *opts)
+{
+    // fail before the (possibly long) host build when there is no usable device
+    int dev = -1, sms = 0;
+    int st = usable_device(&dev, &sms);
+    if (st != CUTESPMM_OK) return st;
+    NvtxRange range("cutespmm: plan creation");
+    if ((st = build_common(plan, M, K, rowPtr, cols, vals, opts)) != CUTESPMM_OK) return st;
+    if ((st = upload_plan(*plan, dev, sms)) != CUTESPMM_OK) {
+        delete *plan;
+        *plan = nullptr;
+    }
+    return st;
 }
 
 int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, const uint32_t *rowPtr_dev, const uint32_t *cols_dev,
@@ -388,7 +413,7 @@ int cutespmm_plan_active_cols(const cutespmm_plan_t *p, uint32_t *out)
 int cutespmm_plan_decode_csr(const cutespmm_plan_t *p, uint64_t *rowPtr, uint32_t *cols, float *vals)
 {
     if (!p || !rowPtr || (p->host.nnz && (!cols || !vals))) return fail(CUTESPMM_EINVAL, "null argument");
-    if (p->host.device_built) {  // the pairs live on the device only, in CSR order
+    if (p->host.device_built && p->on_device) {  // the pairs live on the device only, in CSR order
         const HostPlan &h = p->host;
         for (uint64_t r = 0; r <= h.M; ++r) rowPtr[r] = h.row_ptr[r];
         std::vector<Pair> pr(h.nnz);
@@ -530,6 +555,42 @@ int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float 
         if ((e = launch_fixup(ra, s)) != cudaSuccess) return fail_cuda(e, "fix-up kernel launch");
     }
     return CUTESPMM_OK;
+}
+
+int cutespmm_sddmm(const cutespmm_plan_t *p, const float *X, uint64_t ldx, const float *Y, uint64_t ldy, uint32_t N, int scale_by_values,
+                   float *out, void *stream)
+{
+    if (!p) return fail(CUTESPMM_EINVAL, "plan is NULL");
+    if (!p->on_device) return fail(CUTESPMM_EUNSUPPORTED, "host-only plan cannot execute");
+    if (!p->host.row_map.empty()) return fail(CUTESPMM_EUNSUPPORTED, "SDDMM is not available for a plan with row reordering");
+    const HostPlan &h = p->host;
+    if (h.nnz == 0) return CUTESPMM_OK;
+    if (!out) return fail(CUTESPMM_EINVAL, "out is NULL");
+    if (N && (!X || !Y)) return fail(CUTESPMM_EINVAL, "X or Y is NULL");
+    if (ldx < N || ldy < N) return fail(CUTESPMM_EINVAL, "leading dimension smaller than N");
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(out)) & 3)
+        return fail(CUTESPMM_EINVAL, "X, Y and out must be 4-byte aligned");
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != p->device)
+        return fail(CUTESPMM_EINVAL, "the current CUDA device is not the one the plan was created on");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N == 0) {  // an empty sum
+        cudaError_t e = cudaMemsetAsync(out, 0, h.nnz * sizeof(float), s);
+        return e == cudaSuccess ? CUTESPMM_OK : fail_cuda(e, "cudaMemsetAsync");
+    }
+    const bool all = h.num_bricks || h.slab_panels;  // the work list that covers every row
+    SddmmArgs a{};
+    a.row_ptr = static_cast<const uint32_t *>(p->d_row_ptr);
+    a.pairs = p->d_pairs;
+    a.tiles = all ? p->d_tiles_all : p->d_tiles;
+    a.chunks = all ? p->d_chunks_all : p->d_chunks;
+    a.num_tiles = (uint32_t)(all ? h.tiles_all.size() : h.tiles.size());
+    a.num_chunks = (uint32_t)(all ? h.chunks_all.size() : h.chunks.size());
+    a.X = X; a.Y = Y; a.ldx = ldx; a.ldy = ldy; a.out = out; a.N = N;
+    a.scale = scale_by_values ? 1u : 0u;
+    a.vec4 = !((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) & 15) && !((ldx | ldy) & 3) ? 1u : 0u;
+    cudaError_t e = launch_sddmm(a, p->sm_count, s);
+    return e == cudaSuccess ? CUTESPMM_OK : fail_cuda(e, "SDDMM kernel launch");
 }
 
 int cutespmm_plan_device_status(const cutespmm_plan_t *p, uint32_t *status)

@@ -45,6 +45,20 @@ cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s);
 cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
 int rows_kernel_count(const RowsArgs &a);
 
+// Arguments of the SDDMM kernel (sddmm_kernel.cu): out[j] = (scale ? value of nonzero j : 1) * <X[row of j], Y[column of j]>.
+struct SddmmArgs {
+    const uint32_t *row_ptr;
+    const void *pairs, *tiles, *chunks;  // the plan's nonzeros and its row-kernel work list over every row
+    uint32_t num_tiles, num_chunks;
+    const float *X, *Y;                  // M x N and K x N, row-major
+    uint64_t ldx, ldy;
+    float *out;                          // one value per nonzero, in the plan's storage order
+    uint32_t N;
+    uint32_t scale;                      // 1: multiply by the stored value of A
+    uint32_t vec4;                       // 1: X, Y and their leading dimensions allow 16-byte loads
+};
+cudaError_t launch_sddmm(const SddmmArgs &a, int sm_count, cudaStream_t s);
+
 // Arguments of the tensor-core brick kernel.
 constexpr int kBrickWarps = 15;  // warps per block; each is an independent pipeline over its own brick range
 struct BrickArgs {

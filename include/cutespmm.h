@@ -134,6 +134,13 @@ int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, 
                                 const uint32_t *cols_dev, const float *vals_dev, const cutespmm_options_t *opts,
                                 void *stream);
 
+/* Saves a plan to a file / loads it back (onto the current device, or host-only): preprocessing done once serves
+ * later runs -- the reference preprocesses at every start (run.cu:17-20).  The file is specific to this library
+ * version and byte order and carries a checksum; a damaged or foreign file is refused with CUTESPMM_EIO.  A loaded
+ * plan behaves like the one that was saved (same kernels, bit-identical products). */
+int cutespmm_plan_save(const cutespmm_plan_t *plan, const char *path);
+int cutespmm_plan_load(cutespmm_plan_t **plan, const char *path, int host_only);
+
 int cutespmm_plan_destroy(cutespmm_plan_t *plan);
 int cutespmm_plan_info(const cutespmm_plan_t *plan, cutespmm_plan_info_t *info);
 
@@ -166,6 +173,17 @@ int cutespmm_spmm(const cutespmm_plan_t *plan, const float *B_dev, uint64_t ldb,
  * grows.  kernel_ms (may be NULL) receives the device time of the products alone. */
 int cutespmm_spmm_host(cutespmm_plan_t *plan, const float *B_host, uint64_t ldb, float *C_host,
                        uint64_t ldc, uint32_t N, void *stream, float *kernel_ms);
+
+/* ---- SDDMM over the pattern of A ---------------------------------------------------------------
+ * out[j] = (scale_by_values ? A_j : 1) * dot(X[row of j], Y[column of j]) for every stored nonzero j of the plan,
+ * N columns wide.  The operator that accompanies SpMM in a graph layer (edge scores; the reference tree has it only
+ * inside the TC-GNN baseline, TC-GNN_ATC23/TCGNN_conv/TCGNN.cpp:265 "forward_ef") and the gradient of C = A*B with
+ * respect to the values of A (X = dC, Y = B).  X: M x N, Y: K x N, device, row-major.  out: nnz floats on the device,
+ * in the plan's storage order: CSR order with the columns of a row ascending for a plan built on the host (the order
+ * cutespmm_plan_decode_csr returns), the caller's own order for a plan built from device CSR.  fp32 throughout.
+ * Not available for a plan with row reordering (CUTESPMM_EUNSUPPORTED). */
+int cutespmm_sddmm(const cutespmm_plan_t *plan, const float *X_dev, uint64_t ldx, const float *Y_dev, uint64_t ldy, uint32_t N,
+                   int scale_by_values, float *out_dev, void *stream);
 
 /* ---- product without any allocation ------------------------------------------------------------
  * No counterpart in the reference.  For callers that must not allocate device memory when they

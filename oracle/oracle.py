@@ -16,7 +16,7 @@ LIB_PATH = HERE / "liboracle.so"
 REF_PATH = HERE / "_ref" / "libcutespmm_ref.so"
 REF_LOADERS_PATH = HERE / "_ref" / "libcutespmm_ref_loaders.so"
 
-__all__ = ["build", "reference_root", "set_threads", "spmm_coo", "spmm_csr", "spmm_csr_rows", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
+__all__ = ["build", "reference_root", "set_threads", "spmm_coo", "spmm_csr", "spmm_csr_rows", "sddmm_csr", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
 
 
 def reference_root() -> Path | None:
@@ -69,6 +69,8 @@ def _load():
         _lib.oracle_max_rel_err.restype = C.c_float
         _lib.oracle_rel_fro.argtypes = [vp, vp, C.c_uint64]
         _lib.oracle_rel_fro.restype = C.c_double
+        _lib.oracle_sddmm_csr.argtypes = [vp, vp, vp, vp, vp, vp, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64]
+        _lib.oracle_sddmm_csr.restype = None
         _lib.oracle_set_threads.argtypes = [C.c_int]
         _lib.oracle_set_threads.restype = None
         _lib.oracle_max_threads.argtypes = []
@@ -115,6 +117,16 @@ def spmm_csr_rows(row_ptr, cols, vals, B, which) -> np.ndarray:
     out = np.empty((which.size, N), dtype=np.float32)
     _load().oracle_spmm_csr_rows(rp.ctypes.data, cols.ctypes.data, vals.ctypes.data, B.ctypes.data, out.ctypes.data,
                                  which.ctypes.data, which.size, N, N)
+    return out
+
+
+def sddmm_csr(row_ptr, cols, vals, X, Y) -> np.ndarray:
+    """out[j] = (vals[j] if vals is not None else 1) * <X[row of j], Y[cols[j]]> for every stored position j."""
+    rp, cols, X, Y = _a(row_ptr, np.uint64), _a(cols, np.uint32), _a(X, np.float32), _a(Y, np.float32)
+    v = None if vals is None else _a(vals, np.float32)
+    out = np.empty(cols.size, dtype=np.float32)
+    _load().oracle_sddmm_csr(rp.ctypes.data, cols.ctypes.data, None if v is None else v.ctypes.data, X.ctypes.data, Y.ctypes.data,
+                             out.ctypes.data, rp.size - 1, X.shape[1], X.shape[1], Y.shape[1])
     return out
 
 

@@ -143,3 +143,24 @@ double oracle_rel_fro(const float *C_ref, const float *C_test, uint64_t count)
         return num == 0.0 ? 0.0 : INFINITY;
     return sqrt(num / den);
 }
+
+/* SDDMM over a CSR pattern: out[j] = (vals ? vals[j] : 1) * sum_n X[row(j)][n] * Y[cols[j]][n], one fp32 multiply
+ * and one fp32 add per term, in column order n = 0 .. N-1.  The checker of cutespmm_sddmm.  The reference's own
+ * kernels have no such operator; the definition is the one of the TC-GNN baseline that travels with it
+ * (TC-GNN_ATC23/TCGNN_conv/TCGNN_kernel.cu:582, sddmm_forward_cuda_kernel: the dot product of the two
+ * endpoints' feature rows per edge). */
+void oracle_sddmm_csr(const uint64_t *rowPtr, const uint32_t *cols, const float *vals, const float *X, const float *Y,
+                      float *out, uint64_t M, uint32_t N, uint64_t ldx, uint64_t ldy)
+{
+#pragma omp parallel for schedule(dynamic, 256)
+    for (int64_t r = 0; r < (int64_t)M; ++r) {
+        const float *x = X + (size_t)r * ldx;
+        for (uint64_t j = rowPtr[r]; j < rowPtr[r + 1]; ++j) {
+            const float *y = Y + (size_t)cols[j] * ldy;
+            float s = 0.0f;
+            for (uint32_t n = 0; n < N; ++n)
+                s += x[n] * y[n];
+            out[j] = vals ? vals[j] * s : s;
+        }
+    }
+}

@@ -131,3 +131,31 @@ def test_device_built_views_match_the_reference_preprocessing(name):
                                 torch.from_numpy(gd["vals"]).cuda())
     assert np.array_equal(p.blocked_row_ptr(), gd["blocked_row_ptr"])
     assert np.array_equal(p.active_cols(), gd["active_cols"])
+
+
+@pytest.mark.parametrize("how", ["host_auto", "host_rows_chunks", "host_slab", "host_clustered", "device_auto", "device_rows"])
+def test_saved_plan_gives_the_same_product_after_loading(tmp_path, how):
+    """cutespmm_plan_save / cutespmm_plan_load: the loaded plan runs the same kernels on the same arrays (bit-identical C),
+    whichever builder made the plan."""
+    if how == "host_rows_chunks" or how == "device_rows":
+        A = g.rmat(13, 8, seed=15, values="uniform")
+    else:
+        A = g.stencil9(128)
+    if how.startswith("device"):
+        p = cs.Plan.from_device_csr(A.M, A.K, *_dev(A), path=cs.PATH_AUTO if how == "device_auto" else cs.PATH_ROWS)
+    else:
+        kw = {"host_auto": {}, "host_rows_chunks": dict(path=cs.PATH_ROWS, split_nnz=64), "host_slab": dict(path=cs.PATH_SLAB),
+              "host_clustered": dict(reorder="cluster")}[how]
+        p = cs.Plan.from_csr(A, **kw)
+    f = tmp_path / "plan.bin"
+    p.save(f)
+    q = cs.Plan.load(f)
+    ip, iq = p.info(), q.info()
+    for k in ("M", "K", "nnz", "num_tiles", "num_chunks", "num_long_rows", "brick_panels", "num_bricks"):
+        assert ip[k] == iq[k], k
+    B = g.dense_operand(A.K, 128, 23, device="cuda")
+    C0, C1 = p.spmm(B), q.spmm(B)
+    torch.cuda.synchronize()
+    assert torch.equal(C0, C1)
+    for a, b in zip(p.decode_csr(), q.decode_csr()):
+        assert np.array_equal(a, b)

@@ -204,3 +204,27 @@ def test_row_clustering_is_refused_where_it_is_not_built():
     with pytest.raises(cs.CuteSpmmError) as e:
         cs.Plan.from_csr(A, reorder=7, host_only=True)
     assert e.value.status == -1
+
+
+@pytest.mark.parametrize("kw", [dict(path=cs.PATH_AUTO), dict(path=cs.PATH_ROWS, split_nnz=32), dict(path=cs.PATH_SLAB),
+                                dict(path=cs.PATH_AUTO, reorder="cluster")])
+def test_plan_save_and_load_round_trip(tmp_path, kw):
+    """A saved plan loads back to the same description and the same matrix; a damaged, cut or foreign file is refused."""
+    A = g.stencil9(40) if kw.get("path") != cs.PATH_ROWS else g.rmat(10, 8, seed=2, values="uniform")
+    p = cs.Plan.from_csr(A, host_only=True, **kw)
+    f = tmp_path / "plan.bin"
+    p.save(f)
+    q = cs.Plan.load(f, host_only=True)
+    assert q.info() == p.info() and (q.M, q.K, q.nnz) == (A.M, A.K, A.nnz)
+    for a, b in zip(p.decode_csr(), q.decode_csr()):
+        assert np.array_equal(a, b)
+    assert np.array_equal(p.blocked_row_ptr(), q.blocked_row_ptr()) and np.array_equal(p.active_cols(), q.active_cols())
+    raw = bytearray(f.read_bytes())
+    raw[len(raw) // 2] ^= 0x40
+    (tmp_path / "flipped.bin").write_bytes(raw)
+    (tmp_path / "cut.bin").write_bytes(bytes(raw[: len(raw) // 3]))
+    (tmp_path / "foreign.bin").write_bytes(b"%%MatrixMarket matrix coordinate real general\n")
+    for name in ("flipped.bin", "cut.bin", "foreign.bin", "missing.bin"):
+        with pytest.raises(cs.CuteSpmmError) as e:
+            cs.Plan.load(tmp_path / name, host_only=True)
+        assert e.value.status == -5, name

@@ -1,0 +1,59 @@
+"""torch.library wrapper over the C ABI (cutespmm_ae_b200/torch_ops.py): forward equals the plan's product,
+the gradient with respect to B is A^T dC (transposed plan), the registered fake kernels give shapes without running
+anything, and torch's own operator checker accepts the registration."""
+import numpy as np
+import pytest
+import torch
+
+import cutespmm_ae_b200 as cs
+from cutespmm_ae_b200 import generators as g
+from cutespmm_ae_b200 import torch_ops
+
+
+def test_transpose_csr_matches_dense_transpose():
+    A = g.uniform_random(37, 23, 4, seed=3)
+    rp, cols, vals = torch_ops.transpose_csr(A.M, A.K, A.row_ptr.numpy(), A.cols.numpy(), A.vals.numpy())
+    dense = np.zeros((A.M, A.K), np.float32)
+    rows = np.repeat(np.arange(A.M), np.diff(A.row_ptr.numpy()))
+    dense[rows, A.cols.numpy()] = A.vals.numpy()
+    dt = np.zeros((A.K, A.M), np.float32)
+    trows = np.repeat(np.arange(A.K), np.diff(rp.astype(np.int64)))
+    dt[trows, cols] = vals
+    assert np.array_equal(dt, dense.T)
+
+
+def test_ops_are_registered_and_fake_kernels_give_shapes():
+    A = g.stencil9(16)
+    op = torch_ops.SparseOperator(cs.Plan.from_csr(A, host_only=True))
+    assert hasattr(torch.ops.cutespmm, "spmm") and hasattr(torch.ops.cutespmm, "sddmm")
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        B = torch.empty(A.K, 24)
+        assert tuple(torch.ops.cutespmm.spmm(op.id, B).shape) == (A.M, 24)
+        assert tuple(torch.ops.cutespmm.spmm_transposed(op.id, torch.empty(A.M, 8)).shape) == (A.K, 8)
+        assert tuple(torch.ops.cutespmm.sddmm(op.id, torch.empty(A.M, 8), torch.empty(A.K, 8), False).shape) == (A.nnz,)
+    with pytest.raises(RuntimeError):
+        torch.ops.cutespmm.spmm(10**9, torch.empty(3, 3))
+    op.close()
+
+
+@pytest.mark.gpu
+def test_forward_backward_and_opcheck(oracle_mod):
+    A = g.rmat(10, 8, seed=9, values="uniform")
+    op = torch_ops.SparseOperator(cs.Plan.from_csr(A, path=cs.PATH_ROWS))
+    B = g.dense_operand(A.K, 64, 10, device="cuda").requires_grad_(True)
+    C = op(B)
+    ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B.detach().cpu().numpy(), A.M, A.K)
+    assert oracle_mod.rel_fro(ref, C.detach().cpu().numpy()) <= 2e-6
+    G = g.dense_operand(A.M, 64, 11, device="cuda")
+    (C * G).sum().backward()
+    t_rp, t_cols, t_vals = torch_ops.transpose_csr(A.M, A.K, A.row_ptr.numpy(), A.cols.numpy(), A.vals.numpy())
+    want = oracle_mod.spmm_csr(t_rp, t_cols, t_vals, G.cpu().numpy(), A.K, A.M)  # A^T G
+    assert oracle_mod.rel_fro(want, B.grad.cpu().numpy()) <= 2e-6
+    scores = op.sddmm(G, B.detach())
+    want_s = oracle_mod.sddmm_csr(A.row_ptr, A.cols, None, G.cpu().numpy(), B.detach().cpu().numpy())
+    assert np.linalg.norm(scores.cpu().numpy() - want_s) <= 2e-6 * np.linalg.norm(want_s)
+    torch.library.opcheck(torch.ops.cutespmm.spmm.default, (op.id, B.detach().clone().requires_grad_(True)),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+    op.close()
