@@ -388,7 +388,7 @@ def parity_sample(A_dev, B, C, n_random=1 << 13, n_longest=8, seed=7):
     return oracle.rel_fro(want, C[which].cpu().numpy()), int(which.numel())
 
 
-def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak):
+def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak, reference_gpu=True):
     """Kernel-only figures of one single-GPU configuration (the per_config block)."""
     A, N0, b_seed, b_dist = make_matrix(g, workload, 1, dev)
     N = N or N0
@@ -415,7 +415,39 @@ def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak):
            "e2e_ms_per_step": round(e2e_ms, 3), "e2e_gflops": round(2.0 * A.nnz * N / (e2e_ms * 1e-3) / 1e9, 1),
            "plan_create_ms": round(plan_ms, 1), "plan_builder": how, "rel_fro_sample": err, "rows_checked": rows}
     plan.close()
+    # the reference's own kernel on the same GPU, for context (its preprocessing cannot hold the two R-MAT configurations)
+    if reference_gpu and workload in ("uniform4096", "stencil512", "elasticity40"):
+        out["reference_gpu"] = reference_gpu_block(A, N, B, flush)
     return out
+
+
+def reference_gpu_block(A_dev, N, B_dev, flush):
+    """The reference project's GPU path (its HRPB preprocessing, work list and kernel SpMM<NUM_WARPS, ILP_LEVEL>,
+    kernel.cu:119-288) built for sm_100a into oracle/_ref by oracle/Makefile: result checked against the CPU oracle
+    first, then its first (cold) launch and the mean of ten more, each alone between CUDA events."""
+    import oracle
+
+    if not oracle.ref_gpu_available():
+        return {"unavailable": "oracle/_ref/libcutespmm_ref_gpu.so is not built (needs a checkout of the reference next to this repository)"}
+    if N not in (16, 32, 64, 128, 256, 512) or A_dev.M % 16 or A_dev.K % 16:
+        return {"unavailable": "shape outside what the reference's launcher takes"}
+    try:
+        A = A_dev.cpu()
+        Bh = B_dev.cpu().numpy()
+        if flush is not None:
+            flush.fill_(1)
+            torch.cuda.synchronize()
+        C, prep, cold, warm = oracle.ref_gpu_spmm(A.M, A.K, A.row_ptr, A.cols, A.vals, Bh, iters=10)
+        want = oracle.spmm_csr(A.row_ptr, A.cols, A.vals, Bh, A.M, A.K)
+        err = oracle.rel_fro(want, C)
+    except (RuntimeError, OSError) as e:
+        return {"unavailable": f"failed here: {e}"}
+    if not err <= 1e-3:
+        return {"unavailable": f"its result differs from the CPU oracle (relative Frobenius error {err:.3e}): not timed"}
+    gf = lambda ms: round(2.0 * A.nnz * N / (ms * 1e-3) / 1e9, 1)  # noqa: E731
+    return {"kernel": "SpMM<NUM_WARPS,ILP_LEVEL> (kernel.cu:119-288), TM=16 TN=4 Machine=0, built for sm_100a", "rel_fro": err,
+            "ms_cold": round(cold, 5), "ms_warm": round(warm, 5), "gflops_cold": gf(cold), "gflops_warm": gf(warm),
+            "preprocessing_ms": round(prep, 1), "note": "C zeroed before every launch (not timed), as run.cu:43,49 does"}
 
 
 def run_ours(args):

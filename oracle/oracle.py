@@ -15,8 +15,9 @@ HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "liboracle.so"
 REF_PATH = HERE / "_ref" / "libcutespmm_ref.so"
 REF_LOADERS_PATH = HERE / "_ref" / "libcutespmm_ref_loaders.so"
+REF_GPU_PATH = HERE / "_ref" / "libcutespmm_ref_gpu.so"
 
-__all__ = ["build", "reference_root", "set_threads", "spmm_coo", "spmm_csr", "spmm_csr_rows", "sddmm_csr", "max_rel_err", "rel_fro", "ref_available", "Ref", "LIB_PATH", "REF_PATH"]
+__all__ = ["build", "reference_root", "set_threads", "spmm_coo", "spmm_csr", "spmm_csr_rows", "sddmm_csr", "max_rel_err", "rel_fro", "ref_available", "ref_gpu_available", "ref_gpu_spmm", "Ref", "LIB_PATH", "REF_PATH"]
 
 
 def reference_root() -> Path | None:
@@ -144,6 +145,29 @@ def rel_fro(C_ref, C_test) -> float:
 
 def ref_available() -> bool:
     return REF_PATH.exists()
+
+
+def ref_gpu_available() -> bool:
+    return REF_GPU_PATH.exists()
+
+
+def ref_gpu_spmm(M: int, K: int, row_ptr, cols, vals, B, iters: int = 10):
+    """The reference project's own GPU path (HRPB preprocessing, SPMM_TC work list, its kernel; oracle/ref_gpu_shim.cu)
+    on the current CUDA device.  Rows need ascending unique columns, M and K multiples of 16, N one of the widths its
+    launcher knows.  Returns (C, preprocessing ms, first-launch ms, mean ms of `iters` further launches)."""
+    L = C.CDLL(str(REF_GPU_PATH))
+    vp = C.c_void_p
+    L.ref_gpu_spmm.argtypes = [C.c_uint, C.c_uint, C.c_uint, vp, vp, vp, vp, vp, C.c_int, vp, vp, vp]
+    L.ref_gpu_spmm.restype = C.c_int
+    rp, cols, vals, B = _a(row_ptr, np.uint32), _a(cols, np.uint32), _a(vals, np.float32), _a(B, np.float32)
+    N = B.shape[1]
+    out = np.empty((M, N), dtype=np.float32)
+    prep, cold, warm = C.c_float(), C.c_float(), C.c_float()
+    st = L.ref_gpu_spmm(M, K, N, rp.ctypes.data, cols.ctypes.data, vals.ctypes.data, B.ctypes.data, out.ctypes.data, iters,
+                        C.byref(prep), C.byref(cold), C.byref(warm))
+    if st != 0:
+        raise RuntimeError(f"the reference's GPU path failed with CUDA error {st}")
+    return out, prep.value, cold.value, warm.value
 
 
 class Ref:

@@ -41,7 +41,8 @@ def test_ops_are_registered_and_fake_kernels_give_shapes():
 @pytest.mark.gpu
 def test_forward_backward_and_opcheck(oracle_mod):
     A = g.rmat(10, 8, seed=9, values="uniform")
-    op = torch_ops.SparseOperator(cs.Plan.from_csr(A, path=cs.PATH_ROWS))
+    # the transposed plan (backward pass) is built with the same options: the fp32 row kernel on both sides
+    op = torch_ops.SparseOperator(cs.Plan.from_csr(A, path=cs.PATH_ROWS), plan_kwargs=dict(path=cs.PATH_ROWS))
     B = g.dense_operand(A.K, 64, 10, device="cuda").requires_grad_(True)
     C = op(B)
     ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B.detach().cpu().numpy(), A.M, A.K)
