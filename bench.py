@@ -417,37 +417,29 @@ def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak, refer
     plan.close()
     # the reference's own kernel on the same GPU, for context (its preprocessing cannot hold the two R-MAT configurations)
     if reference_gpu and workload in ("uniform4096", "stencil512", "elasticity40"):
-        out["reference_gpu"] = reference_gpu_block(A, N, B, flush)
+        del B, C
+        torch.cuda.empty_cache()
+        out["reference_gpu"] = reference_gpu_block(workload, N)
     return out
 
 
-def reference_gpu_block(A_dev, N, B_dev, flush):
+def reference_gpu_block(workload, N):
     """The reference project's GPU path (its HRPB preprocessing, work list and kernel SpMM<NUM_WARPS, ILP_LEVEL>,
-    kernel.cu:119-288) built for sm_100a into oracle/_ref by oracle/Makefile: result checked against the CPU oracle
-    first, then its first (cold) launch and the mean of ten more, each alone between CUDA events."""
-    import oracle
-
-    if not oracle.ref_gpu_available():
+    kernel.cu:119-288) built for sm_100a into oracle/_ref by oracle/Makefile, run by oracle/ref_gpu_run.py in a process
+    of its own (the reference's host code exits on errors): result checked against the CPU oracle first, then its first
+    (cold) launch and the mean of ten more."""
+    if not (ROOT / "oracle" / "_ref" / "libcutespmm_ref_gpu.so").exists():
         return {"unavailable": "oracle/_ref/libcutespmm_ref_gpu.so is not built (needs a checkout of the reference next to this repository)"}
-    if N not in (16, 32, 64, 128, 256, 512) or A_dev.M % 16 or A_dev.K % 16:
-        return {"unavailable": "shape outside what the reference's launcher takes"}
     try:
-        A = A_dev.cpu()
-        Bh = B_dev.cpu().numpy()
-        if flush is not None:
-            flush.fill_(1)
-            torch.cuda.synchronize()
-        C, prep, cold, warm = oracle.ref_gpu_spmm(A.M, A.K, A.row_ptr, A.cols, A.vals, Bh, iters=10)
-        want = oracle.spmm_csr(A.row_ptr, A.cols, A.vals, Bh, A.M, A.K)
-        err = oracle.rel_fro(want, C)
-    except (RuntimeError, OSError) as e:
-        return {"unavailable": f"failed here: {e}"}
-    if not err <= 1e-3:
-        return {"unavailable": f"its result differs from the CPU oracle (relative Frobenius error {err:.3e}): not timed"}
-    gf = lambda ms: round(2.0 * A.nnz * N / (ms * 1e-3) / 1e9, 1)  # noqa: E731
-    return {"kernel": "SpMM<NUM_WARPS,ILP_LEVEL> (kernel.cu:119-288), TM=16 TN=4 Machine=0, built for sm_100a", "rel_fro": err,
-            "ms_cold": round(cold, 5), "ms_warm": round(warm, 5), "gflops_cold": gf(cold), "gflops_warm": gf(warm),
-            "preprocessing_ms": round(prep, 1), "note": "C zeroed before every launch (not timed), as run.cu:43,49 does"}
+        res = subprocess.run([sys.executable, str(ROOT / "oracle" / "ref_gpu_run.py"), "--workload", workload, "--N", str(N)],
+                             capture_output=True, text=True, timeout=240)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference's GPU path did not finish within 240 s"}
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    if res.returncode != 0 or not lines:
+        tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or [""]
+        return {"unavailable": f"the reference's GPU path ended with code {res.returncode}: {tail[0][:200]}"}
+    return json.loads(lines[-1])
 
 
 def run_ours(args):

@@ -1,0 +1,53 @@
+"""Runs the reference project's own GPU path (oracle/_ref/libcutespmm_ref_gpu.so, built by oracle/Makefile from the
+reference sources) on one of the synthetic workloads, in a process of its own, and prints one JSON line:
+
+    python oracle/ref_gpu_run.py --workload stencil512 --N 128
+
+A separate process on purpose: the reference's host code ends the process on any CUDA error (chkerr, inc.h:61-69) and
+indexes its occupancy table without checking the key, so a failure there must not take a benchmark run with it.
+The result is checked against the CPU oracle before any time is reported.  MEASUREMENT INFRASTRUCTURE ONLY.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", required=True, choices=["uniform4096", "stencil512", "elasticity40"])
+    ap.add_argument("--N", type=int, required=True)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    import oracle
+
+    spec = importlib.util.spec_from_file_location("cutespmm_generators", HERE.parent / "cutespmm_ae_b200" / "generators.py")
+    g = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = g
+    spec.loader.exec_module(g)
+    w = g.WORKLOADS[a.workload]
+    A = w["make"]()
+    if a.N not in (16, 32, 64, 128, 256, 512) or A.M % 16 or A.K % 16:
+        print(json.dumps({"unavailable": "shape outside what the reference's launcher takes"}))
+        return
+    B = g.dense_operand(A.K, a.N, w["b_seed"], w["b_dist"]).numpy()
+    C, prep, cold, warm = oracle.ref_gpu_spmm(A.M, A.K, A.row_ptr, A.cols, A.vals, B, iters=a.iters)
+    err = oracle.rel_fro(oracle.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K), C)
+    if not err <= 1e-3:
+        print(json.dumps({"unavailable": f"its result differs from the CPU oracle (relative Frobenius error {err:.3e}): not timed"}))
+        return
+    gf = lambda ms: round(2.0 * A.nnz * a.N / (ms * 1e-3) / 1e9, 1)  # noqa: E731
+    print(json.dumps({"kernel": "SpMM<NUM_WARPS,ILP_LEVEL> (kernel.cu:119-288), TM=16 TN=4 Machine=0, built for sm_100a", "rel_fro": err,
+                      "ms_cold": round(cold, 5), "ms_warm": round(warm, 5), "gflops_cold": gf(cold), "gflops_warm": gf(warm),
+                      "preprocessing_ms": round(prep, 1), "launches": a.iters + 1,
+                      "note": "each launch alone between CUDA events; C zeroed before every launch (not timed), as run.cu:43,49 does"}))
+
+
+if __name__ == "__main__":
+    main()
