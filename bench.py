@@ -73,7 +73,7 @@ def parse_args():
     ap.add_argument("--no-per-config", action="store_true", help="skip the per_config block (1 GPU)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = chosen by operand size)")
-    ap.add_argument("--reorder", default="none", choices=["none", "cluster"], help="plan-time reordering option")
+    ap.add_argument("--reorder", default="none", choices=["none", "cluster", "similar"], help="plan-time reordering option")
     return ap.parse_args()
 
 

@@ -27,7 +27,7 @@ __all__ = ["CuteSpmmError", "Plan", "Comm", "MtxReader", "partition_rows", "spmm
 
 PATH_AUTO, PATH_ROWS, PATH_BRICK, PATH_SLAB = 0, 1, 2, 3
 FLAG_ROUND_B_NEAREST = 1
-REORDER_NONE, REORDER_CLUSTER_ROWS = 0, 1
+REORDER_NONE, REORDER_CLUSTER_ROWS, REORDER_SIMILAR_ROWS = 0, 1, 2
 B_RESIDENT, B_FROM_ROOT, B_ROW_SHARDED = 0, 1, 2  # cutespmm_b_mode_t
 COMM_ID_BYTES = 128
 
@@ -128,7 +128,7 @@ class Plan:
         rp, cc, vv = _np(row_ptr, np.uint64), _np(cols, np.uint32), _np(vals, np.float32)
         if rp.shape[0] != M + 1:
             raise ValueError("row_ptr must have M+1 entries")
-        reorder = {"none": REORDER_NONE, "cluster": REORDER_CLUSTER_ROWS}.get(reorder, reorder)
+        reorder = {"none": REORDER_NONE, "cluster": REORDER_CLUSTER_ROWS, "similar": REORDER_SIMILAR_ROWS}.get(reorder, reorder)
         opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, FLAG_ROUND_B_NEAREST if round_b_nearest else 0, reorder)
         fn = lib.cutespmm_plan_build_host if host_only else lib.cutespmm_plan_create
         _check(fn(C.byref(self._h), M, K, rp.ctypes.data, cc.ctypes.data, vv.ctypes.data, C.byref(opts)))

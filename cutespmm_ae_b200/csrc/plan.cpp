@@ -140,6 +140,8 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
     tiles = std::move(row_tiles);
 }
 
+static void apply_row_order(HostPlan &p, std::vector<uint32_t> &&order);
+
 // CUTESPMM_REORDER_CLUSTER_ROWS: reorders the rows of the plan so that rows with similar column sets are neighbours.
 // Rows are sorted by their first kClusterKeyCols column indices (columns are ascending inside a row), a row with
 // fewer columns before its extensions, ties by original position (stable, so an already good order survives); empty
@@ -166,18 +168,109 @@ static void cluster_rows(HostPlan &p)
         return a < b;
     };
     std::stable_sort(order.begin(), order.end(), less);
+    apply_row_order(p, std::move(order));
+}
+
+// Applies a row order (order[new position] = original row) to row_ptr / pairs and records it as row_map.
+static void apply_row_order(HostPlan &p, std::vector<uint32_t> &&order)
+{
+    const uint64_t M = p.M;
     bool identity = true;
     for (uint64_t r = 0; r < M && identity; ++r) identity = order[r] == r;
     if (identity) return;
+    const std::vector<uint32_t> &rp = p.row_ptr;
     std::vector<uint32_t> new_rp(M + 1, 0);
     for (uint64_t r = 0; r < M; ++r) new_rp[r + 1] = new_rp[r] + (rp[order[r] + 1] - rp[order[r]]);
     std::vector<Pair> new_pairs(p.nnz);
 #pragma omp parallel for schedule(dynamic, 4096)
     for (int64_t r = 0; r < (int64_t)M; ++r)
-        std::copy(pr.begin() + rp[order[r]], pr.begin() + rp[order[r] + 1], new_pairs.begin() + new_rp[r]);
+        std::copy(p.pairs.begin() + rp[order[r]], p.pairs.begin() + rp[order[r] + 1], new_pairs.begin() + new_rp[r]);
     p.row_ptr = std::move(new_rp);
     p.pairs = std::move(new_pairs);
     p.row_map = std::move(order);
+}
+
+// CUTESPMM_REORDER_SIMILAR_ROWS: grows every 16-row panel greedily.  A panel starts from the first unplaced row;
+// then, fifteen times, the unplaced row with the most columns already in the panel's column set joins it.  Ties go to
+// the row whose shared columns are shared with the most rows of the panel (the sum over its columns of how many panel
+// rows have the column: this is what makes a panel grow as a compact patch instead of a chain), then to the row that
+// brings the fewest new columns, then to the lowest index.  Both scores are kept up to date through the
+// column-to-rows index: every row that has a column of the row just placed gains one.  The first score is
+// the pairwise similarity the reference defines (row_simlarity, inc/CSR.hpp:612-662) used the way its
+// find_most_similar (inc/CSR.hpp:664-679) would be, without the all-pairs search.  Columns named by more than
+// kMaxFanout rows are left out of the index (a hub column makes every row look similar and costs the most to follow).
+static void group_similar_rows(HostPlan &p)
+{
+    constexpr uint32_t kMaxFanout = 96;
+    const uint64_t M = p.M, K = p.K;
+    if (M <= kPanelRows || p.nnz == 0) return;
+    const std::vector<uint32_t> &rp = p.row_ptr;
+    const std::vector<Pair> &pr = p.pairs;
+    // column -> rows index (CSC pattern) over the columns of modest fan-out
+    std::vector<uint32_t> cdeg(K, 0u);
+    for (const Pair &e : pr) ++cdeg[e.col];
+    std::vector<uint64_t> cptr(K + 1, 0);
+    for (uint64_t c = 0; c < K; ++c) cptr[c + 1] = cptr[c] + (cdeg[c] <= kMaxFanout ? cdeg[c] : 0);
+    std::vector<uint32_t> crow(cptr[K]);
+    {
+        std::vector<uint64_t> cur(cptr.begin(), cptr.end() - 1);
+        for (uint64_t r = 0; r < M; ++r)
+            for (uint32_t j = rp[r]; j < rp[r + 1]; ++j)
+                if (cdeg[pr[j].col] <= kMaxFanout) crow[cur[pr[j].col]++] = (uint32_t)r;
+    }
+    std::vector<uint8_t> placed(M, 0);
+    std::vector<uint32_t> in_set(K, 0u);  // panel stamp of the panel whose column set holds the column
+    std::vector<uint32_t> score(M, 0u), weight(M, 0u), touched, order;
+    order.reserve(M);
+    uint64_t next_seed = 0;
+    uint32_t stamp = 0;
+    auto add_row = [&](uint32_t r) {
+        placed[r] = 1;
+        order.push_back(r);
+        for (uint32_t j = rp[r]; j < rp[r + 1]; ++j) {
+            const uint32_t c = pr[j].col;
+            const bool fresh = in_set[c] != stamp;
+            in_set[c] = stamp;
+            for (uint64_t i = cptr[c]; i < cptr[c + 1]; ++i) {
+                const uint32_t q = crow[i];
+                if (placed[q]) continue;
+                if (weight[q]++ == 0) touched.push_back(q);
+                if (fresh) ++score[q];
+            }
+        }
+    };
+    while (order.size() < M) {
+        while (placed[next_seed]) ++next_seed;
+        ++stamp;
+        touched.clear();
+        add_row((uint32_t)next_seed);
+        for (uint32_t i = 1; i < kPanelRows && order.size() < M; ++i) {
+            uint32_t best = 0xffffffffu, best_score = 0, best_weight = 0, best_new = 0;
+            size_t keep = 0;
+            for (size_t t = 0; t < touched.size(); ++t) {
+                const uint32_t q = touched[t];
+                if (placed[q]) continue;
+                touched[keep++] = q;
+                const uint32_t sc = score[q], wt = weight[q], fresh = (rp[q + 1] - rp[q]) - std::min(sc, rp[q + 1] - rp[q]);
+                const bool better = sc != best_score ? sc > best_score
+                                    : wt != best_weight ? wt > best_weight
+                                    : fresh != best_new ? fresh < best_new
+                                                        : q < best;
+                if (best == 0xffffffffu || better) {
+                    best = q; best_score = sc; best_weight = wt; best_new = fresh;
+                }
+            }
+            touched.resize(keep);
+            if (best == 0xffffffffu) {  // nothing shares a column with the panel: take the next unplaced row
+                while (next_seed < M && placed[next_seed]) ++next_seed;
+                if (next_seed >= M) break;
+                best = (uint32_t)next_seed;
+            }
+            add_row(best);
+        }
+        for (uint32_t q : touched) score[q] = weight[q] = 0;
+    }
+    apply_row_order(p, std::move(order));
 }
 
 // Which kernel executes each 16-row panel (row_path: 0 = row kernel, 1 = brick kernel), from the panel's nonzero
@@ -260,7 +353,7 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
     if (nnz && (!cols || !vals)) { err = "cols/vals is NULL"; return CUTESPMM_EINVAL; }
     if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
     fill_default_options(p.opts, opts);
-    if (p.opts.reorder > CUTESPMM_REORDER_CLUSTER_ROWS) { err = "unknown reorder option"; return CUTESPMM_EINVAL; }
+    if (p.opts.reorder > CUTESPMM_REORDER_SIMILAR_ROWS) { err = "unknown reorder option"; return CUTESPMM_EINVAL; }
     if (p.opts.path == CUTESPMM_PATH_SLAB && p.opts.reorder) {
         err = "row reordering is available on the row and brick kernels (path auto, rows or brick)";
         return CUTESPMM_EUNSUPPORTED;
@@ -302,6 +395,7 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
     if (bad & 2) { err = "column index out of range (>= K)"; return CUTESPMM_EINVAL; }
 
     if (p.opts.reorder == CUTESPMM_REORDER_CLUSTER_ROWS) cluster_rows(p);
+    if (p.opts.reorder == CUTESPMM_REORDER_SIMILAR_ROWS) group_similar_rows(p);
 
     const std::vector<uint32_t> panel_ncols = analyze_panels(p);
 

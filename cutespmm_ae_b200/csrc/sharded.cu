@@ -119,7 +119,7 @@ int list_transfers(int nranks, int b_mode, int root, uint64_t K, uint64_t ld, co
     if (nranks <= 1 || b_mode == CUTESPMM_B_RESIDENT) return CUTESPMM_OK;
     if (b_mode == CUTESPMM_B_FROM_ROOT) {
         if (root < 0 || root >= nranks) return fail_status(CUTESPMM_EINVAL, "root is not a rank of the communicator");
-        if (K * ld) out.push_back(Transfer{root, 0, K * ld});
+        if (K != 0 && ld != 0) out.push_back(Transfer{root, 0, K * ld});
         return CUTESPMM_OK;
     }
     if (b_mode != CUTESPMM_B_ROW_SHARDED) return fail_status(CUTESPMM_EINVAL, "unknown b_mode");

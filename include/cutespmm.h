@@ -69,7 +69,13 @@ typedef enum {
  * place), and the panel views describe the reordered matrix.  Host builder only. */
 typedef enum {
     CUTESPMM_REORDER_NONE = 0,
-    CUTESPMM_REORDER_CLUSTER_ROWS = 1
+    CUTESPMM_REORDER_CLUSTER_ROWS = 1,  /* rows sorted by their leading column indices: one sort, restores a good order
+                                           that was lost (shuffled input) */
+    CUTESPMM_REORDER_SIMILAR_ROWS = 2   /* every 16-row panel grown greedily: the next row is the unplaced row that shares
+                                           the most columns with the panel so far (the reference's row_simlarity /
+                                           find_most_similar idea, inc/CSR.hpp:612-679, made linear-time through the
+                                           column-to-rows index).  Panels become compact patches of the matrix graph, so
+                                           they name fewer distinct rows of B than 16 consecutive rows do */
 } cutespmm_reorder_t;
 
 typedef struct {

@@ -154,20 +154,21 @@ def ref_gpu_available() -> bool:
 def ref_gpu_spmm(M: int, K: int, row_ptr, cols, vals, B, iters: int = 10):
     """The reference project's own GPU path (HRPB preprocessing, SPMM_TC work list, its kernel; oracle/ref_gpu_shim.cu)
     on the current CUDA device.  Rows need ascending unique columns, M and K multiples of 16, N one of the widths its
-    launcher knows.  Returns (C, preprocessing ms, first-launch ms, mean ms of `iters` further launches)."""
+    launcher knows.  Returns (C, preprocessing ms, first-launch ms, mean ms of `iters` back-to-back launches, mean ms of
+    `iters` launches each after an L2 flush)."""
     L = C.CDLL(str(REF_GPU_PATH))
     vp = C.c_void_p
-    L.ref_gpu_spmm.argtypes = [C.c_uint, C.c_uint, C.c_uint, vp, vp, vp, vp, vp, C.c_int, vp, vp, vp]
+    L.ref_gpu_spmm.argtypes = [C.c_uint, C.c_uint, C.c_uint, vp, vp, vp, vp, vp, C.c_int, vp, vp, vp, vp]
     L.ref_gpu_spmm.restype = C.c_int
     rp, cols, vals, B = _a(row_ptr, np.uint32), _a(cols, np.uint32), _a(vals, np.float32), _a(B, np.float32)
     N = B.shape[1]
     out = np.empty((M, N), dtype=np.float32)
-    prep, cold, warm = C.c_float(), C.c_float(), C.c_float()
+    prep, cold, warm, flushed = C.c_float(), C.c_float(), C.c_float(), C.c_float()
     st = L.ref_gpu_spmm(M, K, N, rp.ctypes.data, cols.ctypes.data, vals.ctypes.data, B.ctypes.data, out.ctypes.data, iters,
-                        C.byref(prep), C.byref(cold), C.byref(warm))
+                        C.byref(prep), C.byref(cold), C.byref(warm), C.byref(flushed))
     if st != 0:
         raise RuntimeError(f"the reference's GPU path failed with CUDA error {st}")
-    return out, prep.value, cold.value, warm.value
+    return out, prep.value, cold.value, warm.value, flushed.value
 
 
 class Ref:

@@ -20,12 +20,14 @@
 
 extern "C" {
 
-/* Preprocesses (host, timed into *prep_ms), uploads, runs once cold (*cold_ms: the first launch) and
- * `iters` more times (*warm_ms: their mean), each launch alone between CUDA events after a cudaMemset of
- * C that is not timed.  C_host receives the last result.  Rows must have ascending unique columns and
+/* Preprocesses (host, timed into *prep_ms), uploads, runs once cold (*cold_ms: the first launch, library
+ * start-up included), `iters` times back to back (*warm_ms: their mean; L2 as the previous launch left it)
+ * and `iters` times with the L2 cache flushed before each launch by a 256 MiB write (*flushed_ms: the
+ * protocol of this project's benchmark).  Each launch runs alone between CUDA events after a cudaMemset
+ * of C that is not timed.  C_host receives the last result.  Rows must have ascending unique columns and
  * M, K be multiples of 16 (data.cu:80-93).  Returns 0, or a CUDA error code. */
 int ref_gpu_spmm(unsigned M, unsigned K, unsigned N, unsigned *rowPtr, unsigned *cols, float *vals, const float *B_host, float *C_host,
-                 int iters, float *prep_ms, float *cold_ms, float *warm_ms)
+                 int iters, float *prep_ms, float *cold_ms, float *warm_ms, float *flushed_ms)
 {
     cudaEvent_t e0, e1;
     cudaError_t err;
@@ -38,10 +40,14 @@ int ref_gpu_spmm(unsigned M, unsigned K, unsigned N, unsigned *rowPtr, unsigned 
     if ((err = cudaMalloc(&b_device, (size_t)K * N * sizeof(float))) != cudaSuccess) return (int)err;
     if ((err = cudaMalloc(&c_device, (size_t)M * N * sizeof(float))) != cudaSuccess) return (int)err;
     if ((err = cudaMemcpy(b_device, B_host, (size_t)K * N * sizeof(float), cudaMemcpyHostToDevice)) != cudaSuccess) return (int)err;
-    float total = 0.f;
-    *cold_ms = *warm_ms = 0.f;
-    for (int it = 0; it <= iters; ++it) {
+    const size_t flush_bytes = 256u << 20;
+    void *flush = nullptr;
+    if ((err = cudaMalloc(&flush, flush_bytes)) != cudaSuccess) return (int)err;
+    float total = 0.f, total_flushed = 0.f;
+    *cold_ms = *warm_ms = *flushed_ms = 0.f;
+    for (int it = 0; it <= 2 * iters; ++it) {
         if ((err = cudaMemset(c_device, 0, (size_t)M * N * sizeof(float))) != cudaSuccess) return (int)err;
+        if (it > iters && (err = cudaMemset(flush, 1, flush_bytes)) != cudaSuccess) return (int)err;
         cudaEventRecord(e0);
         spmmTc.run(hrpb.blocksDevice, b_device, c_device, hrpb.activeColsDevice, hrpb.sizePtrDevice);
         cudaEventRecord(e1);
@@ -49,9 +55,15 @@ int ref_gpu_spmm(unsigned M, unsigned K, unsigned N, unsigned *rowPtr, unsigned 
         if ((err = cudaGetLastError()) != cudaSuccess) return (int)err;
         float ms = 0.f;
         cudaEventElapsedTime(&ms, e0, e1);
-        if (it == 0) *cold_ms = ms; else total += ms;
+        if (it == 0) *cold_ms = ms;
+        else if (it <= iters) total += ms;
+        else total_flushed += ms;
     }
-    if (iters > 0) *warm_ms = total / iters;
+    if (iters > 0) {
+        *warm_ms = total / iters;
+        *flushed_ms = total_flushed / iters;
+    }
+    cudaFree(flush);
     err = cudaMemcpy(C_host, c_device, (size_t)M * N * sizeof(float), cudaMemcpyDeviceToHost);
     cudaFree(b_device);
     cudaFree(c_device);

@@ -176,20 +176,21 @@ def _shuffle_rows(A, seed=5):
     return g.CsrMatrix(A.M, A.K, rp, A.cols[idx], A.vals[idx], A.name + "_shuffled"), perm
 
 
+@pytest.mark.parametrize("how", ["cluster", "similar"])
 @pytest.mark.parametrize("path", [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO])
-def test_row_clustering_round_trip_and_effect(path):
+def test_row_clustering_round_trip_and_effect(path, how):
     """CUTESPMM_REORDER_CLUSTER_ROWS changes the order rows are processed in, nothing else: the plan decodes to the
     caller's matrix in the caller's row order.  On a stencil whose rows were shuffled it brings similar rows back
     together, so the panels are dense enough for the tensor-core kernel again."""
     S, _ = _shuffle_rows(g.stencil9(48))
     for A in (S, g.rmat(10, 8, seed=3, values="uniform"), g.uniform_random(100, 64, 3, seed=8)):
-        p = cs.Plan.from_csr(A, path=path, reorder="cluster", host_only=True)
+        p = cs.Plan.from_csr(A, path=path, reorder=how, host_only=True)
         rp, cols, vals = p.decode_csr()
         assert np.array_equal(rp, A.row_ptr.numpy().astype(np.uint64))
         assert np.array_equal(cols, A.cols.numpy().astype(np.uint32)) and np.array_equal(vals, A.vals.numpy())
     if path == cs.PATH_AUTO:
         plain = cs.Plan.from_csr(S, host_only=True).info()
-        clustered = cs.Plan.from_csr(S, reorder="cluster", host_only=True).info()
+        clustered = cs.Plan.from_csr(S, reorder=how, host_only=True).info()
         ordered = cs.Plan.from_csr(g.stencil9(48), host_only=True).info()
         assert plain["brick_panels"] == 0                    # 16 random rows share no columns: no panel is dense enough
         assert clustered["brick_panels"] >= 0.9 * ordered["brick_panels"] > 0
@@ -228,3 +229,14 @@ def test_plan_save_and_load_round_trip(tmp_path, kw):
         with pytest.raises(cs.CuteSpmmError) as e:
             cs.Plan.load(tmp_path / name, host_only=True)
         assert e.value.status == -5, name
+
+
+def test_similar_rows_grouping_shrinks_the_panels_column_sets():
+    """CUTESPMM_REORDER_SIMILAR_ROWS grows each 16-row panel as a compact patch of the matrix graph: on a 2-D stencil in
+    natural order (16 consecutive grid points per panel: 3 x 18 columns) and on the block-structured 3-D matrix the
+    panels name clearly fewer distinct columns, i.e. fewer tensor-core bricks and fewer gathered rows of B."""
+    for A, gain in ((g.stencil9(96), 0.80), (g.elasticity3d(12, 3, 2), 0.90)):
+        plain = cs.Plan.from_csr(A, host_only=True).info()
+        grouped = cs.Plan.from_csr(A, reorder="similar", host_only=True).info()
+        assert grouped["num_bricks"] <= gain * plain["num_bricks"], (A.name, plain["num_bricks"], grouped["num_bricks"])
+        assert grouped["nnz"] == plain["nnz"]

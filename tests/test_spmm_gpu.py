@@ -244,8 +244,9 @@ def test_largest_configuration_at_its_own_size(oracle_mod):
         assert oracle_mod.rel_fro(want, got_rows) <= tol, (which.numel(), tol)
 
 
+@pytest.mark.parametrize("how", ["cluster", "similar"])
 @pytest.mark.parametrize("path", [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO], ids=["rows", "brick", "auto"])
-def test_row_clustering_keeps_the_callers_row_order(oracle_mod, path):
+def test_row_clustering_keeps_the_callers_row_order(oracle_mod, path, how):
     """A plan with CUTESPMM_REORDER_CLUSTER_ROWS processes the rows in another order but writes every row of C to its
     own place: the product of a row-shuffled stencil and of a power-law graph (hub rows cut into chunks: the fix-up
     kernel writes mapped rows too) must equal the oracle's on the caller's matrix."""
@@ -253,9 +254,9 @@ def test_row_clustering_keeps_the_callers_row_order(oracle_mod, path):
 
     S, _ = _shuffle_rows(g.stencil9(160))
     for A, N in ((S, 128), (S, 96), (g.rmat(13, 8, seed=5, values="uniform"), 64)):
-        p = cs.Plan.from_csr(A, path=path, reorder="cluster", split_nnz=64)
+        p = cs.Plan.from_csr(A, path=path, reorder=how, split_nnz=64)
         B = g.dense_operand(A.K, N, 77).numpy()
         ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K)
         assert oracle_mod.rel_fro(ref, run(p, B)) <= PATH_TOL[path], (A.name, N)
     if path == cs.PATH_AUTO:  # the point of the option: the shuffled stencil is back on the tensor-core kernel
-        assert cs.Plan.from_csr(S, reorder="cluster").info()["num_bricks"] > 0 and cs.Plan.from_csr(S).info()["num_bricks"] == 0
+        assert cs.Plan.from_csr(S, reorder=how).info()["num_bricks"] > 0 and cs.Plan.from_csr(S).info()["num_bricks"] == 0
