@@ -73,6 +73,7 @@ def parse_args():
     ap.add_argument("--no-per-config", action="store_true", help="skip the per_config block (1 GPU)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = chosen by operand size)")
+    ap.add_argument("--matrices", default="", help="a folder of MatrixMarket files: print the per-matrix table instead of the benchmark line")
     ap.add_argument("--reorder", default="none", choices=["none", "cluster", "similar"], help="plan-time reordering option")
     return ap.parse_args()
 
@@ -423,7 +424,7 @@ def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak, refer
     return out
 
 
-def reference_gpu_block(workload, N):
+def reference_gpu_block(workload, N, mtx=None):
     """The reference project's GPU path (its HRPB preprocessing, work list and kernel SpMM<NUM_WARPS, ILP_LEVEL>,
     kernel.cu:119-288) built for sm_100a into oracle/_ref by oracle/Makefile, run by oracle/ref_gpu_run.py in a process
     of its own (the reference's host code exits on errors): result checked against the CPU oracle first, then its first
@@ -431,7 +432,8 @@ def reference_gpu_block(workload, N):
     if not (ROOT / "oracle" / "_ref" / "libcutespmm_ref_gpu.so").exists():
         return {"unavailable": "oracle/_ref/libcutespmm_ref_gpu.so is not built (needs a checkout of the reference next to this repository)"}
     try:
-        res = subprocess.run([sys.executable, str(ROOT / "oracle" / "ref_gpu_run.py"), "--workload", workload, "--N", str(N)],
+        what = ["--mtx", str(mtx)] if mtx else ["--workload", workload]
+        res = subprocess.run([sys.executable, str(ROOT / "oracle" / "ref_gpu_run.py"), *what, "--N", str(N)],
                              capture_output=True, text=True, timeout=240)
     except subprocess.TimeoutExpired:
         return {"unavailable": "the reference's GPU path did not finish within 240 s"}
@@ -669,8 +671,65 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_matrices(args):
+    """--matrices DIR: the table the reference's report script prints (present_gflops.py:36-42: matrix, N, GFLOP/s of its
+    kernel and of a baseline) over the MatrixMarket files under DIR, N in {32, 128, 512} (run.cu:16).  Every file is
+    read the way run.cu reads it (pattern only, values 1.0, padded to multiples of 16; rows then sorted); the product is
+    checked on sampled rows against the CPU oracle; beside this library's figure stands the reference's own kernel on
+    the same GPU, L2 flushed before every launch for both, where oracle/_ref holds it."""
+    import cutespmm_ae_b200 as cs
+    from cutespmm_ae_b200 import generators as g
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: libcutespmm has no CPU path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    files = sorted(Path(args.matrices).glob("**/*.mtx"))
+    if not files:
+        raise SystemExit(f"no .mtx files under {args.matrices}")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    print("matrix, rows, nnz, N(feature size), path, GFLOPS, relFro (sampled rows), reference kernel GFLOPS (same GPU), ratio")
+    table = []
+    for f in files:
+        r = cs.MtxReader(f, pattern_only=True)
+        rows = np.repeat(np.arange(r.M, dtype=np.int64), np.diff(r.rowPtr.astype(np.int64)))
+        keys = np.unique(rows * r.K + r.cols.astype(np.int64))  # rows sorted, duplicates dropped (what HRPB needs, data.cu:80-93)
+        rr, cc = keys // r.K, (keys % r.K).astype(np.int32)
+        rp = np.zeros(r.M + 1, dtype=np.int64)
+        np.cumsum(np.bincount(rr, minlength=r.M), out=rp[1:])
+        A = g.CsrMatrix(r.M, r.K, torch.from_numpy(rp).to(dev), torch.from_numpy(cc).to(dev), torch.ones(cc.size, dtype=torch.float32, device=dev), f.stem)
+        plan, _, _ = build_plan(cs, A, "auto", args.reorder)
+        info = plan.info()
+        for N in (32, 128, 512):
+            B = g.dense_operand(A.K, N, 4242, "normal", device=dev)
+            C = torch.empty((A.M, N), dtype=torch.float32, device=dev)
+            ms, _, _ = time_steps(lambda: plan.spmm(B, C), 10, 3, flush, None, dev)
+            err, _ = parity_sample(A, B, C, n_random=1 << 10)
+            gf = 2.0 * A.nnz * N / (ms * 1e-3) / 1e9
+            ref = reference_gpu_block("", N, mtx=f)
+            ref_gf = ref.get("gflops_l2_flushed")
+            kind = "brick+rows" if info["num_bricks"] and info["num_tiles"] else ("brick" if info["num_bricks"] else "rows")
+            row = {"matrix": f.stem, "rows": A.M, "nnz": A.nnz, "N": N, "path": kind, "gflops": round(gf, 1), "rel_fro": err,
+                   "reference_gpu_gflops": ref_gf, "ratio": None if not ref_gf else round(gf / ref_gf, 2),
+                   "reference_note": ref.get("unavailable")}
+            table.append(row)
+            print(f"{f.stem}, {A.M}, {A.nnz}, {N}, {kind}, {gf:.1f}, {err:.2e}, {ref_gf if ref_gf else 'n/a'}, {row['ratio'] if row['ratio'] else 'n/a'}", flush=True)
+            if not err <= 1e-3:
+                raise SystemExit(f"parity failed on {f}: {err}")
+            del B, C
+        plan.close()
+        del A
+        torch.cuda.empty_cache()
+    ratios = [t["ratio"] for t in table if t["ratio"]]
+    print(json.dumps({"metric": "spmm_gflops_table", "matrices": len(files), "rows": table,
+                      "geomean_ratio_vs_reference_kernel": round(float(np.exp(np.mean(np.log(ratios)))), 3) if ratios else None}), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.matrices:
+        run_matrices(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

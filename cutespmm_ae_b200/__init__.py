@@ -89,6 +89,7 @@ def _load() -> C.CDLL:
         "cutespmm_comm_destroy": (C.c_int, [vp]),
         "cutespmm_spmm_sharded": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, C.c_uint64, vp, vp, C.c_uint64, C.c_uint32, vp]),
         "cutespmm_spmm_sharded_host": (C.c_int, [vp, vp, vp, C.c_uint64, vp, vp, C.c_uint64, C.c_uint32, vp, f32p, f32p]),
+        "cutespmm_plan_reserve_host_staging": (C.c_int, [vp, C.c_uint32, C.c_int]),
         "cutespmm_sharded_transfers": (C.c_int, [vp, C.c_int, C.c_int, C.c_uint64, C.c_uint64, vp, C.c_uint32, vp, vp, vp, u32p]),
         "cutespmm_partition_rows": (C.c_int, [C.c_uint64, vp, C.c_uint32, C.c_uint32, C.c_uint32, vp]),
         "cutespmm_mtx_open": (C.c_int, [C.POINTER(vp), C.c_char_p, C.c_int]),

@@ -177,7 +177,76 @@ int new_comm(cutespmm_comm_t **out, nccl_comm_t c, int nranks, int rank, int dev
 
 }  // namespace
 
+namespace {
+
+// How a host-buffer call cuts N columns into windows, and the staging it needs on the device.
+struct Windows {
+    uint32_t count = 1, width = 0;
+    uint64_t ldd = 0;  // leading dimension of a window on the device
+};
+
+// Column windows are independent products (C[:, w] = A * B[:, w]), so a host-buffer call is a pipeline over them: while
+// window w is exchanged, multiplied and copied out, window w+1 is already coming in; the two copy directions run on
+// different engines.  Small operands go in one piece.  With several ranks the cut must be the same on all of them (the
+// exchanges pair up window by window), so it depends on K and N only.  Allocates (or grows) the plan's staging buffers,
+// streams and events; a call that finds them large enough allocates nothing.
+int ensure_staging(cutespmm_plan *p, uint32_t N, bool sharded, Windows &w)
+{
+    const uint64_t M = p->host.M, K = p->host.K;
+    const uint64_t rows_for_cut = sharded ? K : std::max(M, K);
+    uint32_t nw = 1;
+    if ((uint64_t)N * rows_for_cut * sizeof(float) >= (8u << 20)) nw = std::max(1u, std::min<uint32_t>(cutespmm_plan::kMaxWindows, N / 64));
+    // window width: a multiple of 64 columns (the last may be narrower); strided copies of rows shorter than 256 bytes
+    // were measured at 2/3 of the link rate, 256-byte rows at the full rate
+    w.width = ((N + nw - 1) / nw + 63) / 64 * 64;
+    w.count = (N + w.width - 1) / w.width;
+    w.ldd = w.count == 1 ? (uint64_t)(N + 3) / 4 * 4 : w.width;  // rows start 16-byte aligned
+    const uint64_t needB = (uint64_t)w.count * K * w.ldd * sizeof(float), needC = (uint64_t)w.count * M * w.ldd * sizeof(float);
+    cudaError_t e;
+    if (needB > p->staged_B) {
+        if (p->d_B) cudaFree(p->d_B);
+        p->d_B = nullptr; p->staged_B = 0;
+        if ((e = cudaMalloc(&p->d_B, needB)) != cudaSuccess) return fail_cuda_status(e, "staging buffer for B");
+        p->staged_B = needB;
+    }
+    if (needC > p->staged_C) {
+        if (p->d_C) cudaFree(p->d_C);
+        p->d_C = nullptr; p->staged_C = 0;
+        if ((e = cudaMalloc(&p->d_C, needC)) != cudaSuccess) return fail_cuda_status(e, "staging buffer for C");
+        p->staged_C = needC;
+    }
+    if (!p->s_in) {
+        if ((e = cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking)) != cudaSuccess ||
+            (e = cudaStreamCreateWithFlags(&p->s_x, cudaStreamNonBlocking)) != cudaSuccess ||
+            (e = cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking)) != cudaSuccess)
+            return fail_cuda_status(e, "cudaStreamCreate");
+        if ((e = cudaEventCreateWithFlags(&p->ev_entry, cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming)) != cudaSuccess)
+            return fail_cuda_status(e, "cudaEventCreate");
+        for (int i = 0; i < cutespmm_plan::kMaxWindows; ++i)
+            if ((e = cudaEventCreateWithFlags(&p->ev_in[i], cudaEventDisableTiming)) != cudaSuccess ||
+                (e = cudaEventCreate(&p->ev_x0[i])) != cudaSuccess || (e = cudaEventCreate(&p->ev_x1[i])) != cudaSuccess ||
+                (e = cudaEventCreate(&p->ev_k0[i])) != cudaSuccess || (e = cudaEventCreate(&p->ev_k1[i])) != cudaSuccess)
+                return fail_cuda_status(e, "cudaEventCreate");
+    }
+    return CUTESPMM_OK;
+}
+
+}  // namespace
+
 extern "C" {
+
+int cutespmm_plan_reserve_host_staging(cutespmm_plan_t *p, uint32_t N, int sharded)
+{
+    if (!p) return fail_status(CUTESPMM_EINVAL, "plan is NULL");
+    if (!p->on_device) return fail_status(CUTESPMM_EUNSUPPORTED, "host-only plan cannot execute");
+    if (N == 0) return CUTESPMM_OK;
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != p->device)
+        return fail_status(CUTESPMM_EINVAL, "the current CUDA device is not the one the plan was created on");
+    Windows w;
+    return ensure_staging(p, N, sharded != 0, w);
+}
 
 int cutespmm_comm_unique_id(void *id_out)
 {
@@ -352,45 +421,10 @@ int cutespmm_spmm_sharded_host(cutespmm_plan_t *p, cutespmm_comm_t *comm, const 
         return fail_status(CUTESPMM_EINVAL, "the current CUDA device is not the one the plan was created on");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    // Column windows are independent products (C[:, w] = A * B[:, w]), so the call is a pipeline over them: while
-    // window w is exchanged, multiplied and copied out, window w+1 is already coming in; the two copy directions
-    // run on different engines.  Small operands go in one piece.  With several ranks the cut must be the same on
-    // all of them (the exchanges pair up window by window), so it depends on K and N only.
-    const uint64_t rows_for_cut = nranks > 1 ? K : std::max(M, K);
-    uint32_t nw = 1;
-    if ((uint64_t)N * rows_for_cut * sizeof(float) >= (8u << 20)) nw = std::max(1u, std::min<uint32_t>(cutespmm_plan::kMaxWindows, N / 64));
-    // window width: a multiple of 64 columns (the last may be narrower); strided copies of rows shorter than 256 bytes
-    // were measured at 2/3 of the link rate, 256-byte rows at the full rate
-    const uint32_t wcols = ((N + nw - 1) / nw + 63) / 64 * 64;
-    nw = (N + wcols - 1) / wcols;
-    const uint64_t ldd = nw == 1 ? (uint64_t)(N + 3) / 4 * 4 : wcols;  // device leading dimension: rows start 16-byte aligned
-    const uint64_t needB = (uint64_t)nw * K * ldd * sizeof(float), needC = (uint64_t)nw * M * ldd * sizeof(float);
-    if (needB > p->staged_B) {
-        if (p->d_B) cudaFree(p->d_B);
-        p->d_B = nullptr; p->staged_B = 0;
-        if ((e = cudaMalloc(&p->d_B, needB)) != cudaSuccess) return fail_cuda_status(e, "staging buffer for B");
-        p->staged_B = needB;
-    }
-    if (needC > p->staged_C) {
-        if (p->d_C) cudaFree(p->d_C);
-        p->d_C = nullptr; p->staged_C = 0;
-        if ((e = cudaMalloc(&p->d_C, needC)) != cudaSuccess) return fail_cuda_status(e, "staging buffer for C");
-        p->staged_C = needC;
-    }
-    if (!p->s_in) {
-        if ((e = cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking)) != cudaSuccess ||
-            (e = cudaStreamCreateWithFlags(&p->s_x, cudaStreamNonBlocking)) != cudaSuccess ||
-            (e = cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking)) != cudaSuccess)
-            return fail_cuda_status(e, "cudaStreamCreate");
-        if ((e = cudaEventCreateWithFlags(&p->ev_entry, cudaEventDisableTiming)) != cudaSuccess ||
-            (e = cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming)) != cudaSuccess)
-            return fail_cuda_status(e, "cudaEventCreate");
-        for (int w = 0; w < cutespmm_plan::kMaxWindows; ++w)
-            if ((e = cudaEventCreateWithFlags(&p->ev_in[w], cudaEventDisableTiming)) != cudaSuccess ||
-                (e = cudaEventCreate(&p->ev_x0[w])) != cudaSuccess || (e = cudaEventCreate(&p->ev_x1[w])) != cudaSuccess ||
-                (e = cudaEventCreate(&p->ev_k0[w])) != cudaSuccess || (e = cudaEventCreate(&p->ev_k1[w])) != cudaSuccess)
-                return fail_cuda_status(e, "cudaEventCreate");
-    }
+    Windows wn;
+    if ((st = ensure_staging(p, N, nranks > 1, wn)) != CUTESPMM_OK) return st;
+    const uint32_t nw = wn.count, wcols = wn.width;
+    const uint64_t ldd = wn.ldd;
     auto drain = [&]() {
         cudaStreamSynchronize(p->s_in);
         cudaStreamSynchronize(p->s_x);

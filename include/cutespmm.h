@@ -286,6 +286,16 @@ int cutespmm_spmm_sharded_host(cutespmm_plan_t *plan, cutespmm_comm_t *comm, con
                                const uint64_t *b_bounds, float *C_host, uint64_t ldc, uint32_t N, void *stream,
                                float *kernel_ms, float *exchange_ms);
 
+/* Allocates now what cutespmm_spmm_host / cutespmm_spmm_sharded_host would allocate at their first call for N columns
+ * (device staging for B and C, streams, events); `sharded` != 0 sizes it for a call with more than one rank.  A later
+ * host-buffer call for the same or a smaller N then allocates nothing.
+ * Needed by a process that drives several GPUs from several threads: a cudaMalloc -- and the first launch of a kernel
+ * on a device, which loads its code -- synchronises with every device of the process, so it must not run on one thread
+ * while another thread's collective kernel is already waiting for this thread to join (both would wait for ever).
+ * Such a host reserves the staging and runs one local product per plan (cutespmm_spmm on resident data) before its
+ * first collective; tests/cpp/sharded_driver.cpp does exactly that.  One process per GPU has no such coupling. */
+int cutespmm_plan_reserve_host_staging(cutespmm_plan_t *plan, uint32_t N, int sharded);
+
 /* The collectives a sharded call issues for one contiguous K x N block of B, in order: transfer i sends
  * count[i] floats starting at element offset[i] of the block from rank root[i] to every rank.  Returns the
  * number of transfers in *n (at most `max` are written).  Pure bookkeeping: works on a stub communicator. */

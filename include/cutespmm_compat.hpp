@@ -90,13 +90,27 @@ public:
     unsigned int M;
     unsigned int K;
     unsigned int numRowPanels;
+    // the public members of the reference class, in its order (data.cu:62-79), so code that reads them still compiles;
+    // members the reference declares but never fills (num_bricks stays 0 there, the float statistics are never assigned)
+    // carry this plan's figures instead
+    unsigned int *blocksData = nullptr;                // the reference's host copy of its packed stream: not kept here
+    unsigned long long int dataStructSize = 0;         // bytes of device memory the plan owns
+    unsigned int num_bricks = 0;                       // non-empty 16 x 8 bricks of the panels on the tensor-core kernel
     unsigned int *blocksDevice = nullptr;              // token for SPMM_TC::run
     unsigned int *blockedRowPtr = nullptr;             // host, numRowPanels + 1 entries (data.cu:65)
+    unsigned int *blockedRowPtrDevice = nullptr;       // token (the kernels here do not read this view)
+    unsigned long long int *sizePtr = nullptr;         // the reference's per-block offsets: records here have a fixed size
     unsigned long long int *sizePtrDevice = nullptr;   // token for SPMM_TC::run
     unsigned int numActiveCols = 0;
     unsigned int *activeCols = nullptr;                // host, blockedRowPtr[numRowPanels] * 16 entries (data.cu:70)
     unsigned int *activeColsDevice = nullptr;          // token for SPMM_TC::run
+    float averageNNZcol = 0.f;                         // nonzeros per active column
     unsigned int numNNZ = 0;
+    float block_density = 0.f;                         // nonzeros per cell of the 16 x 16 active-column blocks
+    unsigned int atomic_blocks = 0;                    // the reference counts split panels it adds with atomics; here: chunks of long rows
+    float atomic_ratio = 0.f;                          // ... as a share of the row panels
+    float waves = 0.f;                                 // occupancy-table figure of the reference's work list; no such table here
+    std::vector<std::vector<unsigned int>> blocks_nnz_counter_vec;  // never filled by the reference either
     cutespmm_plan_t *plan = nullptr;                   // the object behind the tokens
 
     HRPB(unsigned int M_, unsigned int K_, unsigned int *rowPtr_, unsigned int *cols_, float *vals_,
@@ -114,6 +128,13 @@ public:
         blockedRowPtr = blocked_.data();
         activeCols = active_.data();
         numActiveCols = (unsigned int)(info.num_blocks * 16);
+        dataStructSize = info.device_bytes;
+        num_bricks = (unsigned int)info.num_bricks;
+        averageNNZcol = numActiveCols ? (float)numNNZ / (float)numActiveCols : 0.f;
+        block_density = info.num_blocks ? (float)numNNZ / (float)(info.num_blocks * 256) : 0.f;
+        atomic_blocks = (unsigned int)info.num_chunks;
+        atomic_ratio = numRowPanels ? (float)info.num_long_rows / (float)numRowPanels : 0.f;
+        blockedRowPtrDevice = reinterpret_cast<unsigned int *>(plan);
         blocksDevice = reinterpret_cast<unsigned int *>(plan);
         activeColsDevice = reinterpret_cast<unsigned int *>(plan);
         sizePtrDevice = reinterpret_cast<unsigned long long int *>(plan);
@@ -123,7 +144,7 @@ public:
     {
         if (plan) cutespmm_plan_destroy(plan);
         plan = nullptr;
-        blocksDevice = activeColsDevice = nullptr;
+        blocksDevice = activeColsDevice = blockedRowPtrDevice = nullptr;
         sizePtrDevice = nullptr;
     }
     ~HRPB() { freeDevice(); }

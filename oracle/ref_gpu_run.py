@@ -2,6 +2,7 @@
 reference sources) on one of the synthetic workloads, in a process of its own, and prints one JSON line:
 
     python oracle/ref_gpu_run.py --workload stencil512 --N 128
+    python oracle/ref_gpu_run.py --mtx some/matrix.mtx --N 128      (pattern of a MatrixMarket file, values 1.0, as run.cu reads it)
 
 A separate process on purpose: the reference's host code ends the process on any CUDA error (chkerr, inc.h:61-69) and
 indexes its occupancy table without checking the key, so a failure there must not take a benchmark run with it.
@@ -19,9 +20,28 @@ HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent))
 
 
+def sorted_pattern_from_mtx(g, path):
+    """The file's pattern as the reference's own reader delivers it (IO.cu:10-87: values 1.0, dimensions padded to
+    multiples of 16, symmetric files mirrored), with every row's columns sorted and duplicates dropped -- the order its
+    preprocessing needs (data.cu:80-93)."""
+    import numpy as np
+    import torch
+
+    import oracle
+
+    M, K, nnz, rp, cols, vals = oracle.Ref().mtx_read(path)
+    rows = np.repeat(np.arange(M, dtype=np.int64), np.diff(rp.astype(np.int64)))
+    keys = np.unique(rows * K + cols.astype(np.int64))
+    r, c = keys // K, (keys % K).astype(np.int32)
+    row_ptr = np.zeros(M + 1, dtype=np.int64)
+    np.cumsum(np.bincount(r, minlength=M), out=row_ptr[1:])
+    return g.CsrMatrix(M, K, torch.from_numpy(row_ptr), torch.from_numpy(c), torch.ones(c.size, dtype=torch.float32), Path(path).stem)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", required=True, choices=["uniform4096", "stencil512", "elasticity40"])
+    ap.add_argument("--workload", default="", choices=["", "uniform4096", "stencil512", "elasticity40"])
+    ap.add_argument("--mtx", default="", help="a MatrixMarket file instead of a named workload")
     ap.add_argument("--N", type=int, required=True)
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
@@ -31,10 +51,17 @@ def main():
     g = importlib.util.module_from_spec(spec)
     sys.modules[spec.name] = g
     spec.loader.exec_module(g)
-    w = g.WORKLOADS[a.workload]
-    A = w["make"]()
+    if a.mtx:
+        A = sorted_pattern_from_mtx(g, a.mtx)
+        w = {"b_seed": 4242, "b_dist": "normal"}
+    else:
+        w = g.WORKLOADS[a.workload]
+        A = w["make"]()
     if a.N not in (16, 32, 64, 128, 256, 512) or A.M % 16 or A.K % 16:
         print(json.dumps({"unavailable": "shape outside what the reference's launcher takes"}))
+        return
+    if (A.M // 16) * (A.K // 16) > (1 << 31):
+        print(json.dumps({"unavailable": "the reference's preprocessing allocates (M/16)*(K/16) offsets (data.cu:91): too large for this matrix"}))
         return
     B = g.dense_operand(A.K, a.N, w["b_seed"], w["b_dist"]).numpy()
     C, prep, cold, warm, flushed = oracle.ref_gpu_spmm(A.M, A.K, A.row_ptr, A.cols, A.vals, B, iters=a.iters)

@@ -5,7 +5,8 @@
 //   1. cutespmm_spmm_sharded, B on rank 0 only            (broadcast over NVLink, then the product)
 //   2. cutespmm_spmm_sharded, B row-sharded in place      (all-gather, then the product)
 //   3. cutespmm_spmm_sharded_host, host slices in, host C out
-// and every result is compared with the CPU oracle on that rank's rows.
+// and every result is compared with the CPU oracle on that rank's rows.  All allocation and the first launch of
+// every kernel happen before the first collective (see cutespmm_plan_reserve_host_staging in cutespmm.h).
 //
 //   sharded_driver [ngpus]     prints "rank r mode m relFro=e" lines; exit 0 = all passed,
 //                              exit 77 = fewer than two GPUs visible (nothing to test)
@@ -120,6 +121,13 @@ int main(int argc, char **argv)
             std::printf("rank %d rows [%llu, %llu) mode %s relFro=%.3e\n", rank, (unsigned long long)r0, (unsigned long long)r1, mode, fro);
             if (!(fro <= 1e-3)) failures.fetch_add(1);
         };
+        // Before the first collective: everything that allocates or loads code on this device -- the staging of the
+        // host-buffer call, and one local product so that the kernels are resident.  A cudaMalloc or a first launch
+        // synchronises with all devices of the process and must not meet another thread's collective in flight.
+        CK(cutespmm_plan_reserve_host_staging(plan, N, 1));
+        CU(cudaMemsetAsync(dB, 0, (size_t)K * N * sizeof(float), s));
+        CK(cutespmm_spmm(plan, dB, N, dC, N, N, s));
+        CU(cudaStreamSynchronize(s));
         // 1. B on rank 0 only
         CU(cudaMemsetAsync(dB, 0xff, (size_t)K * N * sizeof(float), s));
         if (rank == 0) CU(cudaMemcpyAsync(dB, B.data(), (size_t)K * N * sizeof(float), cudaMemcpyHostToDevice, s));
