@@ -52,6 +52,7 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
         acol_off[q + 1] = acol_off[q] + (uint64_t)((panel_ncols[q] + kBlockCols - 1) / kBlockCols) * kBlockCols;
     std::vector<uint32_t> which;  // panels routed to the brick kernel, ascending
     const uint64_t slots = layout_brick_slots(p, panel_ncols, which);
+    p.brick_panel_ids = which;
     p.brick_cols.assign(slots * kBrickCols, 0u);
     p.brick_recs.assign(slots * kBrickRecWords, 0u);  // empty slots: zero records
     p.brick_rec_off.resize(slots + 1);

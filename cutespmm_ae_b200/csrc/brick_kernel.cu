@@ -227,7 +227,7 @@ bool brick_supports(uint32_t N, uint64_t ldb, uint64_t ldc, const void *B, const
 
 cudaError_t launch_brick(const BrickArgs &a, int sm_count, cudaStream_t s)
 {
-    if (a.num_bricks == 0) return cudaSuccess;
+    if (a.num_bricks == 0 || a.num_panels == 0) return cudaSuccess;
     if (a.round_b) {
         if (a.N % 128 == 0) return launch_brick_t<16, true>(a, sm_count, s);
         if (a.N % 64 == 0) return launch_brick_t<8, true>(a, sm_count, s);

@@ -256,6 +256,26 @@ int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, 
     by += (h.nnz + 2) * sizeof(Pair);
     e = launch_pack_pairs(cols_dev, vals_dev, p->d_pairs, h.nnz, (uint32_t)K, p->d_status + 1, p->sm_count, s);
     if (e != cudaSuccess) return bail(e, "packing the nonzeros");
+    {   // largest column of every panel (4 bytes per panel to the host): what the row-block host-buffer call schedules by
+        const uint64_t P = h.num_panels();
+        uint32_t *d_max = nullptr;
+        try {
+            h.panel_max_col.assign(P, 0u);
+        } catch (const std::bad_alloc &) {
+            delete p;
+            return fail(CUTESPMM_ENOMEM, "host allocation failed");
+        }
+        if (P && h.nnz) {
+            if ((e = cudaMalloc(&d_max, P * sizeof(uint32_t))) != cudaSuccess ||
+                (e = launch_panel_max_col(static_cast<const uint32_t *>(p->d_row_ptr), p->d_pairs, (uint32_t)M, (uint32_t)P, d_max, p->sm_count, s)) != cudaSuccess ||
+                (e = cudaMemcpyAsync(h.panel_max_col.data(), d_max, P * sizeof(uint32_t), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+                (e = cudaStreamSynchronize(s)) != cudaSuccess) {
+                if (d_max) cudaFree(d_max);
+                return bail(e, "panel column ranges");
+            }
+            cudaFree(d_max);
+        }
+    }
     // panel analysis and brick packing on the device (paths auto and brick); the per-panel column counts visit the host,
     // where each panel's kernel is chosen and the brick slots and work lists are laid out
     uint32_t *d_ncols = nullptr, *d_acols = nullptr, *d_which = nullptr;
@@ -432,7 +452,7 @@ int cutespmm_plan_decode_csr(const cutespmm_plan_t *p, uint64_t *rowPtr, uint32_
 }
 
 static RowsArgs rows_args(const cutespmm_plan *p, bool all_rows, const float *B, uint64_t ldb, float *C, uint64_t ldc,
-                          uint32_t N)
+                          uint32_t N, const cutespmm_item_range *rg = nullptr)
 {
     const HostPlan &h = p->host;
     RowsArgs a{};
@@ -451,9 +471,21 @@ static RowsArgs rows_args(const cutespmm_plan *p, bool all_rows, const float *B,
     a.N = N;
     a.status = p->d_status;
     a.row_map = static_cast<const uint32_t *>(p->d_row_map);
+    if (rg) {  // a sub-range of the lists: 16-byte tiles, chunks and fix-up entries
+        const uint32_t t0 = all_rows ? rg->ta0 : rg->t0, t1 = all_rows ? rg->ta1 : rg->t1;
+        const uint32_t c0 = all_rows ? rg->ca0 : rg->c0, c1 = all_rows ? rg->ca1 : rg->c1;
+        const uint32_t l0 = all_rows ? rg->la0 : rg->l0, l1 = all_rows ? rg->la1 : rg->l1;
+        a.tiles = static_cast<const char *>(a.tiles) + (size_t)t0 * sizeof(Tile);
+        a.chunks = static_cast<const char *>(a.chunks) + (size_t)c0 * sizeof(Chunk);
+        a.long_rows = static_cast<const char *>(a.long_rows) + (size_t)l0 * sizeof(LongRow);
+        a.num_tiles = t1 - t0;
+        a.num_chunks = c1 - c0;
+        a.num_long_rows = l1 - l0;
+    }
     return a;
 }
-static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N)
+static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N,
+                            const cutespmm_item_range *rg = nullptr)
 {
     BrickArgs a{};
     a.cols = static_cast<const uint32_t *>(p->d_bcols);
@@ -470,6 +502,12 @@ static BrickArgs brick_args(const cutespmm_plan *p, const float *B, uint64_t ldb
     a.round_b = (p->host.opts.flags & CUTESPMM_FLAG_ROUND_B_NEAREST) ? 1u : 0u;
     a.status = p->d_status;
     a.row_map = static_cast<const uint32_t *>(p->d_row_map);
+    if (rg) {  // the kernel numbers its panels from panel_first[0]: hand it the sub-list
+        a.panel_first += rg->p0;
+        a.panel_last += rg->p0;
+        a.num_panels = rg->p1 - rg->p0;
+        if (a.num_panels == 0) a.num_bricks = 0;
+    }
     return a;
 }
 
@@ -521,6 +559,14 @@ int cutespmm_spmm_launch_count(const cutespmm_plan_t *p, uint32_t N)
 int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N,
                   void *stream)
 {
+    return cutespmm_internal_spmm_range(p, B, ldb, C, ldc, N, stream, nullptr);
+}
+
+}  // extern "C"
+
+int cutespmm_internal_spmm_range(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N, void *stream,
+                                 const cutespmm_item_range *rg)
+{
     if (!p) return fail(CUTESPMM_EINVAL, "plan is NULL");
     if (!p->on_device) return fail(CUTESPMM_EUNSUPPORTED, "host-only plan: build it with cutespmm_plan_create on a CUDA device to execute it");
     if (N == 0) return CUTESPMM_OK;
@@ -539,23 +585,26 @@ int cutespmm_spmm(const cutespmm_plan_t *p, const float *B, uint64_t ldb, float 
         const uint32_t nw = N - n0 < kScratchCols ? N - n0 : kScratchCols;
         cudaError_t e;
         const bool slab = p->host.slab_panels && slab_supports(nw, ldb, ldc, B + n0, C + n0);
+        if (slab && rg) return fail(CUTESPMM_EUNSUPPORTED, "a plan with slab panels runs whole");
         if (slab) {
             SlabArgs sa = slab_args(p, B + n0, ldb, C + n0, ldc, nw);
             if ((e = launch_slab(sa, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "slab kernel launch");
         }
         const bool brick = use_brick(p, B + n0, ldb, C + n0, ldc, nw);
         if (brick) {
-            BrickArgs ba = brick_args(p, B + n0, ldb, C + n0, ldc, nw);
+            BrickArgs ba = brick_args(p, B + n0, ldb, C + n0, ldc, nw, rg);
             if ((e = launch_brick(ba, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "brick kernel launch");
         }
         // brick panels whose shape the brick kernel does not take (N not a multiple of 32, unaligned
         // operands) are executed by the row kernel from its all-rows work list
-        RowsArgs ra = rows_args(p, (!brick && p->host.num_bricks) || (!slab && p->host.slab_panels), B + n0, ldb, C + n0, ldc, nw);
+        RowsArgs ra = rows_args(p, (!brick && p->host.num_bricks) || (!slab && p->host.slab_panels), B + n0, ldb, C + n0, ldc, nw, rg);
         if ((e = launch_rows(ra, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "row kernel launch");
         if ((e = launch_fixup(ra, s)) != cudaSuccess) return fail_cuda(e, "fix-up kernel launch");
     }
     return CUTESPMM_OK;
 }
+
+extern "C" {
 
 int cutespmm_sddmm(const cutespmm_plan_t *p, const float *X, uint64_t ldx, const float *Y, uint64_t ldy, uint32_t N, int scale_by_values,
                    float *out, void *stream)

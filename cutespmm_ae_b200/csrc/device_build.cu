@@ -79,6 +79,21 @@ __global__ void __launch_bounds__(256) panel_columns_kernel(const uint32_t *__re
     }
 }
 
+// maxcol[q] = largest column index among the nonzeros of 16-row panel q (0 when it has none); one warp per panel
+__global__ void __launch_bounds__(256) panel_max_col_kernel(const uint32_t *__restrict__ row_ptr, const uint2 *__restrict__ pairs, uint32_t M,
+                                                            uint32_t num_panels, uint32_t *__restrict__ maxcol)
+{
+    const uint32_t lane = threadIdx.x & 31, warps = gridDim.x * (blockDim.x / 32);
+    for (uint32_t q = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5); q < num_panels; q += warps) {
+        const uint32_t r0 = q * kPanelRows, r1 = min(M, r0 + kPanelRows);
+        const uint32_t j0 = __ldg(row_ptr + r0), j1 = __ldg(row_ptr + r1);
+        uint32_t m = 0;
+        for (uint32_t j = j0 + lane; j < j1; j += 32) m = max(m, __ldg(&pairs[j].x));
+        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, o));
+        if (lane == 0) maxcol[q] = m;
+    }
+}
+
 // position of (row r, column c) of a 16 x 8 brick in its record, in mma.m16n8k8 A-fragment order (plan.hpp)
 __device__ __forceinline__ uint32_t frag_index(uint32_t r, uint32_t c) { return ((r & 7u) * 4u + (c & 3u)) * 4u + (r >> 3) + 2u * (c >> 2); }
 
@@ -164,6 +179,16 @@ cudaError_t launch_panel_columns(const uint32_t *row_ptr, const void *pairs, uin
     const uint32_t blocks = num_panels < (uint32_t)sm_count * 16 ? num_panels : (uint32_t)sm_count * 16;
     panel_columns_kernel<<<blocks, 256, kDevPanelMax * sizeof(uint32_t), s>>>(row_ptr, static_cast<const uint2 *>(pairs), M, num_panels,
                                                                               ncols, acols);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_panel_max_col(const uint32_t *row_ptr, const void *pairs, uint32_t M, uint32_t num_panels, uint32_t *maxcol, int sm_count,
+                                 cudaStream_t s)
+{
+    if (num_panels == 0) return cudaSuccess;
+    const uint32_t want = (num_panels + 7) / 8;
+    const uint32_t blocks = want < (uint32_t)sm_count * 8 ? want : (uint32_t)sm_count * 8;
+    panel_max_col_kernel<<<blocks, 256, 0, s>>>(row_ptr, static_cast<const uint2 *>(pairs), M, num_panels, maxcol);
     return cudaGetLastError();
 }
 

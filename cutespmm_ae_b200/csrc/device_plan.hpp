@@ -108,6 +108,8 @@ cudaError_t launch_pack_pairs(const uint32_t *cols, const float *vals, void *pai
 constexpr uint32_t kDevPanelMax = 8192;
 cudaError_t launch_panel_columns(const uint32_t *row_ptr, const void *pairs, uint32_t M, uint32_t num_panels, uint32_t *ncols,
                                  uint32_t *acols, int sm_count, cudaStream_t s);
+cudaError_t launch_panel_max_col(const uint32_t *row_ptr, const void *pairs, uint32_t M, uint32_t num_panels, uint32_t *maxcol, int sm_count,
+                                 cudaStream_t s);
 cudaError_t launch_brick_fill(const uint32_t *row_ptr, const void *pairs, uint32_t M, const uint32_t *which,
                               const uint32_t *first_slot, const uint32_t *last_slot, uint32_t num_brick_panels, const uint32_t *ncols,
                               const uint32_t *acols, uint32_t *bcols, uint32_t *brecs, int sm_count, cudaStream_t s);

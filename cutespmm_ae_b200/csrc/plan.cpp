@@ -60,6 +60,7 @@ static std::vector<uint32_t> analyze_panels(HostPlan &p)
             ncols[q] = (uint32_t)(std::unique(buf.begin(), buf.end()) - buf.begin());
         }
     }
+    p.panel_max_col.assign(P, 0u);
     p.blocked_row_ptr.assign(P + 1, 0);
     for (uint64_t q = 0; q < P; ++q) {
         const uint32_t nb = (ncols[q] + kBlockCols - 1) / kBlockCols;
@@ -80,6 +81,7 @@ static std::vector<uint32_t> analyze_panels(HostPlan &p)
             std::sort(buf.begin(), buf.end());
             const size_t n = std::unique(buf.begin(), buf.end()) - buf.begin();
             std::copy(buf.begin(), buf.begin() + n, p.active_cols.begin() + col_off[q]);
+            if (n) p.panel_max_col[q] = buf[n - 1];
         }
     }
     return ncols;

@@ -91,6 +91,10 @@ struct HostPlan {
     std::vector<uint32_t> blocked_row_ptr;  // num_panels+1
     std::vector<uint32_t> active_cols;      // per panel ascending distinct columns, zero-padded to x16
 
+    // largest column index of every 16-row panel (0 for an empty panel): which rows of B a block of rows needs, for
+    // the host-buffer call that lets rows of C leave while later rows of B still arrive
+    std::vector<uint32_t> panel_max_col;
+
     // ---- row kernel over every row (used when a product's N does not fit the brick kernel) ----
     std::vector<Tile> tiles_all;
     std::vector<Chunk> chunks_all;

@@ -70,7 +70,7 @@ template <class Fn> void for_each_array(HostPlan &h, Fn &&fn)
     fn(7, h.blocked_row_ptr); fn(8, h.active_cols); fn(9, h.tiles_all); fn(10, h.chunks_all); fn(11, h.long_rows_all);
     fn(12, h.brick_cols); fn(13, h.brick_recs); fn(14, h.brick_rec_off); fn(15, h.panel_first_brick); fn(16, h.panel_last_brick);
     fn(17, h.brick_panel_ids); fn(18, h.slab_cols); fn(19, h.slab_recs); fn(20, h.slab_rec_off); fn(21, h.slab_first);
-    fn(22, h.slab_last); fn(23, h.slab_ids); fn(24, h.slab_path); fn(25, h.row_map);
+    fn(22, h.slab_last); fn(23, h.slab_ids); fn(24, h.slab_path); fn(25, h.row_map); fn(26, h.panel_max_col);
 }
 
 }  // namespace

@@ -5,8 +5,24 @@
 
 #include <cstdint>
 #include <string>
+#include <vector>
 
 #include "plan.hpp"
+
+// A contiguous range of the plan's work items (tiles, chunks and fix-up entries of the row kernel -- of its own list and
+// of the list over every row -- and panels of the brick kernel): what one launch covers when a product is issued in
+// blocks of rows.
+struct cutespmm_item_range {
+    uint32_t t0 = 0, t1 = 0, c0 = 0, c1 = 0, l0 = 0, l1 = 0;        // row kernel: tiles, chunks, long rows
+    uint32_t ta0 = 0, ta1 = 0, ca0 = 0, ca1 = 0, la0 = 0, la1 = 0;  // the same lists over every row
+    uint32_t p0 = 0, p1 = 0;                                        // brick panels (ordinals)
+};
+// One block of rows of the row-block host-buffer call: rows [row0, row1) of C, computed once rows [0, need) of B are
+// on the device.
+struct cutespmm_row_block {
+    uint32_t row0 = 0, row1 = 0, need = 0;
+    cutespmm_item_range items;
+};
 
 struct cutespmm_plan {
     cutespmm::HostPlan host;
@@ -32,6 +48,13 @@ struct cutespmm_plan {
     cudaEvent_t ev_entry = nullptr, ev_done = nullptr;
     cudaEvent_t ev_in[kMaxWindows] = {}, ev_x0[kMaxWindows] = {}, ev_x1[kMaxWindows] = {}, ev_k0[kMaxWindows] = {}, ev_k1[kMaxWindows] = {};
 
+    // the single-GPU host-buffer call in blocks of rows (banded matrices): C rows leave while later rows of B arrive
+    static constexpr int kMaxRowBlocks = 16;
+    std::vector<cutespmm_row_block> row_blocks;  // cut at the first such call
+    bool row_blocks_tried = false;
+    uint32_t row_blocks_n = 0;                   // the N they were cut for
+    cudaEvent_t rb_in[kMaxRowBlocks] = {}, rb_k0[kMaxRowBlocks] = {}, rb_k1[kMaxRowBlocks] = {};
+
     ~cutespmm_plan()
     {
         if (!on_device) return;
@@ -47,6 +70,9 @@ struct cutespmm_plan {
         for (int w = 0; w < kMaxWindows; ++w)
             for (cudaEvent_t ev : {ev_in[w], ev_x0[w], ev_x1[w], ev_k0[w], ev_k1[w]})
                 if (ev) cudaEventDestroy(ev);
+        for (int i = 0; i < kMaxRowBlocks; ++i)
+            for (cudaEvent_t ev : {rb_in[i], rb_k0[i], rb_k1[i]})
+                if (ev) cudaEventDestroy(ev);
         for (cudaStream_t st : {s_in, s_x, s_out})
             if (st) cudaStreamDestroy(st);
         if (cur != device && cur >= 0) cudaSetDevice(cur);
@@ -59,3 +85,7 @@ namespace cutespmm {
 int fail_status(int status, const std::string &msg);          // records the message, returns status
 int fail_cuda_status(cudaError_t e, const char *what);        // same for a CUDA error
 }  // namespace cutespmm
+
+// cutespmm_spmm restricted to a range of work items (nullptr: everything).  capi.cu
+int cutespmm_internal_spmm_range(const cutespmm_plan *p, const float *B, uint64_t ldb, float *C, uint64_t ldc, uint32_t N, void *stream,
+                                 const cutespmm_item_range *range);

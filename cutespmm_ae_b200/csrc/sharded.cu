@@ -232,6 +232,157 @@ int ensure_staging(cutespmm_plan *p, uint32_t N, bool sharded, Windows &w)
     return CUTESPMM_OK;
 }
 
+// ---- the single-GPU host-buffer call in blocks of rows -------------------------------------------------------------
+// For a matrix whose rows name a bounded, advancing range of columns (banded and block-structured matrices) the rows
+// of C of an early block need only the leading rows of B.  The call then uploads B in row order, launches the product
+// block of rows by block of rows as soon as the rows of B a block needs are on the device, and sends each block's
+// rows of C back while later rows of B are still arriving: the two PCIe directions overlap at full width (no column
+// windows, so every launch keeps the full-width kernels).
+
+// Cuts the plan's rows into blocks and finds, per block, its work items and how many leading rows of B it needs.
+// Returns false when the matrix does not qualify (half of the rows already need more than 80 % of B, too small, ...).
+bool cut_row_blocks(cutespmm_plan *p, uint32_t N)
+{
+    const HostPlan &h = p->host;
+    p->row_blocks.clear();
+    if (!h.row_map.empty() || h.slab_panels || h.panel_max_col.size() != h.num_panels() || h.M < 4096) return false;
+    const uint64_t c_bytes = h.M * (uint64_t)N * sizeof(float);
+    // blocks of about 16 MiB of C: every block costs about 40 us of hand-over between the copy engines and its kernel
+    // (measured: 6-8 blocks are best for 134 MB, 16 blocks lose what the finer overlap gains)
+    int R = (int)std::min<uint64_t>(cutespmm_plan::kMaxRowBlocks, c_bytes / (16u << 20));
+    if (R < 2) return false;
+    // boundaries: near equal row counts, on 16-row panel boundaries, never inside a tile of either tile list
+    auto snap = [&](uint64_t target, const std::vector<Tile> &tiles) {
+        auto it = std::upper_bound(tiles.begin(), tiles.end(), target, [](uint64_t r, const Tile &t) { return r < t.row_begin; });
+        if (it != tiles.begin()) {
+            const Tile &t = *(it - 1);
+            if (t.row_begin < target && target < t.row_end) return (uint64_t)t.row_begin;
+        }
+        return target;
+    };
+    std::vector<uint32_t> bounds(1, 0u);
+    for (int i = 1; i < R; ++i) {
+        uint64_t r = (uint64_t)i * h.M / R / kPanelRows * kPanelRows;
+        for (int pass = 0; pass < 4; ++pass) {  // the two tile lists may pull the boundary down in turn
+            const uint64_t before = r;
+            r = snap(r, h.tiles);
+            r = snap(r, h.tiles_all);
+            if (r == before) break;
+        }
+        if (r > bounds.back()) bounds.push_back((uint32_t)r);
+    }
+    bounds.push_back((uint32_t)h.M);
+    auto first_at = [](const auto &list, uint32_t row, auto key) {
+        return (uint32_t)(std::lower_bound(list.begin(), list.end(), row, [&](const auto &x, uint32_t r) { return key(x) < r; }) - list.begin());
+    };
+    uint32_t need = 0;
+    for (size_t i = 0; i + 1 < bounds.size(); ++i) {
+        cutespmm_row_block b;
+        b.row0 = bounds[i];
+        b.row1 = bounds[i + 1];
+        auto &it = b.items;
+        it.t0 = first_at(h.tiles, b.row0, [](const Tile &t) { return t.row_begin; });
+        it.t1 = first_at(h.tiles, b.row1, [](const Tile &t) { return t.row_begin; });
+        it.c0 = first_at(h.chunks, b.row0, [](const Chunk &c) { return c.row; });
+        it.c1 = first_at(h.chunks, b.row1, [](const Chunk &c) { return c.row; });
+        it.l0 = first_at(h.long_rows, b.row0, [](const LongRow &l) { return l.row; });
+        it.l1 = first_at(h.long_rows, b.row1, [](const LongRow &l) { return l.row; });
+        it.ta0 = first_at(h.tiles_all, b.row0, [](const Tile &t) { return t.row_begin; });
+        it.ta1 = first_at(h.tiles_all, b.row1, [](const Tile &t) { return t.row_begin; });
+        it.ca0 = first_at(h.chunks_all, b.row0, [](const Chunk &c) { return c.row; });
+        it.ca1 = first_at(h.chunks_all, b.row1, [](const Chunk &c) { return c.row; });
+        it.la0 = first_at(h.long_rows_all, b.row0, [](const LongRow &l) { return l.row; });
+        it.la1 = first_at(h.long_rows_all, b.row1, [](const LongRow &l) { return l.row; });
+        it.p0 = first_at(h.brick_panel_ids, b.row0 / kPanelRows, [](uint32_t q) { return q; });
+        it.p1 = first_at(h.brick_panel_ids, (b.row1 + kPanelRows - 1) / kPanelRows, [](uint32_t q) { return q; });
+        for (uint64_t q = b.row0 / kPanelRows; q < (b.row1 + kPanelRows - 1) / kPanelRows; ++q)
+            if (h.row_ptr[std::min<uint64_t>(h.M, (q + 1) * kPanelRows)] > h.row_ptr[q * kPanelRows]) need = std::max(need, h.panel_max_col[q] + 1);
+        b.need = need;  // running maximum: B arrives in row order
+        p->row_blocks.push_back(b);
+    }
+    if (h.brick_panels && h.brick_panel_ids.size() != h.brick_panels) { p->row_blocks.clear(); return false; }
+    const size_t half = p->row_blocks.size() / 2;
+    if (p->row_blocks.size() < 2 || (uint64_t)p->row_blocks[half - 1].need * 10 > h.K * 8) {
+        p->row_blocks.clear();
+        return false;
+    }
+    return true;
+}
+
+// rows x N floats between host and device; one plain copy when both sides are contiguous (faster than the 2-D form)
+cudaError_t copy_rows(void *dst, uint64_t ld_dst, const void *src, uint64_t ld_src, uint32_t N, uint64_t rows, cudaMemcpyKind kind, cudaStream_t s)
+{
+    if (ld_dst == N && ld_src == N) return cudaMemcpyAsync(dst, src, rows * N * sizeof(float), kind, s);
+    return cudaMemcpy2DAsync(dst, ld_dst * sizeof(float), src, ld_src * sizeof(float), (size_t)N * sizeof(float), rows, kind, s);
+}
+
+int run_row_blocks(cutespmm_plan *p, const float *B_host, uint64_t ldb, float *C_host, uint64_t ldc, uint32_t N, cudaStream_t s, float *kernel_ms)
+{
+    const uint64_t M = p->host.M, K = p->host.K;
+    const uint64_t ldd = (uint64_t)(N + 3) / 4 * 4;
+    cudaError_t e;
+    if (!p->rb_in[0])
+        for (int i = 0; i < cutespmm_plan::kMaxRowBlocks; ++i)
+            if ((e = cudaEventCreateWithFlags(&p->rb_in[i], cudaEventDisableTiming)) != cudaSuccess || (e = cudaEventCreate(&p->rb_k0[i])) != cudaSuccess ||
+                (e = cudaEventCreate(&p->rb_k1[i])) != cudaSuccess)
+                return fail_cuda_status(e, "cudaEventCreate");
+    auto drain = [&]() {
+        cudaStreamSynchronize(p->s_in);
+        cudaStreamSynchronize(p->s_out);
+        cudaStreamSynchronize(s);
+    };
+    NvtxRange range("cutespmm: product from host buffers, in blocks of rows");
+    cudaEventRecord(p->ev_entry, s);  // whatever the caller queued on `stream` comes first
+    cudaStreamWaitEvent(p->s_in, p->ev_entry, 0);
+    // All uploads are queued before the first download, so that no download waiting for its kernel sits in front of an
+    // upload in a copy queue.
+    uint64_t have = 0;  // rows of B already queued for upload
+    const size_t nb = p->row_blocks.size();
+    for (size_t i = 0; i < nb; ++i) {
+        const uint64_t upto = std::min<uint64_t>(K, p->row_blocks[i].need);  // rows of B beyond the last column any row names are never read
+        if (upto > have) {
+            if ((e = copy_rows(p->d_B + have * ldd, ldd, B_host + have * ldb, ldb, N, upto - have, cudaMemcpyHostToDevice, p->s_in)) != cudaSuccess) {
+                drain();
+                return fail_cuda_status(e, "copy of B to the device");
+            }
+            have = upto;
+        }
+        cudaEventRecord(p->rb_in[i], p->s_in);
+    }
+    for (size_t i = 0; i < nb; ++i) {
+        const cutespmm_row_block &b = p->row_blocks[i];
+        cudaStreamWaitEvent(s, p->rb_in[i], 0);
+        cudaEventRecord(p->rb_k0[i], s);
+        const int st = cutespmm_internal_spmm_range(p, p->d_B, ldd, p->d_C, ldd, N, s, &b.items);
+        if (st != CUTESPMM_OK) {
+            drain();
+            return st;
+        }
+        cudaEventRecord(p->rb_k1[i], s);
+        cudaStreamWaitEvent(p->s_out, p->rb_k1[i], 0);
+        if (b.row1 > b.row0 && (e = copy_rows(C_host + (uint64_t)b.row0 * ldc, ldc, p->d_C + (uint64_t)b.row0 * ldd, ldd, N, b.row1 - b.row0,
+                                              cudaMemcpyDeviceToHost, p->s_out)) != cudaSuccess) {
+            drain();
+            return fail_cuda_status(e, "copy of C to the host");
+        }
+    }
+    (void)M;
+    cudaEventRecord(p->ev_done, p->s_out);
+    cudaStreamWaitEvent(s, p->ev_done, 0);
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return fail_cuda_status(e, "SpMM execution");
+    if (kernel_ms) {
+        *kernel_ms = 0.f;
+        for (size_t i = 0; i < nb; ++i) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, p->rb_k0[i], p->rb_k1[i]) == cudaSuccess) *kernel_ms += ms;
+        }
+    }
+    uint32_t dev_status = 0;
+    cutespmm_plan_device_status(p, &dev_status);
+    if (dev_status) return fail_status(CUTESPMM_ETIMEOUT, "a device-side wait ran out (status " + std::to_string(dev_status) + ")");
+    return CUTESPMM_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -423,6 +574,22 @@ int cutespmm_spmm_sharded_host(cutespmm_plan_t *p, cutespmm_comm_t *comm, const 
     cudaError_t e;
     Windows wn;
     if ((st = ensure_staging(p, N, nranks > 1, wn)) != CUTESPMM_OK) return st;
+    if (nranks == 1 && N <= kScratchCols && (uint64_t)N * std::max(M, K) * sizeof(float) >= (8u << 20)) {
+        // large operands on one GPU: blocks of rows where the matrix allows it, column windows otherwise
+        if (!p->row_blocks_tried || p->row_blocks_n != N) {
+            p->row_blocks_tried = true;
+            p->row_blocks_n = N;
+            try {
+                cut_row_blocks(p, N);
+            } catch (const std::bad_alloc &) {
+                p->row_blocks.clear();
+            }
+        }
+        if (!p->row_blocks.empty()) {
+            if (exchange_ms) *exchange_ms = 0.f;
+            return run_row_blocks(p, B_host_rows, ldb, C_host, ldc, N, s, kernel_ms);
+        }
+    }
     const uint32_t nw = wn.count, wcols = wn.width;
     const uint64_t ldd = wn.ldd;
     auto drain = [&]() {
@@ -436,15 +603,21 @@ int cutespmm_spmm_sharded_host(cutespmm_plan_t *p, cutespmm_comm_t *comm, const 
     cudaEventRecord(p->ev_entry, s);
     cudaStreamWaitEvent(p->s_in, p->ev_entry, 0);
     std::vector<Transfer> t(unit.size());
+    // every upload is queued before the first download, so that no download waiting for its kernel sits in front of
+    // an upload in a copy queue
     for (uint32_t w = 0; w < nw; ++w) {
         const uint32_t c0 = w * wcols, cw = std::min(wcols, N - c0);
-        float *dB = p->d_B + (uint64_t)w * K * ldd, *dC = p->d_C + (uint64_t)w * M * ldd;
+        float *dB = p->d_B + (uint64_t)w * K * ldd;
         if (k1 > k0 && (e = cudaMemcpy2DAsync(dB + k0 * ldd, ldd * sizeof(float), B_host_rows + c0, ldb * sizeof(float),
                                               (size_t)cw * sizeof(float), k1 - k0, cudaMemcpyHostToDevice, p->s_in)) != cudaSuccess) {
             drain();
             return fail_cuda_status(e, "copy of B to the device");
         }
         cudaEventRecord(p->ev_in[w], p->s_in);
+    }
+    for (uint32_t w = 0; w < nw; ++w) {
+        const uint32_t c0 = w * wcols, cw = std::min(wcols, N - c0);
+        float *dB = p->d_B + (uint64_t)w * K * ldd, *dC = p->d_C + (uint64_t)w * M * ldd;
         if (!unit.empty()) {  // the slices of this window meet on every rank
             cudaStreamWaitEvent(p->s_x, p->ev_in[w], 0);
             cudaEventRecord(p->ev_x0[w], p->s_x);

@@ -260,3 +260,46 @@ def test_row_clustering_keeps_the_callers_row_order(oracle_mod, path, how):
         assert oracle_mod.rel_fro(ref, run(p, B)) <= PATH_TOL[path], (A.name, N)
     if path == cs.PATH_AUTO:  # the point of the option: the shuffled stencil is back on the tensor-core kernel
         assert cs.Plan.from_csr(S, reorder=how).info()["num_bricks"] > 0 and cs.Plan.from_csr(S).info()["num_bricks"] == 0
+
+
+@pytest.mark.parametrize("N,pad,path", [(128, 0, cs.PATH_AUTO), (200, 8, cs.PATH_AUTO), (64, 0, cs.PATH_ROWS), (256, 0, cs.PATH_BRICK)])
+def test_host_call_in_blocks_of_rows_on_banded_matrices(oracle_mod, N, pad, path):
+    """On one GPU, operands of many megabytes and a matrix whose rows name an advancing range of columns, the host call
+    uploads B in row order, multiplies block of rows by block of rows and returns each block's rows of C while B is
+    still arriving.  Every block boundary, both work lists (N = 200 is not a width the brick kernel takes) and padded
+    leading dimensions must give the oracle's product; a matrix that does not qualify (a graph whose every block of
+    rows names all of B) takes the column-window path and must be right as well."""
+    A = g.stencil9(384)  # M = K = 147456: 75 MB at N = 128 -> 9 blocks of rows
+    p = cs.Plan.from_csr(A, path=path, split_nnz=256)
+    Bfull = g.dense_operand(A.K, N + pad, 91).pin_memory()
+    Cfull = torch.full((A.M, N + pad), float("nan")).pin_memory()
+    Bh, Ch = Bfull[:, :N], Cfull[:, :N]
+    for _ in range(2):  # the second call reuses the cut and the staging
+        Ch.fill_(float("nan"))
+        _, ms = p.spmm_host(Bh, Ch)
+        assert ms > 0.0
+        want = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, Bh.contiguous().numpy(), A.M, A.K)
+        assert oracle_mod.rel_fro(want, Ch.contiguous().numpy()) <= PATH_TOL[path]
+    if pad:
+        assert torch.isnan(Cfull[:, N:]).all()
+    G = g.rmat(16, 16, seed=93, values="uniform")  # hub rows (chunks + fix-up) and no band: column windows
+    pg = cs.Plan.from_csr(G)
+    Bg = g.dense_operand(G.K, 128, 94).pin_memory()
+    Cg, _ = pg.spmm_host(Bg)
+    want = oracle_mod.spmm_csr(G.row_ptr, G.cols, G.vals, Bg.numpy(), G.M, G.K)
+    assert oracle_mod.rel_fro(want, Cg.numpy()) <= REL_FRO_TOL_FP32 * 5
+    # a banded matrix with long rows inside the band: the chunk and fix-up lists are cut by blocks too
+    rows, K2 = 1 << 16, 1 << 16
+    lens = np.full(rows, 6, dtype=np.int64)
+    lens[::997] = 700
+    rp = np.zeros(rows + 1, dtype=np.int64)
+    np.cumsum(lens, out=rp[1:])
+    r_of = np.repeat(np.arange(rows), lens)
+    cols = np.clip(r_of + (np.arange(rp[-1]) - rp[r_of]) - 3, 0, K2 - 1)
+    vals = np.linspace(-1.0, 1.0, rp[-1]).astype(np.float32)
+    pb = cs.Plan(rows, K2, rp, cols.astype(np.uint32), vals)
+    assert pb.info()["num_long_rows"] > 0
+    Bb = g.dense_operand(K2, 128, 95).pin_memory()
+    Cb, _ = pb.spmm_host(Bb)
+    want = oracle_mod.spmm_csr(rp.astype(np.uint64), cols.astype(np.uint32), vals, Bb.numpy(), rows, K2)
+    assert oracle_mod.rel_fro(want, Cb.numpy()) <= REL_FRO_TOL
