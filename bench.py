@@ -74,6 +74,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = chosen by operand size)")
     ap.add_argument("--matrices", default="", help="a folder of MatrixMarket files: print the per-matrix table instead of the benchmark line")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="--matrices: skip the reference's own kernel")
     ap.add_argument("--reorder", default="none", choices=["none", "cluster", "similar"], help="plan-time reordering option")
     return ap.parse_args()
 
@@ -424,24 +425,34 @@ def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak, refer
     return out
 
 
-def reference_gpu_block(workload, N, mtx=None):
+def reference_gpu_blocks(workload, Ns, mtx_files=None, timeout=600):
     """The reference project's GPU path (its HRPB preprocessing, work list and kernel SpMM<NUM_WARPS, ILP_LEVEL>,
     kernel.cu:119-288) built for sm_100a into oracle/_ref by oracle/Makefile, run by oracle/ref_gpu_run.py in a process
-    of its own (the reference's host code exits on errors): result checked against the CPU oracle first, then its first
-    (cold) launch and the mean of ten more."""
+    of its own (the reference's host code exits on errors): results checked against the CPU oracle first, then timed.
+    Returns {(matrix name, N): block}; a (matrix, N) the process did not reach is missing."""
     if not (ROOT / "oracle" / "_ref" / "libcutespmm_ref_gpu.so").exists():
-        return {"unavailable": "oracle/_ref/libcutespmm_ref_gpu.so is not built (needs a checkout of the reference next to this repository)"}
+        return {None: {"unavailable": "oracle/_ref/libcutespmm_ref_gpu.so is not built (needs a checkout of the reference next to this repository)"}}
+    what = ["--mtx", ",".join(str(f) for f in mtx_files)] if mtx_files else ["--workload", workload]
     try:
-        what = ["--mtx", str(mtx)] if mtx else ["--workload", workload]
-        res = subprocess.run([sys.executable, str(ROOT / "oracle" / "ref_gpu_run.py"), *what, "--N", str(N)],
-                             capture_output=True, text=True, timeout=240)
-    except subprocess.TimeoutExpired:
-        return {"unavailable": "the reference's GPU path did not finish within 240 s"}
-    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
-    if res.returncode != 0 or not lines:
-        tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or [""]
-        return {"unavailable": f"the reference's GPU path ended with code {res.returncode}: {tail[0][:200]}"}
-    return json.loads(lines[-1])
+        res = subprocess.run([sys.executable, str(ROOT / "oracle" / "ref_gpu_run.py"), *what, "--N", ",".join(str(n) for n in Ns)],
+                             capture_output=True, text=True, timeout=timeout)
+        out, code, err = res.stdout, res.returncode, res.stderr
+    except subprocess.TimeoutExpired as e:
+        out, code, err = (e.stdout or b"").decode() if isinstance(e.stdout, bytes) else (e.stdout or ""), -1, f"did not finish within {timeout} s"
+    blocks = {}
+    for ln in out.splitlines():
+        if ln.startswith("{"):
+            d = json.loads(ln)
+            blocks[(d.pop("matrix"), d.pop("N"))] = d
+    if code != 0:
+        tail = (err or "").strip().splitlines()[-1:] or [""]
+        blocks[None] = {"unavailable": f"the reference's GPU path ended with code {code}: {tail[0][:200]}"}
+    return blocks
+
+
+def reference_gpu_block(workload, N):
+    blocks = reference_gpu_blocks(workload, [N], timeout=240)
+    return blocks.get((workload, N)) or blocks.get(None) or {"unavailable": "no result"}
 
 
 def run_ours(args):
@@ -688,6 +699,8 @@ def run_matrices(args):
     if not files:
         raise SystemExit(f"no .mtx files under {args.matrices}")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ref_blocks = {None: {"unavailable": "skipped (--no-reference-gpu)"}} if args.no_reference_gpu else \
+        reference_gpu_blocks("", (32, 128, 512), mtx_files=files, timeout=1200)  # one process for all files
     print("matrix, rows, nnz, N(feature size), path, GFLOPS, relFro (sampled rows), reference kernel GFLOPS (same GPU), ratio")
     table = []
     for f in files:
@@ -698,7 +711,7 @@ def run_matrices(args):
         rp = np.zeros(r.M + 1, dtype=np.int64)
         np.cumsum(np.bincount(rr, minlength=r.M), out=rp[1:])
         A = g.CsrMatrix(r.M, r.K, torch.from_numpy(rp).to(dev), torch.from_numpy(cc).to(dev), torch.ones(cc.size, dtype=torch.float32, device=dev), f.stem)
-        plan, _, _ = build_plan(cs, A, "auto", args.reorder)
+        plan, _, _ = build_plan(cs, A, args.path, args.reorder)
         info = plan.info()
         for N in (32, 128, 512):
             B = g.dense_operand(A.K, N, 4242, "normal", device=dev)
@@ -706,7 +719,7 @@ def run_matrices(args):
             ms, _, _ = time_steps(lambda: plan.spmm(B, C), 10, 3, flush, None, dev)
             err, _ = parity_sample(A, B, C, n_random=1 << 10)
             gf = 2.0 * A.nnz * N / (ms * 1e-3) / 1e9
-            ref = reference_gpu_block("", N, mtx=f)
+            ref = ref_blocks.get((f.stem, N)) or ref_blocks.get(None) or {"unavailable": "not reached"}
             ref_gf = ref.get("gflops_l2_flushed")
             kind = "brick+rows" if info["num_bricks"] and info["num_tiles"] else ("brick" if info["num_bricks"] else "rows")
             row = {"matrix": f.stem, "rows": A.M, "nnz": A.nnz, "N": N, "path": kind, "gflops": round(gf, 1), "rel_fro": err,

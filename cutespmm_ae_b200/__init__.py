@@ -30,6 +30,8 @@ FLAG_ROUND_B_NEAREST = 1
 REORDER_NONE, REORDER_CLUSTER_ROWS, REORDER_SIMILAR_ROWS = 0, 1, 2
 B_RESIDENT, B_FROM_ROOT, B_ROW_SHARDED = 0, 1, 2  # cutespmm_b_mode_t
 COMM_ID_BYTES = 128
+# What Plan(...) passes as cutespmm_options_t::min_brick_panels when the caller gives none (0 = the library's default).
+default_min_brick_panels = 0
 
 
 class CuteSpmmError(RuntimeError):
@@ -41,7 +43,7 @@ class CuteSpmmError(RuntimeError):
 class Options(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("path", C.c_uint32), ("split_nnz", C.c_uint32),
                 ("tile_nnz", C.c_uint32), ("brick_density", C.c_float), ("flags", C.c_uint32), ("reorder", C.c_uint32),
-                ("reserved", C.c_uint32)]
+                ("min_brick_panels", C.c_uint32)]
 
 
 class PlanInfo(C.Structure):
@@ -124,13 +126,15 @@ class Plan:
     of SPMM_TC (spmm.cu:691-822).  `host_only=True` builds the plan without touching CUDA."""
 
     def __init__(self, M: int, K: int, row_ptr, cols, vals, *, path: int = PATH_AUTO, split_nnz: int = 0,
-                 tile_nnz: int = 0, brick_density: float = 0.0, round_b_nearest: bool = False, reorder: int | str = 0, host_only: bool = False):
+                 tile_nnz: int = 0, brick_density: float = 0.0, round_b_nearest: bool = False, reorder: int | str = 0, min_brick_panels: int = 0,
+                 host_only: bool = False):
         self._h = C.c_void_p()
         rp, cc, vv = _np(row_ptr, np.uint64), _np(cols, np.uint32), _np(vals, np.float32)
         if rp.shape[0] != M + 1:
             raise ValueError("row_ptr must have M+1 entries")
         reorder = {"none": REORDER_NONE, "cluster": REORDER_CLUSTER_ROWS, "similar": REORDER_SIMILAR_ROWS}.get(reorder, reorder)
-        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, FLAG_ROUND_B_NEAREST if round_b_nearest else 0, reorder)
+        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, brick_density, FLAG_ROUND_B_NEAREST if round_b_nearest else 0, reorder,
+                       min_brick_panels or default_min_brick_panels)
         fn = lib.cutespmm_plan_build_host if host_only else lib.cutespmm_plan_create
         _check(fn(C.byref(self._h), M, K, rp.ctypes.data, cc.ctypes.data, vv.ctypes.data, C.byref(opts)))
         self.M, self.K, self.nnz = M, K, int(rp[-1])
@@ -142,7 +146,7 @@ class Plan:
 
     @classmethod
     def from_device_csr(cls, M: int, K: int, row_ptr, cols, vals, *, path: int = PATH_AUTO, split_nnz: int = 0,
-                        tile_nnz: int = 0, stream=None) -> "Plan":
+                        tile_nnz: int = 0, min_brick_panels: int = 0, stream=None) -> "Plan":
         """From CSR tensors that live on the GPU (row_ptr: M+1 int32, cols: nnz int32, vals: nnz float32): the
         nonzeros are packed, the 16-row panels analysed and the tensor-core bricks written on the device
         (cutespmm_plan_create_device); path auto, rows or brick."""
@@ -155,7 +159,7 @@ class Plan:
             raise ValueError("row_ptr must have M+1 entries; cols and vals the same length")
         self = cls.__new__(cls)
         self._h = C.c_void_p()
-        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, 0.0, 0)
+        opts = Options(C.sizeof(Options), path, split_nnz, tile_nnz, 0.0, 0, 0, min_brick_panels or default_min_brick_panels)
         st = (stream or torch.cuda.current_stream(vals.device)).cuda_stream
         _check(lib.cutespmm_plan_create_device(C.byref(self._h), M, K, row_ptr.data_ptr(), cols.data_ptr(), vals.data_ptr(),
                                                C.byref(opts), st))

@@ -37,6 +37,7 @@ static void fill_default_options(cutespmm_options_t &o, const cutespmm_options_t
     if (o.split_nnz > kMaxSplitNnz) o.split_nnz = kMaxSplitNnz;
     if (o.tile_nnz == 0) o.tile_nnz = kDefaultTileCost;
     if (o.brick_density <= 0.0f) o.brick_density = 0.125f;
+    if (o.min_brick_panels == 0) o.min_brick_panels = kMinBrickPanels;
 }
 
 // Distinct columns of every 16-row panel, ascending: the HRPB view (data.cu:116-149 counts them,
@@ -296,6 +297,16 @@ void choose_panel_paths(HostPlan &p, const std::vector<uint32_t> &panel_ncols)
         bool long_row = false;
         for (uint64_t r = r0; r < r1; ++r) long_row |= (p.row_ptr[r + 1] - p.row_ptr[r]) > p.opts.split_nnz;
         p.row_path[q] = (fill >= p.opts.brick_density && !long_row) ? 1 : 0;
+    }
+    if (p.opts.path == CUTESPMM_PATH_AUTO) {
+        // The brick kernel is a grid of independent per-warp pipelines, one panel at a time each: below about two
+        // panels per warp of a full grid (148 SMs x 15 warps) most of them idle while the others walk their panel
+        // brick by brick, and a second launch for the remaining rows costs more than it saves.  Measured on the 43
+        // matrices the reference ships (10 k - 80 k rows): the row kernel alone is 1.3 - 1.4x faster than the mixed
+        // plan there, while the two synthetic brick workloads (12 000 and 16 384 panels) stay on bricks.
+        uint64_t bricks = 0;
+        for (uint64_t q = 0; q < P; ++q) bricks += p.row_path[q] == 1;
+        if (bricks < p.opts.min_brick_panels) std::fill(p.row_path.begin(), p.row_path.end(), (uint8_t)0);
     }
 }
 

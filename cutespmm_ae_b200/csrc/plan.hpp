@@ -34,6 +34,7 @@ struct Tile {
     uint32_t row_begin, row_end, pair_begin, pair_end;
 };
 
+constexpr uint32_t kMinBrickPanels = 4440;  // path auto: fewer dense panels than two per warp of a full brick grid go to the row kernel
 constexpr uint32_t kPanelTooLarge = 0xffffffffu;  // column count of a panel the device builder did not analyse
 
 // A chunk of a long row: nonzeros [j0, j1) of `row`; its partial result is row `slot` of the scratch.

@@ -278,6 +278,84 @@ __global__ void __launch_bounds__(128) spmm_fixup_kernel(const uint4 *__restrict
     }
 }
 
+// ---- narrow products (N <= 64) -----------------------------------------------------------------------------------
+// With 32 or 64 columns a row of B is 128 or 256 bytes: a whole warp per nonzero would leave most lanes idle or move
+// four bytes per lane.  Here the warp still owns a row of A, but G of its nonzeros are in flight per load instruction:
+// the lanes form G groups of 32/G, a group holds one nonzero, a lane one float4 of that nonzero's row of B.  Each
+// group accumulates its own partial sum; the groups are added with shuffles when the row ends (the order of the sum
+// differs from the row kernel's: group g adds nonzeros g, g+G, ... first).  Work items are the same tiles and chunks;
+// rows are taken in turn by the warps of a block, pairs and row pointers come straight from global memory (rows are
+// short here, the tile staging of the wide kernel does not pay).
+template <int G>
+__global__ void __launch_bounds__(kWarps * 32, 6) spmm_rows_narrow_kernel(RowsArgs a)
+{
+    constexpr int L = 32 / G;   // lanes per nonzero
+    constexpr int U = 4;        // loads in flight per lane
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int grp = lane / L, sub = lane % L;
+    const uint32_t col = sub * 4;
+    const bool has_col = col < a.N;
+    const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
+    const float *bl = a.B + col;
+    const uint32_t ldb32 = (uint32_t)a.ldb;
+    auto run = [&](uint32_t j0, uint32_t j1, float *out) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t j = j0 + grp; j < j1; j += G * U) {
+            float v[U];
+            float4 b[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t jj = j + u * G;
+                v[u] = 0.f;
+                b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (jj < j1) {
+                    const uint2 pr = __ldg(pairs + jj);  // the lanes of a group read one address
+                    v[u] = __uint_as_float(pr.y);
+                    if (has_col) b[u] = __ldg(reinterpret_cast<const float4 *>(bl + (uint64_t)pr.x * ldb32));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (j + u * G < j1) fma_vec(acc, v[u], b[u]);
+        }
+#pragma unroll
+        for (int off = L; off < 32; off <<= 1) {
+            acc.x += __shfl_xor_sync(kFull, acc.x, off);
+            acc.y += __shfl_xor_sync(kFull, acc.y, off);
+            acc.z += __shfl_xor_sync(kFull, acc.z, off);
+            acc.w += __shfl_xor_sync(kFull, acc.w, off);
+        }
+        if (grp == 0 && has_col) *reinterpret_cast<float4 *>(out + col) = acc;
+    };
+    // chunks of long rows first
+    {
+        const uint32_t gw = blockIdx.x * kWarps + warp, nw = gridDim.x * kWarps;
+        for (uint32_t c = gw; c < a.num_chunks; c += nw) {
+            const uint4 ck = __ldg(reinterpret_cast<const uint4 *>(a.chunks) + c);  // row, j0, j1, slot
+            run(ck.y, ck.z, a.scratch + (uint64_t)ck.w * a.ld_scratch);
+        }
+    }
+    const uint4 *tiles = reinterpret_cast<const uint4 *>(a.tiles);
+    for (uint32_t t = blockIdx.x; t < a.num_tiles; t += gridDim.x) {
+        const uint4 d = __ldg(tiles + t);
+        for (uint32_t r = d.x + warp; r < d.y; r += kWarps) {
+            const uint32_t j0 = __ldg(a.row_ptr + r), j1 = __ldg(a.row_ptr + r + 1);
+            const uint32_t r_out = a.row_map ? __ldg(a.row_map + r) : r;
+            run(j0, j1, a.C + (uint64_t)r_out * a.ldc);
+        }
+    }
+}
+
+template <int G> cudaError_t launch_rows_narrow_t(const RowsArgs &a, int sm_count, cudaStream_t s)
+{
+    const uint64_t want = (uint64_t)sm_count * 6;
+    uint64_t work = a.num_tiles > (a.num_chunks + kWarps - 1) / kWarps ? a.num_tiles : (a.num_chunks + kWarps - 1) / kWarps;
+    uint32_t gx = (uint32_t)(work < want ? work : want);
+    if (gx == 0) gx = 1;
+    spmm_rows_narrow_kernel<G><<<gx, kWarps * 32, 0, s>>>(a);
+    return cudaGetLastError();
+}
+
 template <int VEC, int CH, bool FULL, bool DEEP>
 cudaError_t launch_rows_t(const RowsArgs &a, uint32_t slabs, int sm_count, cudaStream_t s)
 {
@@ -310,6 +388,11 @@ cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s)
     const bool v4 = !((pb | pc | ps) & 15) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 3);
     const bool v2 = !((pb | pc | ps) & 7) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 1);
     const uint32_t N = a.N;
+    if (v4 && N <= 64) {  // narrow products: several nonzeros of a row in flight per load instruction
+        if (N <= 16) return launch_rows_narrow_t<8>(a, sm_count, s);
+        if (N <= 32) return launch_rows_narrow_t<4>(a, sm_count, s);
+        return launch_rows_narrow_t<2>(a, sm_count, s);
+    }
     // deep: at most one resident wave of tiles, or long rows (measured on shards of R-MAT 2^24: 300 nonzeros per row
     // 2.19 vs 2.38 ms, 21 per row 1.88 vs 1.93 ms in favour of deep; 15 per row (R-MAT 2^20) 0.645 vs 0.611 ms and
     // 3.4 per row 1.50 vs 1.48 ms in favour of shallow)

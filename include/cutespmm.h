@@ -86,7 +86,9 @@ typedef struct {
     float brick_density;  /* AUTO: panels whose 16x8 bricks are at least this full go to the brick kernel (0 = default) */
     uint32_t flags;       /* CUTESPMM_FLAG_* */
     uint32_t reorder;     /* cutespmm_reorder_t */
-    uint32_t reserved;
+    uint32_t min_brick_panels; /* AUTO: with fewer dense panels than this, every panel goes to the row kernel (0 = default
+                                  4440, two panels per warp of a full brick-kernel grid: below that most of its per-warp
+                                  pipelines idle and a second launch for the other rows costs more than it saves) */
 } cutespmm_options_t;
 
 typedef struct {

@@ -38,11 +38,31 @@ def sorted_pattern_from_mtx(g, path):
     return g.CsrMatrix(M, K, torch.from_numpy(row_ptr), torch.from_numpy(c), torch.ones(c.size, dtype=torch.float32), Path(path).stem)
 
 
+def run_one(oracle, g, A, N, b_seed, b_dist, iters):
+    """One (matrix, N): the JSON-able result of the reference's GPU path, checked against the CPU oracle."""
+    if N not in (16, 32, 64, 128, 256, 512) or A.M % 16 or A.K % 16:
+        return {"unavailable": "shape outside what the reference's launcher takes"}
+    if (A.M // 16) * (A.K // 16) > (1 << 31):
+        return {"unavailable": "the reference's preprocessing allocates (M/16)*(K/16) offsets (data.cu:91): too large for this matrix"}
+    B = g.dense_operand(A.K, N, b_seed, b_dist).numpy()
+    C, prep, cold, warm, flushed = oracle.ref_gpu_spmm(A.M, A.K, A.row_ptr, A.cols, A.vals, B, iters=iters)
+    err = oracle.rel_fro(oracle.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K), C)
+    if not err <= 1e-3:
+        return {"unavailable": f"its result differs from the CPU oracle (relative Frobenius error {err:.3e}): not timed"}
+    gf = lambda ms: round(2.0 * A.nnz * N / (ms * 1e-3) / 1e9, 1)  # noqa: E731
+    return {"kernel": "SpMM<NUM_WARPS,ILP_LEVEL> (kernel.cu:119-288), TM=16 TN=4 Machine=0, built for sm_100a", "rel_fro": err,
+            "ms_l2_flushed": round(flushed, 5), "gflops_l2_flushed": gf(flushed), "ms_l2_not_flushed": round(warm, 5),
+            "gflops_l2_not_flushed": gf(warm), "ms_first_launch": round(cold, 5), "preprocessing_ms": round(prep, 1),
+            "launches": 2 * iters + 1,
+            "note": "each launch alone between CUDA events; C zeroed before every launch (not timed), as run.cu:43,49 does; "
+                    "ms_l2_flushed follows this benchmark's own protocol (256 MiB write before each launch)"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="", choices=["", "uniform4096", "stencil512", "elasticity40"])
-    ap.add_argument("--mtx", default="", help="a MatrixMarket file instead of a named workload")
-    ap.add_argument("--N", type=int, required=True)
+    ap.add_argument("--mtx", default="", help="MatrixMarket file(s) instead of a named workload, comma-separated: one JSON line per (file, N)")
+    ap.add_argument("--N", required=True, help="feature size(s), comma-separated")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     import oracle
@@ -51,31 +71,21 @@ def main():
     g = importlib.util.module_from_spec(spec)
     sys.modules[spec.name] = g
     spec.loader.exec_module(g)
+    Ns = [int(x) for x in a.N.split(",")]
     if a.mtx:
-        A = sorted_pattern_from_mtx(g, a.mtx)
-        w = {"b_seed": 4242, "b_dist": "normal"}
-    else:
-        w = g.WORKLOADS[a.workload]
-        A = w["make"]()
-    if a.N not in (16, 32, 64, 128, 256, 512) or A.M % 16 or A.K % 16:
-        print(json.dumps({"unavailable": "shape outside what the reference's launcher takes"}))
+        for f in a.mtx.split(","):
+            A = sorted_pattern_from_mtx(g, f)
+            for N in Ns:
+                out = run_one(oracle, g, A, N, 4242, "normal", a.iters)
+                out.update(matrix=Path(f).stem, N=N)
+                print(json.dumps(out), flush=True)
         return
-    if (A.M // 16) * (A.K // 16) > (1 << 31):
-        print(json.dumps({"unavailable": "the reference's preprocessing allocates (M/16)*(K/16) offsets (data.cu:91): too large for this matrix"}))
-        return
-    B = g.dense_operand(A.K, a.N, w["b_seed"], w["b_dist"]).numpy()
-    C, prep, cold, warm, flushed = oracle.ref_gpu_spmm(A.M, A.K, A.row_ptr, A.cols, A.vals, B, iters=a.iters)
-    err = oracle.rel_fro(oracle.spmm_csr(A.row_ptr, A.cols, A.vals, B, A.M, A.K), C)
-    if not err <= 1e-3:
-        print(json.dumps({"unavailable": f"its result differs from the CPU oracle (relative Frobenius error {err:.3e}): not timed"}))
-        return
-    gf = lambda ms: round(2.0 * A.nnz * a.N / (ms * 1e-3) / 1e9, 1)  # noqa: E731
-    print(json.dumps({"kernel": "SpMM<NUM_WARPS,ILP_LEVEL> (kernel.cu:119-288), TM=16 TN=4 Machine=0, built for sm_100a", "rel_fro": err,
-                      "ms_l2_flushed": round(flushed, 5), "gflops_l2_flushed": gf(flushed), "ms_l2_not_flushed": round(warm, 5),
-                      "gflops_l2_not_flushed": gf(warm), "ms_first_launch": round(cold, 5), "preprocessing_ms": round(prep, 1),
-                      "launches": 2 * a.iters + 1,
-                      "note": "each launch alone between CUDA events; C zeroed before every launch (not timed), as run.cu:43,49 does; "
-                              "ms_l2_flushed follows this benchmark's own protocol (256 MiB write before each launch)"}))
+    w = g.WORKLOADS[a.workload]
+    A = w["make"]()
+    for N in Ns:
+        out = run_one(oracle, g, A, N, w["b_seed"], w["b_dist"], a.iters)
+        out.update(matrix=a.workload, N=N)
+        print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":

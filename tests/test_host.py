@@ -240,3 +240,15 @@ def test_similar_rows_grouping_shrinks_the_panels_column_sets():
         grouped = cs.Plan.from_csr(A, reorder="similar", host_only=True).info()
         assert grouped["num_bricks"] <= gain * plain["num_bricks"], (A.name, plain["num_bricks"], grouped["num_bricks"])
         assert grouped["nnz"] == plain["nnz"]
+
+
+def test_auto_keeps_small_matrices_on_the_row_kernel():
+    """The default of path auto: dense panels go to the tensor-core kernel only when there are enough of them to fill
+    its grid (4440); a small stencil stays on the row kernel, the 512 x 512 one does not."""
+    small, big = g.stencil9(96), g.stencil9(512)
+    assert cs.Plan.from_csr(small, host_only=True, min_brick_panels=4440).info()["brick_panels"] == 0
+    assert cs.Plan.from_csr(small, host_only=True, min_brick_panels=1).info()["brick_panels"] == small.M // 16
+    cs.default_min_brick_panels = 0  # the library's own default
+    assert cs.Plan.from_csr(small, host_only=True).info()["brick_panels"] == 0
+    assert cs.Plan.from_csr(big, host_only=True).info()["brick_panels"] == big.M // 16
+    assert cs.Plan.from_csr(small, host_only=True, path=cs.PATH_BRICK).info()["brick_panels"] == small.M // 16  # an explicit path is obeyed
