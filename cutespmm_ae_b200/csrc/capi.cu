@@ -110,6 +110,36 @@ static int usable_device(int *dev, int *sm_count)
     return CUTESPMM_OK;
 }
 
+// What the row kernel needs to finish long rows inside the launch: per scratch slot the long row it belongs to (for
+// both work lists), one arrival counter per long row and column slab (zero between launches), and the scratch matrix.
+static cudaError_t reserve_long_row_state(cutespmm_plan *p, uint64_t &by, const char **what)
+{
+    const HostPlan &h = p->host;
+    auto owners = [](const std::vector<Chunk> &chunks, const std::vector<LongRow> &rows) {
+        std::vector<uint32_t> v(chunks.size(), 0u);
+        for (size_t i = 0; i < rows.size(); ++i)
+            for (uint32_t k = rows[i].slot0; k < rows[i].slot1; ++k) v[k] = (uint32_t)i;
+        return v;
+    };
+    cudaError_t e;
+    *what = "chunk owners";
+    if ((e = upload(owners(h.chunks, h.long_rows), &p->d_chunk_owner, by)) != cudaSuccess) return e;
+    if ((e = upload(owners(h.chunks_all, h.long_rows_all), &p->d_chunk_owner_all, by)) != cudaSuccess) return e;
+    const uint64_t counters = (uint64_t)std::max(h.long_rows.size(), h.long_rows_all.size()) * (kScratchCols / 32) * sizeof(uint32_t);
+    if (counters) {
+        *what = "arrival counters";
+        if ((e = cudaMalloc(&p->d_arrivals, counters)) != cudaSuccess || (e = cudaMemset(p->d_arrivals, 0, counters)) != cudaSuccess) return e;
+        by += counters;
+    }
+    const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
+    if (scratch) {
+        *what = "scratch";
+        if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) return e;
+        by += scratch;
+    }
+    return cudaSuccess;
+}
+
 // Uploads every array of a complete host-side plan to the current device and reserves scratch and status word.
 static int upload_plan(cutespmm_plan *p, int dev, int sm_count)
 {
@@ -157,11 +187,8 @@ static int upload_plan(cutespmm_plan *p, int dev, int sm_count)
         UP(h.slab_ids, p->d_sids)
     }
 #undef UP
-    const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
-    if (scratch) {
-        if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) return fail_cuda(e, "scratch");
-        by += scratch;
-    }
+    const char *what = "";
+    if ((e = reserve_long_row_state(p, by, &what)) != cudaSuccess) return fail_cuda(e, what);
     if ((e = cudaMalloc(&p->d_status, 256)) != cudaSuccess || (e = cudaMemset(p->d_status, 0, 256)) != cudaSuccess)
         return fail_cuda(e, "status word");
     by += 256;
@@ -213,7 +240,7 @@ int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, 
     if (prop.major < 10)
         return fail(CUTESPMM_EUNSUPPORTED, "this library is built for sm_100a (B200) only; found compute capability " +
                                                std::to_string(prop.major) + "." + std::to_string(prop.minor));
-    // the row pointers come to the host (4 bytes per row): tiles, chunks and the fix-up list are cut from them alone
+    // the row pointers come to the host (4 bytes per row): tiles, chunks and the list of long rows are cut from them alone
     std::vector<uint32_t> rp;
     try {
         rp.resize(M + 1);
@@ -333,11 +360,8 @@ int cutespmm_plan_create_device(cutespmm_plan_t **plan, uint64_t M, uint64_t K, 
         (e = upload(h.long_rows, &p->d_long_rows, by)) != cudaSuccess || (e = upload(h.tiles_all, &p->d_tiles_all, by)) != cudaSuccess ||
         (e = upload(h.chunks_all, &p->d_chunks_all, by)) != cudaSuccess || (e = upload(h.long_rows_all, &p->d_long_rows_all, by)) != cudaSuccess)
         return bail(e, "uploading the work lists");
-    const uint64_t scratch = (uint64_t)std::max(h.chunks.size(), h.chunks_all.size()) * kScratchCols * sizeof(float);
-    if (scratch) {
-        if ((e = cudaMalloc(&p->d_scratch, scratch)) != cudaSuccess) return bail(e, "scratch");
-        by += scratch;
-    }
+    const char *what = "";
+    if ((e = reserve_long_row_state(p, by, &what)) != cudaSuccess) return bail(e, what);
     uint32_t bad = 0;
     if ((e = cudaMemcpyAsync(&bad, p->d_status + 1, sizeof(bad), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
         (e = cudaStreamSynchronize(s)) != cudaSuccess)
@@ -463,7 +487,8 @@ static RowsArgs rows_args(const cutespmm_plan *p, bool all_rows, const float *B,
     a.long_rows = all_rows ? p->d_long_rows_all : p->d_long_rows;
     a.num_tiles = (uint32_t)(all_rows ? h.tiles_all.size() : h.tiles.size());
     a.num_chunks = (uint32_t)(all_rows ? h.chunks_all.size() : h.chunks.size());
-    a.num_long_rows = (uint32_t)(all_rows ? h.long_rows_all.size() : h.long_rows.size());
+    a.chunk_owner = static_cast<const uint32_t *>(all_rows ? p->d_chunk_owner_all : p->d_chunk_owner);
+    a.arrivals = p->d_arrivals;
     a.split_nnz = h.opts.split_nnz;
     a.avg_row_nnz = (uint32_t)(h.nnz / std::max<uint64_t>(h.M, 1));
     a.B = B; a.C = C; a.scratch = p->d_scratch;
@@ -471,16 +496,13 @@ static RowsArgs rows_args(const cutespmm_plan *p, bool all_rows, const float *B,
     a.N = N;
     a.status = p->d_status;
     a.row_map = static_cast<const uint32_t *>(p->d_row_map);
-    if (rg) {  // a sub-range of the lists: 16-byte tiles, chunks and fix-up entries
+    if (rg) {  // a sub-range of the lists: 16-byte tiles and chunks (a chunk names its scratch slot and, through it, its long row)
         const uint32_t t0 = all_rows ? rg->ta0 : rg->t0, t1 = all_rows ? rg->ta1 : rg->t1;
         const uint32_t c0 = all_rows ? rg->ca0 : rg->c0, c1 = all_rows ? rg->ca1 : rg->c1;
-        const uint32_t l0 = all_rows ? rg->la0 : rg->l0, l1 = all_rows ? rg->la1 : rg->l1;
         a.tiles = static_cast<const char *>(a.tiles) + (size_t)t0 * sizeof(Tile);
         a.chunks = static_cast<const char *>(a.chunks) + (size_t)c0 * sizeof(Chunk);
-        a.long_rows = static_cast<const char *>(a.long_rows) + (size_t)l0 * sizeof(LongRow);
         a.num_tiles = t1 - t0;
         a.num_chunks = c1 - c0;
-        a.num_long_rows = l1 - l0;
     }
     return a;
 }
@@ -551,7 +573,6 @@ int cutespmm_spmm_launch_count(const cutespmm_plan_t *p, uint32_t N)
         if (brick) total += 1;
         if (slab) total += 1;
         if (all_rows ? (!h.tiles_all.empty() || !h.chunks_all.empty()) : (!h.tiles.empty() || !h.chunks.empty())) total += 1;
-        if (!(all_rows ? h.long_rows_all : h.long_rows).empty()) total += 1;
     }
     return total;
 }
@@ -599,7 +620,6 @@ int cutespmm_internal_spmm_range(const cutespmm_plan *p, const float *B, uint64_
         // operands) are executed by the row kernel from its all-rows work list
         RowsArgs ra = rows_args(p, (!brick && p->host.num_bricks) || (!slab && p->host.slab_panels), B + n0, ldb, C + n0, ldc, nw, rg);
         if ((e = launch_rows(ra, p->sm_count, s)) != cudaSuccess) return fail_cuda(e, "row kernel launch");
-        if ((e = launch_fixup(ra, s)) != cudaSuccess) return fail_cuda(e, "fix-up kernel launch");
     }
     return CUTESPMM_OK;
 }

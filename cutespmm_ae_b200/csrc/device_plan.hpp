@@ -23,14 +23,16 @@ template <auto Kernel> cudaError_t allow_dynamic_smem(int bytes)
     return e;
 }
 
-// Arguments of the row-gather kernel and of the fix-up kernel that follows it.
+// Arguments of the row-gather kernel.
 struct RowsArgs {
     const uint32_t *row_ptr;   // M+1 offsets into pairs
     const void *pairs;         // nnz x {col, fp32 bits}
     const void *tiles;         // num_tiles x {row_begin, row_end, pair_begin, pair_end}
     const void *chunks;        // num_chunks x {row, j0, j1, slot}
-    const void *long_rows;     // num_long_rows x {row, slot0, slot1, -}
-    uint32_t num_tiles, num_chunks, num_long_rows, split_nnz;
+    const void *long_rows;     // the whole list of long rows {row of C, slot0, slot1, -}, indexed by chunk_owner
+    const uint32_t *chunk_owner;  // per scratch slot: index of the long row the chunk belongs to
+    uint32_t *arrivals;        // per long row and column slab: chunks finished so far (zero between launches)
+    uint32_t num_tiles, num_chunks, split_nnz;
     uint32_t avg_row_nnz;      // nonzeros per row of the whole matrix (picks the kernel's tuning)
     const float *B;            // K x N window, leading dimension ldb
     float *C;                  // M x N window, leading dimension ldc
@@ -42,7 +44,6 @@ struct RowsArgs {
 };
 
 cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s);
-cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s);
 int rows_kernel_count(const RowsArgs &a);
 
 // Arguments of the SDDMM kernel (sddmm_kernel.cu): out[j] = (scale ? value of nonzero j : 1) * <X[row of j], Y[column of j]>.

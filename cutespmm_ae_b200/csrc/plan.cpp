@@ -25,7 +25,8 @@ void build_brick_part(HostPlan &p, const std::vector<uint32_t> &panel_ncols);  /
 uint64_t layout_brick_slots(HostPlan &p, const std::vector<uint32_t> &panel_ncols, std::vector<uint32_t> &which);
 void build_slab_part(HostPlan &p);                                             // slab_build.cpp
 
-static void fill_default_options(cutespmm_options_t &o, const cutespmm_options_t *in)
+// Returns whether the caller left both scheduling sizes (split_nnz, tile_nnz) to the library.
+static bool fill_default_options(cutespmm_options_t &o, const cutespmm_options_t *in)
 {
     std::memset(&o, 0, sizeof(o));
     if (in) {
@@ -33,11 +34,13 @@ static void fill_default_options(cutespmm_options_t &o, const cutespmm_options_t
         std::memcpy(&o, in, n);
     }
     o.struct_size = sizeof(o);
+    const bool sizes_left_open = o.split_nnz == 0 && o.tile_nnz == 0;
     if (o.split_nnz == 0) o.split_nnz = kDefaultSplitNnz;
     if (o.split_nnz > kMaxSplitNnz) o.split_nnz = kMaxSplitNnz;
     if (o.tile_nnz == 0) o.tile_nnz = kDefaultTileCost;
     if (o.brick_density <= 0.0f) o.brick_density = 0.125f;
     if (o.min_brick_panels == 0) o.min_brick_panels = kMinBrickPanels;
+    return sizes_left_open;
 }
 
 // Distinct columns of every 16-row panel, ascending: the HRPB view (data.cu:116-149 counts them,
@@ -96,8 +99,35 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
                         std::vector<LongRow> &long_rows)
 {
     const uint64_t P = p.num_panels();
-    const uint32_t split = p.opts.split_nnz;
-    const uint64_t target = p.opts.tile_nnz;
+    uint32_t split = p.opts.split_nnz;
+    uint64_t target = p.opts.tile_nnz;
+    bool latency_bound = false;
+    if (p.adaptive_tiling) {
+        // The default sizes (tiles of cost 512, chunks of 256 nonzeros) keep the per-item overhead small when the grid is
+        // many waves long.  A small job is a handful of memory latencies long, and then the longest chain of dependent
+        // gathers of one warp IS the run time: a 256-nonzero chunk is 64 steps of four loads, about 30 us, when the
+        // rest of a 200 000-nonzero matrix is done in 10.  So the work is cut finer the smaller the job: tiles so that
+        // one resident wave of blocks holds them all, rows cut from a shorter length on, and a cut row into about
+        // sqrt(length) pieces of sqrt(length) nonzeros -- the chain is a piece's gathers followed by the sum of the
+        // pieces, and that split makes the two equally long.
+        uint64_t total = 0;
+        for (uint64_t q = 0; q < P; ++q) {
+            if (!all_rows && p.row_path[q]) continue;
+            const uint64_t r0 = q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
+            total += (p.row_ptr[r1] - p.row_ptr[r0]) + (r1 - r0) * kRowCost;
+        }
+        target = std::min<uint64_t>(target, std::max<uint64_t>(kMinAdaptiveTileCost, total / kResidentTiles));
+        if (total / kAdaptiveSplitDivisor < split) {
+            latency_bound = true;
+            split = (uint32_t)std::max<uint64_t>(kMinAdaptiveSplitNnz, total / kAdaptiveSplitDivisor);
+        }
+    }
+    auto piece_of = [&](uint32_t len) {  // nonzeros per chunk of a row of `len` nonzeros that is being cut
+        if (!latency_bound) return split;
+        uint32_t s = 1;
+        while ((uint64_t)s * s < len) ++s;  // ceil(sqrt(len)): a latency-bound job has fewer than 2.1 M nonzeros, 1 500 steps at most
+        return std::min(split, std::max(kMinChunkNnz, s));
+    };
     tiles.clear();
     chunks.clear();
     long_rows.clear();
@@ -120,8 +150,9 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
                 close(r);
                 begin = r + 1;
                 LongRow lr{p.row_map.empty() ? (uint32_t)r : p.row_map[r], (uint32_t)chunks.size(), 0, 0};  // the row of C the sum goes to
-                for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; j += split)
-                    chunks.push_back(Chunk{(uint32_t)r, j, std::min<uint32_t>(j + split, p.row_ptr[r + 1]),
+                const uint32_t piece = piece_of(len);
+                for (uint32_t j = p.row_ptr[r]; j < p.row_ptr[r + 1]; j += piece)
+                    chunks.push_back(Chunk{(uint32_t)r, j, std::min<uint32_t>(j + piece, p.row_ptr[r + 1]),
                                            (uint32_t)chunks.size()});
                 lr.slot1 = (uint32_t)chunks.size();
                 long_rows.push_back(lr);
@@ -321,7 +352,7 @@ int build_rows_plan_from_row_ptr(HostPlan &p, uint64_t M, uint64_t K, std::vecto
         return CUTESPMM_EUNSUPPORTED;
     }
     if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
-    fill_default_options(p.opts, opts);
+    p.adaptive_tiling = fill_default_options(p.opts, opts);
     if (p.opts.reorder) { err = "row reordering is done by the host builder only (cutespmm_plan_create)"; return CUTESPMM_EUNSUPPORTED; }
     int bad = 0;
 #pragma omp parallel for schedule(static) reduction(| : bad)
@@ -365,7 +396,7 @@ int build_host_plan(HostPlan &p, uint64_t M, uint64_t K, const uint64_t *rowPtr,
     if (nnz >= (1ull << 32)) { err = "more than 2^32-1 nonzeros in one plan: shard the rows"; return CUTESPMM_EUNSUPPORTED; }
     if (nnz && (!cols || !vals)) { err = "cols/vals is NULL"; return CUTESPMM_EINVAL; }
     if (opts && opts->path > CUTESPMM_PATH_SLAB) { err = "unknown path"; return CUTESPMM_EINVAL; }
-    fill_default_options(p.opts, opts);
+    p.adaptive_tiling = fill_default_options(p.opts, opts);
     if (p.opts.reorder > CUTESPMM_REORDER_SIMILAR_ROWS) { err = "unknown reorder option"; return CUTESPMM_EINVAL; }
     if (p.opts.path == CUTESPMM_PATH_SLAB && p.opts.reorder) {
         err = "row reordering is available on the row and brick kernels (path auto, rows or brick)";

@@ -9,12 +9,12 @@
 
 #include "plan.hpp"
 
-// A contiguous range of the plan's work items (tiles, chunks and fix-up entries of the row kernel -- of its own list and
+// A contiguous range of the plan's work items (tiles and chunks of the row kernel -- of its own list and
 // of the list over every row -- and panels of the brick kernel): what one launch covers when a product is issued in
 // blocks of rows.
 struct cutespmm_item_range {
-    uint32_t t0 = 0, t1 = 0, c0 = 0, c1 = 0, l0 = 0, l1 = 0;        // row kernel: tiles, chunks, long rows
-    uint32_t ta0 = 0, ta1 = 0, ca0 = 0, ca1 = 0, la0 = 0, la1 = 0;  // the same lists over every row
+    uint32_t t0 = 0, t1 = 0, c0 = 0, c1 = 0;      // row kernel: tiles, chunks
+    uint32_t ta0 = 0, ta1 = 0, ca0 = 0, ca1 = 0;  // the same lists over every row
     uint32_t p0 = 0, p1 = 0;                                        // brick panels (ordinals)
 };
 // One block of rows of the row-block host-buffer call: rows [row0, row1) of C, computed once rows [0, need) of B are
@@ -36,6 +36,8 @@ struct cutespmm_plan {
     void *d_bcols = nullptr, *d_brecs = nullptr, *d_panel_first = nullptr, *d_panel_last = nullptr;
     void *d_scols = nullptr, *d_srecs = nullptr, *d_srec_off = nullptr, *d_sfirst = nullptr, *d_slast = nullptr, *d_sids = nullptr;
     void *d_row_map = nullptr;
+    void *d_chunk_owner = nullptr, *d_chunk_owner_all = nullptr;  // per scratch slot: its long row
+    uint32_t *d_arrivals = nullptr;                               // per long row and column slab: chunks finished
     float *d_scratch = nullptr;
     uint32_t *d_status = nullptr;
     // staging for the host-buffer call
@@ -63,7 +65,7 @@ struct cutespmm_plan {
         if (cur != device) cudaSetDevice(device);
         for (void *p : {d_row_ptr, d_pairs, d_tiles, d_chunks, d_long_rows, d_tiles_all, d_chunks_all, d_long_rows_all,
                         d_bcols, d_brecs, d_panel_first, d_panel_last, d_scols, d_srecs, d_srec_off, d_sfirst,
-                        d_slast, d_sids, d_row_map, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
+                        d_slast, d_sids, d_row_map, d_chunk_owner, d_chunk_owner_all, (void *)d_arrivals, (void *)d_scratch, (void *)d_status, (void *)d_B, (void *)d_C})
             if (p) cudaFree(p);
         for (cudaEvent_t ev : {ev_entry, ev_done})
             if (ev) cudaEventDestroy(ev);

@@ -10,8 +10,8 @@
 // round with shuffles, and the products are accumulated in fp32 registers in storage order.  The
 // eight warps of a block take interleaved rows of one scheduling tile, so rows that share columns
 // (stencils, block structure) meet in L1.  C rows are written once with streaming stores; nothing
-// is read-modify-written and no atomics are used: a long row is cut into chunks whose partial sums
-// go to a scratch matrix and are added, in order, by a second small kernel.
+// is read-modify-written: a long row is cut into chunks whose partial sums go to a scratch matrix and
+// are added, in slot order, by whichever warp finishes the row's last chunk (one counter per long row).
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -65,6 +65,10 @@ __device__ __forceinline__ void fma_vec(float2 &a, float v, const float2 &b)
 }
 __device__ __forceinline__ void fma_vec(float &a, float v, const float &b) { a = fmaf(v, b, a); }
 
+__device__ __forceinline__ void add_vec(float4 &a, const float4 &b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+__device__ __forceinline__ void add_vec(float2 &a, const float2 &b) { a.x += b.x; a.y += b.y; }
+__device__ __forceinline__ void add_vec(float &a, const float &b) { a += b; }
+
 __device__ __forceinline__ void zero_vec(float4 &a) { a = make_float4(0.f, 0.f, 0.f, 0.f); }
 __device__ __forceinline__ void zero_vec(float2 &a) { a = make_float2(0.f, 0.f); }
 __device__ __forceinline__ void zero_vec(float &a) { a = 0.f; }
@@ -75,13 +79,15 @@ __device__ __forceinline__ void store_stream(float *p, const float &v) { __stcs(
 
 // acc[ch] += sum over nonzeros [j0, j1) of val * B[col][lane's columns].  `bl` points at this lane's
 // first column of row 0 of B; ok[ch] says whether the lane's ch-th column group exists (ragged N).
-template <int VEC, int CH, bool FULL>
+template <int VEC, int CH, bool FULL, bool DEEP>
 __device__ __forceinline__ void accumulate(typename Vec<VEC>::T (&acc)[CH], const uint2 *__restrict__ pairs,
                                            uint32_t j0, uint32_t j1, const float *__restrict__ bl, uint64_t ldb,
                                            const bool (&ok)[CH], int lane)
 {
     using V = typename Vec<VEC>::T;
-    constexpr int U = (CH == 1) ? 4 : 2;  // nonzeros in flight per step (8 was measured: no gain, spills)
+    // nonzeros in flight per step.  With float4 lanes in the 40-register tuning 8 was measured: no gain, spills; the
+    // deep tuning and narrow lanes have the registers, and a deeper step shortens the chain of a latency-bound job
+    constexpr int U = DEEP ? 8 / CH : ((CH == 1) ? (VEC == 4 ? 4 : 8) : 2);
     for (uint32_t j = j0; j < j1; j += 32) {
         const uint32_t n = min(32u, j1 - j);
         uint2 pr = make_uint2(0u, 0u);
@@ -150,35 +156,135 @@ __device__ __forceinline__ void row_group(typename Vec<VEC>::T (&acc)[CH], const
         }
 }
 
-template <int VEC, int CH, bool FULL, bool DEEP>
+// The same sum for a group of 32/G lanes that walks a chunk on its own (G > 1): every lane of the group reads the
+// pair itself (one address per group: a broadcast), no shuffles, so the groups of a warp may run different lengths.
+template <int VEC, int CH, bool FULL, int U>
+__device__ __forceinline__ void accumulate_group(typename Vec<VEC>::T (&acc)[CH], const uint2 *__restrict__ pairs, uint32_t j0, uint32_t j1,
+                                                 const float *__restrict__ bl, uint32_t ldb32, const bool (&ok)[CH])
+{
+    using V = typename Vec<VEC>::T;
+    for (uint32_t j = j0; j < j1; j += U) {
+        float v[U];
+        V b[U][CH];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint2 pr = __ldg(pairs + min(j + u, j1 - 1));
+            v[u] = __uint_as_float(pr.y);
+            const float *row = bl + (uint64_t)pr.x * ldb32;
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) {
+                if (FULL || ok[ch]) b[u][ch] = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
+                else zero_vec(b[u][ch]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (j + u < j1) {
+#pragma unroll
+                for (int ch = 0; ch < CH; ++ch) fma_vec(acc[ch], v[u], b[u][ch]);
+            }
+    }
+}
+
+// What the chunk part of the kernel needs.  The pointers bl / scratch / C already point at this lane's first column.
+struct ChunkArgs {
+    const uint2 *pairs;
+    const uint4 *chunks;     // {row, j0, j1, slot}
+    const uint4 *long_rows;  // {row of C, slot0, slot1, -}
+    const uint32_t *chunk_owner;
+    uint32_t *arrivals;
+    const float *bl;
+    float *scratch, *C;
+    uint64_t ldb, ld_scratch, ldc;
+    uint32_t num_chunks, N, col0;
+};
+
+// A chunk's partial sum goes to its slot of the scratch matrix; the warp (or group) that completes a row's last
+// outstanding chunk adds the slots in slot order -- so the sum does not depend on who that was -- and writes the row
+// of C.  Nobody waits for anybody: whoever is not last just moves on.
+template <int VEC, int CH, bool FULL, bool DEEP, int G>
+__device__ __forceinline__ void run_chunks(const ChunkArgs &a)
+{
+    using V = typename Vec<VEC>::T;
+    constexpr int L = 32 / G;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int grp = G == 1 ? 0 : lane / L, sub = G == 1 ? lane : lane % L;
+    bool ok[CH];
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) ok[ch] = FULL || (a.col0 + ch * 32 * VEC < a.N);
+    // chunk (group) c goes to block c mod gridDim.x: spread over the SMs, and the warps of a block that got none
+    // start on the block's tile at once (rows of a tile are claimed as they go, so they take over the others' share)
+    const uint32_t gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * kWarps;
+    for (uint64_t cw = gw; cw * G < a.num_chunks; cw += nw) {
+        const uint64_t c = cw * G + grp;
+        const bool have = c < a.num_chunks;
+        uint4 ck = make_uint4(0u, 0u, 0u, 0u);
+        if (have) ck = __ldg(a.chunks + c);
+        V acc[CH];
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
+        if constexpr (G == 1) accumulate<VEC, CH, FULL, DEEP>(acc, a.pairs, ck.y, ck.z, a.bl, a.ldb, ok, lane);
+        else accumulate_group<VEC, CH, FULL, Tuning<DEEP>::kUnroll>(acc, a.pairs, ck.y, ck.z, a.bl, (uint32_t)a.ldb, ok);
+        if (have) {
+            float *out = a.scratch + (uint64_t)ck.w * a.ld_scratch;
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch)
+                if (FULL || ok[ch]) __stcg(reinterpret_cast<V *>(out + ch * 32 * VEC), acc[ch]);
+        }
+        __threadfence();  // this lane's part of the slot is visible device-wide before the arrival is counted
+        __syncwarp();
+        uint32_t lr_row = 0, slot0 = 0, slot1 = 0;
+        if (have && sub == 0) {
+            const uint32_t owner = __ldg(a.chunk_owner + ck.w);
+            const uint4 lr = __ldg(a.long_rows + owner);
+            uint32_t *cnt = a.arrivals + (uint64_t)owner * gridDim.y + blockIdx.y;
+            if (atomicAdd(cnt, 1u) == lr.z - lr.y - 1) {  // every chunk of this row and column slab has arrived
+                *cnt = 0;                                  // ready for the next launch
+                __threadfence();
+                lr_row = lr.x; slot0 = lr.y; slot1 = lr.z;
+            }
+        }
+        lr_row = __shfl_sync(kFull, lr_row, grp * L);
+        slot0 = __shfl_sync(kFull, slot0, grp * L);
+        slot1 = __shfl_sync(kFull, slot1, grp * L);
+        if (slot1 > slot0) {
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
+            constexpr int R = (VEC * CH >= 8) ? 4 : 8;  // slots in flight
+#pragma unroll R
+            for (uint32_t k = slot0; k < slot1; ++k) {
+#pragma unroll
+                for (int ch = 0; ch < CH; ++ch)
+                    if (FULL || ok[ch]) add_vec(acc[ch], __ldcg(reinterpret_cast<const V *>(a.scratch + (uint64_t)k * a.ld_scratch + ch * 32 * VEC)));
+            }
+            float *crow = a.C + (uint64_t)lr_row * a.ldc;
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch)
+                if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(crow + ch * 32 * VEC), acc[ch]);
+        }
+        if constexpr (G > 1) __syncwarp();
+    }
+}
+
+// G = rows of A (or chunks) a warp works on at the same time.  G = 1: the 32 lanes span 32*VEC*CH columns of B.
+// G = 2, 4, 8 (narrow products, N <= 64, float4 lanes): the warp is G groups of 32/G lanes, a group spans the whole
+// row of B and owns a row of A of its own, so a warp keeps G times as many gathers in flight and no lane idles.
+template <int VEC, int CH, bool FULL, bool DEEP, int G>
 __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_rows_kernel(RowsArgs a)
 {
     using V = typename Vec<VEC>::T;
+    static_assert(G == 1 || (VEC == 4 && CH == 1), "row groups are for float4 lanes and one column group");
+    constexpr int L = 32 / G;  // lanes of a group
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const uint32_t col0 = blockIdx.y * (32 * VEC * CH) + lane * VEC;  // this lane's first column
+    const int grp = G == 1 ? 0 : lane / L, sub = G == 1 ? lane : lane % L;
+    const uint32_t col0 = blockIdx.y * (32 * VEC * CH) + sub * VEC;  // this lane's first column
     bool ok[CH];
 #pragma unroll
     for (int ch = 0; ch < CH; ++ch) ok[ch] = FULL || (col0 + ch * 32 * VEC < a.N);
     const float *bl = a.B + col0;
     const uint32_t ldb32 = (uint32_t)a.ldb;  // < 2^32 (checked by the caller): one 32x32->64 multiply per address
     const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
-
-    // chunks of long rows first: they are the largest single work items
-    {
-        const uint32_t gw = blockIdx.x * kWarps + warp, nw = gridDim.x * kWarps;
-        for (uint32_t c = gw; c < a.num_chunks; c += nw) {
-            const uint4 ck = __ldg(reinterpret_cast<const uint4 *>(a.chunks) + c);  // row, j0, j1, slot
-            V acc[CH];
-#pragma unroll
-            for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
-            accumulate<VEC, CH, FULL>(acc, pairs, ck.y, ck.z, bl, a.ldb, ok, lane);
-            float *out = a.scratch + (uint64_t)ck.w * a.ld_scratch + col0;
-#pragma unroll
-            for (int ch = 0; ch < CH; ++ch)
-                if (FULL || ok[ch]) *reinterpret_cast<V *>(out + ch * 32 * VEC) = acc[ch];
-        }
-    }
 
     // ---- tiles: descriptor, row pointers and pairs arrive in shared memory by TMA, kStages deep ----
     __shared__ TileStage stage[kStages];
@@ -211,6 +317,12 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
     }
     __syncthreads();
 
+    // Chunks of long rows first (the first tiles are on their way meanwhile): they are the largest single work items.
+    if (a.num_chunks)
+        run_chunks<VEC, CH, FULL, DEEP, G>(ChunkArgs{pairs, reinterpret_cast<const uint4 *>(a.chunks), reinterpret_cast<const uint4 *>(a.long_rows),
+                                                     a.chunk_owner, a.arrivals, bl, a.scratch + col0, a.C + col0, a.ldb, a.ld_scratch, a.ldc,
+                                                     a.num_chunks, a.N, col0});
+
     for (uint32_t i = 0;; ++i) {
         const uint64_t t = blockIdx.x + (uint64_t)i * gridDim.x;
         if (t >= a.num_tiles) break;
@@ -223,27 +335,31 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
         const uint32_t rb = d.x & ~3u, jb = d.z & ~1u;
         for (;;) {
             uint32_t r = 0;
-            if (lane == 0) r = atomicAdd(&next_row[s], 1u);
+            if (lane == 0) r = atomicAdd(&next_row[s], (uint32_t)G);
             r = __shfl_sync(kFull, r, 0) + d.x;
             if (r >= d.y) break;
-            const uint32_t j0 = stage[s].row_ptr[r - rb], j1 = stage[s].row_ptr[r - rb + 1];
-            V acc[CH];
+            r += grp;  // the group's own row
+            if (G == 1 || r < d.y) {
+                const uint32_t j0 = stage[s].row_ptr[r - rb], j1 = stage[s].row_ptr[r - rb + 1];
+                V acc[CH];
 #pragma unroll
-            for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
-            constexpr int U = (CH == 1) ? Tuning<DEEP>::kUnroll : Tuning<DEEP>::kUnroll / 2;  // rows of B in flight per warp and step
-            uint32_t j = j0 - jb, jend = j1 - jb;  // positions in the staged pair slice
-            for (; j + U <= jend; j += U) row_group<VEC, CH, FULL, U, false>(acc, stage[s].pairs + j, U, bl, ldb32, ok);
-            // what is left of the row (fewer than U nonzeros) goes as one more group, so that its loads are in flight
-            // together instead of one after the other: positions past the end repeat the row's last pair and are not added
-            if (const uint32_t rem = jend - j) {
-                if (rem > U / 2) row_group<VEC, CH, FULL, U, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
-                else row_group<VEC, CH, FULL, U / 2, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
+                for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
+                constexpr int U = (CH == 1) ? Tuning<DEEP>::kUnroll : Tuning<DEEP>::kUnroll / 2;  // rows of B in flight per group and step
+                uint32_t j = j0 - jb, jend = j1 - jb;  // positions in the staged pair slice
+                for (; j + U <= jend; j += U) row_group<VEC, CH, FULL, U, false>(acc, stage[s].pairs + j, U, bl, ldb32, ok);
+                // what is left of the row (fewer than U nonzeros) goes as one more group, so that its loads are in flight
+                // together instead of one after the other: positions past the end repeat the row's last pair and are not added
+                if (const uint32_t rem = jend - j) {
+                    if (rem > U / 2) row_group<VEC, CH, FULL, U, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
+                    else row_group<VEC, CH, FULL, U / 2, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
+                }
+                const uint32_t r_out = a.row_map ? __ldg(a.row_map + r) : r;  // a reordered plan writes the row to its place in the caller's C
+                float *out = a.C + (uint64_t)r_out * a.ldc + col0;
+#pragma unroll
+                for (int ch = 0; ch < CH; ++ch)
+                    if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(out + ch * 32 * VEC), acc[ch]);
             }
-            const uint32_t r_out = a.row_map ? __ldg(a.row_map + r) : r;  // a reordered plan writes the row to its place in the caller's C
-            float *out = a.C + (uint64_t)r_out * a.ldc + col0;
-#pragma unroll
-            for (int ch = 0; ch < CH; ++ch)
-                if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(out + ch * 32 * VEC), acc[ch]);
+            if constexpr (G > 1) __syncwarp();
         }
         // this warp is finished with stage s; the last warp to say so refills it
         __syncwarp();
@@ -263,115 +379,23 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
     }
 }
 
-// C[row] = scratch[slot0] + scratch[slot0+1] + ... (in slot order: deterministic).
-__global__ void __launch_bounds__(128) spmm_fixup_kernel(const uint4 *__restrict__ long_rows, uint32_t num_long_rows,
-                                                         const float *__restrict__ scratch, uint64_t ld_scratch,
-                                                         float *__restrict__ C, uint64_t ldc, uint32_t N)
-{
-    for (uint32_t i = blockIdx.x; i < num_long_rows; i += gridDim.x) {
-        const uint4 lr = __ldg(long_rows + i);  // row, slot0, slot1
-        for (uint32_t n = threadIdx.x; n < N; n += blockDim.x) {
-            float s = 0.f;
-            for (uint32_t k = lr.y; k < lr.z; ++k) s += scratch[(uint64_t)k * ld_scratch + n];
-            __stcs(C + (uint64_t)lr.x * ldc + n, s);
-        }
-    }
-}
-
-// ---- narrow products (N <= 64) -----------------------------------------------------------------------------------
-// With 32 or 64 columns a row of B is 128 or 256 bytes: a whole warp per nonzero would leave most lanes idle or move
-// four bytes per lane.  Here the warp still owns a row of A, but G of its nonzeros are in flight per load instruction:
-// the lanes form G groups of 32/G, a group holds one nonzero, a lane one float4 of that nonzero's row of B.  Each
-// group accumulates its own partial sum; the groups are added with shuffles when the row ends (the order of the sum
-// differs from the row kernel's: group g adds nonzeros g, g+G, ... first).  Work items are the same tiles and chunks;
-// rows are taken in turn by the warps of a block, pairs and row pointers come straight from global memory (rows are
-// short here, the tile staging of the wide kernel does not pay).
-template <int G>
-__global__ void __launch_bounds__(kWarps * 32, 6) spmm_rows_narrow_kernel(RowsArgs a)
-{
-    constexpr int L = 32 / G;   // lanes per nonzero
-    constexpr int U = 4;        // loads in flight per lane
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int grp = lane / L, sub = lane % L;
-    const uint32_t col = sub * 4;
-    const bool has_col = col < a.N;
-    const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
-    const float *bl = a.B + col;
-    const uint32_t ldb32 = (uint32_t)a.ldb;
-    auto run = [&](uint32_t j0, uint32_t j1, float *out) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t j = j0 + grp; j < j1; j += G * U) {
-            float v[U];
-            float4 b[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint32_t jj = j + u * G;
-                v[u] = 0.f;
-                b[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (jj < j1) {
-                    const uint2 pr = __ldg(pairs + jj);  // the lanes of a group read one address
-                    v[u] = __uint_as_float(pr.y);
-                    if (has_col) b[u] = __ldg(reinterpret_cast<const float4 *>(bl + (uint64_t)pr.x * ldb32));
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-                if (j + u * G < j1) fma_vec(acc, v[u], b[u]);
-        }
-#pragma unroll
-        for (int off = L; off < 32; off <<= 1) {
-            acc.x += __shfl_xor_sync(kFull, acc.x, off);
-            acc.y += __shfl_xor_sync(kFull, acc.y, off);
-            acc.z += __shfl_xor_sync(kFull, acc.z, off);
-            acc.w += __shfl_xor_sync(kFull, acc.w, off);
-        }
-        if (grp == 0 && has_col) *reinterpret_cast<float4 *>(out + col) = acc;
-    };
-    // chunks of long rows first
-    {
-        const uint32_t gw = blockIdx.x * kWarps + warp, nw = gridDim.x * kWarps;
-        for (uint32_t c = gw; c < a.num_chunks; c += nw) {
-            const uint4 ck = __ldg(reinterpret_cast<const uint4 *>(a.chunks) + c);  // row, j0, j1, slot
-            run(ck.y, ck.z, a.scratch + (uint64_t)ck.w * a.ld_scratch);
-        }
-    }
-    const uint4 *tiles = reinterpret_cast<const uint4 *>(a.tiles);
-    for (uint32_t t = blockIdx.x; t < a.num_tiles; t += gridDim.x) {
-        const uint4 d = __ldg(tiles + t);
-        for (uint32_t r = d.x + warp; r < d.y; r += kWarps) {
-            const uint32_t j0 = __ldg(a.row_ptr + r), j1 = __ldg(a.row_ptr + r + 1);
-            const uint32_t r_out = a.row_map ? __ldg(a.row_map + r) : r;
-            run(j0, j1, a.C + (uint64_t)r_out * a.ldc);
-        }
-    }
-}
-
-template <int G> cudaError_t launch_rows_narrow_t(const RowsArgs &a, int sm_count, cudaStream_t s)
-{
-    const uint64_t want = (uint64_t)sm_count * 6;
-    uint64_t work = a.num_tiles > (a.num_chunks + kWarps - 1) / kWarps ? a.num_tiles : (a.num_chunks + kWarps - 1) / kWarps;
-    uint32_t gx = (uint32_t)(work < want ? work : want);
-    if (gx == 0) gx = 1;
-    spmm_rows_narrow_kernel<G><<<gx, kWarps * 32, 0, s>>>(a);
-    return cudaGetLastError();
-}
-
-template <int VEC, int CH, bool FULL, bool DEEP>
+template <int VEC, int CH, bool FULL, bool DEEP, int G = 1>
 cudaError_t launch_rows_t(const RowsArgs &a, uint32_t slabs, int sm_count, cudaStream_t s)
 {
     static int blocks_per_sm = 0;  // same for every device of one model; queried once
     if (blocks_per_sm == 0) {
         int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, spmm_rows_kernel<VEC, CH, FULL, DEEP>, kWarps * 32, 0);
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, spmm_rows_kernel<VEC, CH, FULL, DEEP, G>, kWarps * 32, 0);
         if (e != cudaSuccess) return e;
         blocks_per_sm = n > 0 ? n : 1;
     }
     const uint64_t want = (uint64_t)sm_count * blocks_per_sm;
-    uint64_t work = a.num_tiles > (a.num_chunks + kWarps - 1) / kWarps ? a.num_tiles : (a.num_chunks + kWarps - 1) / kWarps;
+    const uint64_t chunk_blocks = ((uint64_t)a.num_chunks + kWarps * G - 1) / (kWarps * G);
+    uint64_t work = a.num_tiles > chunk_blocks ? a.num_tiles : chunk_blocks;
     uint32_t gx = (uint32_t)(work < want ? work : want);
     if (slabs > 1) gx = (gx + slabs - 1) / slabs;  // keep the whole grid about one resident wave
     if (gx == 0) gx = 1;
-    spmm_rows_kernel<VEC, CH, FULL, DEEP><<<dim3(gx, slabs), kWarps * 32, 0, s>>>(a);
+    spmm_rows_kernel<VEC, CH, FULL, DEEP, G><<<dim3(gx, slabs), kWarps * 32, 0, s>>>(a);
     return cudaGetLastError();
 }
 
@@ -388,11 +412,6 @@ cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s)
     const bool v4 = !((pb | pc | ps) & 15) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 3);
     const bool v2 = !((pb | pc | ps) & 7) && !((a.ldb | a.ldc | a.ld_scratch | a.N) & 1);
     const uint32_t N = a.N;
-    if (v4 && N <= 64) {  // narrow products: several nonzeros of a row in flight per load instruction
-        if (N <= 16) return launch_rows_narrow_t<8>(a, sm_count, s);
-        if (N <= 32) return launch_rows_narrow_t<4>(a, sm_count, s);
-        return launch_rows_narrow_t<2>(a, sm_count, s);
-    }
     // deep: at most one resident wave of tiles, or long rows (measured on shards of R-MAT 2^24: 300 nonzeros per row
     // 2.19 vs 2.38 ms, 21 per row 1.88 vs 1.93 ms in favour of deep; 15 per row (R-MAT 2^20) 0.645 vs 0.611 ms and
     // 3.4 per row 1.50 vs 1.48 ms in favour of shallow)
@@ -406,7 +425,20 @@ cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s)
         return (N % w == 0) ? launch_rows_t<VEC, CH, true, false>(a, slabs, sm_count, s)       \
                             : launch_rows_t<VEC, CH, false, false>(a, slabs, sm_count, s);     \
     } while (0)
-    if (v4 && N > 64) {
+    if (v4 && N <= 64) {  // narrow products: G rows of A per warp, a group of 32/G float4 lanes spans the row of B
+#define CUTESPMM_GROUPS(G)                                                                              \
+    do {                                                                                                \
+        if (deep) return (N == 128 / G) ? launch_rows_t<4, 1, true, true, G>(a, 1, sm_count, s)         \
+                                        : launch_rows_t<4, 1, false, true, G>(a, 1, sm_count, s);       \
+        return (N == 128 / G) ? launch_rows_t<4, 1, true, false, G>(a, 1, sm_count, s)                  \
+                              : launch_rows_t<4, 1, false, false, G>(a, 1, sm_count, s);                \
+    } while (0)
+        if (N <= 16) CUTESPMM_GROUPS(8);
+        if (N <= 32) CUTESPMM_GROUPS(4);
+        CUTESPMM_GROUPS(2);
+#undef CUTESPMM_GROUPS
+    }
+    if (v4) {
         if (N >= 256) CUTESPMM_GO(4, 2);
         CUTESPMM_GO(4, 1);
     }
@@ -417,15 +449,6 @@ cudaError_t launch_rows(const RowsArgs &a, int sm_count, cudaStream_t s)
     if (N >= 64) CUTESPMM_GO(1, 2);
     CUTESPMM_GO(1, 1);
 #undef CUTESPMM_GO
-}
-
-cudaError_t launch_fixup(const RowsArgs &a, cudaStream_t s)
-{
-    if (a.num_long_rows == 0) return cudaSuccess;
-    const uint32_t g = a.num_long_rows < 4096 ? a.num_long_rows : 4096;
-    spmm_fixup_kernel<<<g, 128, 0, s>>>(reinterpret_cast<const uint4 *>(a.long_rows), a.num_long_rows, a.scratch,
-                                        a.ld_scratch, a.C, a.ldc, a.N);
-    return cudaGetLastError();
 }
 
 }  // namespace cutespmm

@@ -285,14 +285,10 @@ bool cut_row_blocks(cutespmm_plan *p, uint32_t N)
         it.t1 = first_at(h.tiles, b.row1, [](const Tile &t) { return t.row_begin; });
         it.c0 = first_at(h.chunks, b.row0, [](const Chunk &c) { return c.row; });
         it.c1 = first_at(h.chunks, b.row1, [](const Chunk &c) { return c.row; });
-        it.l0 = first_at(h.long_rows, b.row0, [](const LongRow &l) { return l.row; });
-        it.l1 = first_at(h.long_rows, b.row1, [](const LongRow &l) { return l.row; });
         it.ta0 = first_at(h.tiles_all, b.row0, [](const Tile &t) { return t.row_begin; });
         it.ta1 = first_at(h.tiles_all, b.row1, [](const Tile &t) { return t.row_begin; });
         it.ca0 = first_at(h.chunks_all, b.row0, [](const Chunk &c) { return c.row; });
         it.ca1 = first_at(h.chunks_all, b.row1, [](const Chunk &c) { return c.row; });
-        it.la0 = first_at(h.long_rows_all, b.row0, [](const LongRow &l) { return l.row; });
-        it.la1 = first_at(h.long_rows_all, b.row1, [](const LongRow &l) { return l.row; });
         it.p0 = first_at(h.brick_panel_ids, b.row0 / kPanelRows, [](uint32_t q) { return q; });
         it.p1 = first_at(h.brick_panel_ids, (b.row1 + kPanelRows - 1) / kPanelRows, [](uint32_t q) { return q; });
         for (uint64_t q = b.row0 / kPanelRows; q < (b.row1 + kPanelRows - 1) / kPanelRows; ++q)

@@ -49,7 +49,7 @@ def test_named_workloads_match_oracle(oracle_mod, workload, Ns, path):
         assert err <= PATH_TOL[path], (workload, N, err)
 
 
-@pytest.mark.parametrize("N", [1, 3, 8, 33, 48, 64, 100, 128, 130, 200, 256, 384, 512, 516, 640, 1024])
+@pytest.mark.parametrize("N", [1, 3, 4, 8, 12, 16, 20, 32, 33, 36, 48, 60, 64, 100, 128, 130, 200, 256, 384, 512, 516, 640, 1024])
 def test_any_number_of_columns(oracle_mod, N):
     A = g.rmat(9, 8, seed=31, values="uniform")
     B = g.dense_operand(A.K, N, 32).numpy()
@@ -139,6 +139,36 @@ def test_host_buffer_call(oracle_mod):
     assert oracle_mod.rel_fro(gd["C"], C.numpy()) <= REL_FRO_TOL
     C2, _ = p.spmm_host(gd["B"][:, :17].copy())  # narrower N reuses the staging buffers
     assert oracle_mod.rel_fro(gd["C"][:, :17].copy(), C2.numpy()) <= REL_FRO_TOL
+
+
+@pytest.mark.parametrize("N", [16, 32, 64, 128, 512])
+def test_small_job_sizing_cuts_long_rows_finer_and_sums_them_in_the_kernel(oracle_mod, N):
+    """A small matrix (a latency-bound job) with a few rows of thousands of nonzeros among short ones: with the sizes
+    left to the library the long rows are cut into about sqrt(length) pieces, rows from 64 nonzeros on are cut too,
+    and one launch computes everything -- the pieces of a row are added in the kernel by whoever finishes last.
+    Repeated launches must give the same bits (the arrival counters return to zero; the sum order is fixed)."""
+    rng = np.random.default_rng(5)
+    M, K = 3001, 2500
+    lens = rng.integers(0, 9, M)
+    lens[[7, 1500, 2999]] = [2400, 700, 90]   # 49 / 27 / 3 pieces
+    lens[100:140] = 70                        # just over the cut length
+    rp = np.zeros(M + 1, np.int64); np.cumsum(lens, out=rp[1:])
+    cols = np.concatenate([np.sort(rng.choice(K, int(l), replace=False)) for l in lens]).astype(np.int32)
+    vals = rng.standard_normal(cols.size).astype(np.float32)
+    p = cs.Plan(M, K, rp, cols, vals, path=cs.PATH_ROWS)
+    info = p.info()
+    assert info["num_long_rows"] == 43 and info["num_chunks"] > 43 + 49 + 27
+    assert p.launch_count(N) == 1
+    B = g.dense_operand(K, N, 77).numpy()
+    ref = oracle_mod.spmm_csr(rp, cols, vals, B, M, K)
+    C1 = run(p, B)
+    assert oracle_mod.rel_fro(ref, C1) <= REL_FRO_TOL_FP32
+    for _ in range(3):
+        assert np.array_equal(C1, run(p, B))
+    # the same matrix with the sizes given: rows up to 256 nonzeros stay whole
+    q = cs.Plan(M, K, rp, cols, vals, path=cs.PATH_ROWS, split_nnz=256, tile_nnz=512)
+    assert q.info()["num_long_rows"] == 2
+    assert oracle_mod.rel_fro(ref, run(q, B)) <= REL_FRO_TOL_FP32
 
 
 @pytest.mark.parametrize("N,pad,pinned", [(128, 0, True), (256, 0, True), (200, 12, True), (160, 0, False), (40, 8, True)])
