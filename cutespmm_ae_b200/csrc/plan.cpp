@@ -107,16 +107,17 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
         // many waves long.  A small job is a handful of memory latencies long, and then the longest chain of dependent
         // gathers of one warp IS the run time: a 256-nonzero chunk is 64 steps of four loads, about 30 us, when the
         // rest of a 200 000-nonzero matrix is done in 10.  So the work is cut finer the smaller the job: tiles so that
-        // one resident wave of blocks holds them all, rows cut from a shorter length on, and a cut row into about
-        // sqrt(length) pieces of sqrt(length) nonzeros -- the chain is a piece's gathers followed by the sum of the
-        // pieces, and that split makes the two equally long.
+        // one resident wave of blocks holds them all, rows cut from a shorter length on (not below 128: a piece costs
+        // about eight latencies of its own -- descriptor, pairs, arrival count, the sum -- so shorter rows are quicker
+        // whole), and a cut row into pieces of about sqrt(length / 2) nonzeros: the chain is a piece's gathers followed
+        // by the sum of the pieces, the sum runs a few slots per step, and that length makes the two about equal.
         uint64_t total = 0;
         for (uint64_t q = 0; q < P; ++q) {
             if (!all_rows && p.row_path[q]) continue;
             const uint64_t r0 = q * kPanelRows, r1 = std::min<uint64_t>(p.M, r0 + kPanelRows);
             total += (p.row_ptr[r1] - p.row_ptr[r0]) + (r1 - r0) * kRowCost;
         }
-        target = std::min<uint64_t>(target, std::max<uint64_t>(kMinAdaptiveTileCost, total / kResidentTiles));
+        if (total / kResidentTiles <= kMaxAdaptiveTileCost) target = std::max<uint64_t>(kMinAdaptiveTileCost, total / kResidentTiles);
         if (total / kAdaptiveSplitDivisor < split) {
             latency_bound = true;
             split = (uint32_t)std::max<uint64_t>(kMinAdaptiveSplitNnz, total / kAdaptiveSplitDivisor);
@@ -125,7 +126,7 @@ static void build_tiles(const HostPlan &p, bool all_rows, std::vector<Tile> &til
     auto piece_of = [&](uint32_t len) {  // nonzeros per chunk of a row of `len` nonzeros that is being cut
         if (!latency_bound) return split;
         uint32_t s = 1;
-        while ((uint64_t)s * s < len) ++s;  // ceil(sqrt(len)): a latency-bound job has fewer than 2.1 M nonzeros, 1 500 steps at most
+        while ((uint64_t)s * s * 2 < len) ++s;  // ceil(sqrt(len / 2)): a latency-bound job has fewer than 2.1 M nonzeros, about 1 000 steps at most
         return std::min(split, std::max(kMinChunkNnz, s));
     };
     tiles.clear();

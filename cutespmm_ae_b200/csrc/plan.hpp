@@ -16,13 +16,14 @@ constexpr uint32_t kBrickCols = 8;    // one tensor-core brick is 16 rows x 8 ac
 constexpr uint32_t kRowCost = 4;      // scheduling cost of a row besides its nonzeros (pointer loads, C store)
 constexpr uint32_t kDefaultSplitNnz = 256;
 constexpr uint32_t kDefaultTileCost = 512;
-constexpr uint32_t kMaxTileRows = 128;   // rows of one scheduling tile (bounds the staged row-pointer slice)
+constexpr uint32_t kMaxTileRows = 256;   // rows of one scheduling tile (bounds the staged row-pointer slice)
 constexpr uint32_t kMaxTilePairs = 640;  // nonzeros of one scheduling tile (bounds the staged pair slice)
 // Adaptive sizing of the row kernel's work items (when the caller leaves split_nnz and tile_nnz at 0):
 constexpr uint32_t kResidentTiles = 560;          // tiles aimed at for a small job: one wave of the kernel's deep tuning (148 SMs x 4 blocks) less 5 %
 constexpr uint32_t kMinAdaptiveTileCost = 96;     // smallest tile it makes (8 warps x 12 cost units)
+constexpr uint32_t kMaxAdaptiveTileCost = 1024;   // largest: beyond it the job is not small, tiles go back to the default cost
 constexpr uint32_t kAdaptiveSplitDivisor = 8192;  // rows are cut from job cost / this nonzeros on: 256 from 2.1 M cost units
-constexpr uint32_t kMinAdaptiveSplitNnz = 64;     // ... but never from fewer than this
+constexpr uint32_t kMinAdaptiveSplitNnz = 128;    // ... but never from fewer than this
 constexpr uint32_t kMinChunkNnz = 32;             // smallest piece of a cut row
 constexpr uint32_t kMaxSplitNnz = 384;   // a row must fit a tile together with a part-filled one
 constexpr uint32_t kScratchCols = 512;  // widest N one launch handles; wider products run in column windows

@@ -156,33 +156,43 @@ __device__ __forceinline__ void row_group(typename Vec<VEC>::T (&acc)[CH], const
         }
 }
 
-// The same sum for a group of 32/G lanes that walks a chunk on its own (G > 1): every lane of the group reads the
-// pair itself (one address per group: a broadcast), no shuffles, so the groups of a warp may run different lengths.
-template <int VEC, int CH, bool FULL, int U>
+// The same sum for a group of L = 32/G lanes that walks a chunk on its own (G > 1).  The group fetches L pairs with one
+// coalesced load (lane i the i-th), the next L while these are in use, and hands them round with shuffles among its
+// own lanes (`gmask`), so the groups of a warp may run different lengths.
+template <int VEC, int CH, bool FULL, int U, int L>
 __device__ __forceinline__ void accumulate_group(typename Vec<VEC>::T (&acc)[CH], const uint2 *__restrict__ pairs, uint32_t j0, uint32_t j1,
-                                                 const float *__restrict__ bl, uint32_t ldb32, const bool (&ok)[CH])
+                                                 const float *__restrict__ bl, uint32_t ldb32, const bool (&ok)[CH], int sub, unsigned gmask)
 {
     using V = typename Vec<VEC>::T;
-    for (uint32_t j = j0; j < j1; j += U) {
-        float v[U];
-        V b[U][CH];
+    constexpr int UU = U < L ? U : L;  // rows of B in flight per step
+    uint2 nxt = make_uint2(0u, 0u);
+    if (j0 + sub < j1) nxt = __ldg(pairs + j0 + sub);
+    for (uint32_t j = j0; j < j1; j += L) {
+        const uint2 pr = nxt;
+        if (j + L + sub < j1) nxt = __ldg(pairs + j + L + sub);
+        const uint32_t n = min((uint32_t)L, j1 - j);
+        for (uint32_t k = 0; k < n; k += UU) {
+            float v[UU];
+            V b[UU][CH];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const uint2 pr = __ldg(pairs + min(j + u, j1 - 1));
-            v[u] = __uint_as_float(pr.y);
-            const float *row = bl + (uint64_t)pr.x * ldb32;
+            for (int u = 0; u < UU; ++u) {
+                const int src = (int)min(k + u, n - 1);  // positions past the end repeat the last pair and are not added
+                const uint32_t c = __shfl_sync(gmask, pr.x, src, L);
+                v[u] = __uint_as_float(__shfl_sync(gmask, pr.y, src, L));
+                const float *row = bl + (uint64_t)c * ldb32;
 #pragma unroll
-            for (int ch = 0; ch < CH; ++ch) {
-                if (FULL || ok[ch]) b[u][ch] = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
-                else zero_vec(b[u][ch]);
+                for (int ch = 0; ch < CH; ++ch) {
+                    if (FULL || ok[ch]) b[u][ch] = ldg_b(reinterpret_cast<const V *>(row + ch * 32 * VEC));
+                    else zero_vec(b[u][ch]);
+                }
             }
+#pragma unroll
+            for (int u = 0; u < UU; ++u)
+                if (k + u < n) {
+#pragma unroll
+                    for (int ch = 0; ch < CH; ++ch) fma_vec(acc[ch], v[u], b[u][ch]);
+                }
         }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-            if (j + u < j1) {
-#pragma unroll
-                for (int ch = 0; ch < CH; ++ch) fma_vec(acc[ch], v[u], b[u][ch]);
-            }
     }
 }
 
@@ -220,11 +230,19 @@ __device__ __forceinline__ void run_chunks(const ChunkArgs &a)
         const bool have = c < a.num_chunks;
         uint4 ck = make_uint4(0u, 0u, 0u, 0u);
         if (have) ck = __ldg(a.chunks + c);
+        // which long row the chunk belongs to.  The narrow kernels (small N: latency-bound jobs) ask now and use the
+        // answer after the gathers; the wide ones ask when they need it and keep the registers for the gathers.
+        uint32_t owner = 0;
+        uint4 lr = make_uint4(0u, 0u, 0u, 0u);  // row of C, slot0, slot1
+        if (G > 1 && have && sub == 0) {
+            owner = __ldg(a.chunk_owner + ck.w);
+            lr = __ldg(a.long_rows + owner);
+        }
         V acc[CH];
 #pragma unroll
         for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
         if constexpr (G == 1) accumulate<VEC, CH, FULL, DEEP>(acc, a.pairs, ck.y, ck.z, a.bl, a.ldb, ok, lane);
-        else accumulate_group<VEC, CH, FULL, Tuning<DEEP>::kUnroll>(acc, a.pairs, ck.y, ck.z, a.bl, (uint32_t)a.ldb, ok);
+        else accumulate_group<VEC, CH, FULL, Tuning<DEEP>::kUnroll, L>(acc, a.pairs, ck.y, ck.z, a.bl, (uint32_t)a.ldb, ok, sub, (L == 32 ? kFull : ((1u << L) - 1u)) << (grp * L));
         if (have) {
             float *out = a.scratch + (uint64_t)ck.w * a.ld_scratch;
 #pragma unroll
@@ -235,8 +253,10 @@ __device__ __forceinline__ void run_chunks(const ChunkArgs &a)
         __syncwarp();
         uint32_t lr_row = 0, slot0 = 0, slot1 = 0;
         if (have && sub == 0) {
-            const uint32_t owner = __ldg(a.chunk_owner + ck.w);
-            const uint4 lr = __ldg(a.long_rows + owner);
+            if (G == 1) {
+                owner = __ldg(a.chunk_owner + ck.w);
+                lr = __ldg(a.long_rows + owner);
+            }
             uint32_t *cnt = a.arrivals + (uint64_t)owner * gridDim.y + blockIdx.y;
             if (atomicAdd(cnt, 1u) == lr.z - lr.y - 1) {  // every chunk of this row and column slab has arrived
                 *cnt = 0;                                  // ready for the next launch
@@ -244,23 +264,48 @@ __device__ __forceinline__ void run_chunks(const ChunkArgs &a)
                 lr_row = lr.x; slot0 = lr.y; slot1 = lr.z;
             }
         }
-        lr_row = __shfl_sync(kFull, lr_row, grp * L);
-        slot0 = __shfl_sync(kFull, slot0, grp * L);
-        slot1 = __shfl_sync(kFull, slot1, grp * L);
-        if (slot1 > slot0) {
+        constexpr int R = (VEC * CH >= 8) ? 4 : 8;  // slots in flight
+        if constexpr (G == 1) {
+            lr_row = __shfl_sync(kFull, lr_row, 0);
+            slot0 = __shfl_sync(kFull, slot0, 0);
+            slot1 = __shfl_sync(kFull, slot1, 0);
+            if (slot1 > slot0) {
 #pragma unroll
-            for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
-            constexpr int R = (VEC * CH >= 8) ? 4 : 8;  // slots in flight
+                for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
 #pragma unroll R
-            for (uint32_t k = slot0; k < slot1; ++k) {
+                for (uint32_t k = slot0; k < slot1; ++k) {
+#pragma unroll
+                    for (int ch = 0; ch < CH; ++ch)
+                        if (FULL || ok[ch]) add_vec(acc[ch], __ldcg(reinterpret_cast<const V *>(a.scratch + (uint64_t)k * a.ld_scratch + ch * 32 * VEC)));
+                }
+                float *crow = a.C + (uint64_t)lr_row * a.ldc;
 #pragma unroll
                 for (int ch = 0; ch < CH; ++ch)
-                    if (FULL || ok[ch]) add_vec(acc[ch], __ldcg(reinterpret_cast<const V *>(a.scratch + (uint64_t)k * a.ld_scratch + ch * 32 * VEC)));
+                    if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(crow + ch * 32 * VEC), acc[ch]);
             }
-            float *crow = a.C + (uint64_t)lr_row * a.ldc;
+        } else {
+            // The whole warp adds the slots of every row one of its groups completed: group h takes slots h, h+G, ...
+            // in order, then the groups' sums are added pairwise (a fixed tree: the result depends on nothing but G).
+            __syncwarp();
 #pragma unroll
-            for (int ch = 0; ch < CH; ++ch)
-                if (FULL || ok[ch]) store_stream(reinterpret_cast<V *>(crow + ch * 32 * VEC), acc[ch]);
+            for (int g = 0; g < G; ++g) {
+                const uint32_t s0 = __shfl_sync(kFull, slot0, g * L), s1 = __shfl_sync(kFull, slot1, g * L);
+                const uint32_t row = __shfl_sync(kFull, lr_row, g * L);
+                if (s1 > s0) {  // the same for every lane of the warp
+                    zero_vec(acc[0]);
+#pragma unroll R
+                    for (uint32_t k = s0 + grp; k < s1; k += G)
+                        if (FULL || ok[0]) add_vec(acc[0], __ldcg(reinterpret_cast<const V *>(a.scratch + (uint64_t)k * a.ld_scratch)));
+#pragma unroll
+                    for (int off = L; off < 32; off <<= 1) {
+                        acc[0].x += __shfl_xor_sync(kFull, acc[0].x, off);
+                        acc[0].y += __shfl_xor_sync(kFull, acc[0].y, off);
+                        acc[0].z += __shfl_xor_sync(kFull, acc[0].z, off);
+                        acc[0].w += __shfl_xor_sync(kFull, acc[0].w, off);
+                    }
+                    if (grp == 0 && (FULL || ok[0])) store_stream(reinterpret_cast<V *>(a.C + (uint64_t)row * a.ldc), acc[0]);
+                }
+            }
         }
         if constexpr (G > 1) __syncwarp();
     }
@@ -276,7 +321,6 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
     static_assert(G == 1 || (VEC == 4 && CH == 1), "row groups are for float4 lanes and one column group");
     constexpr int L = 32 / G;  // lanes of a group
     const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
     const int grp = G == 1 ? 0 : lane / L, sub = G == 1 ? lane : lane % L;
     const uint32_t col0 = blockIdx.y * (32 * VEC * CH) + sub * VEC;  // this lane's first column
     bool ok[CH];

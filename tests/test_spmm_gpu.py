@@ -144,20 +144,20 @@ def test_host_buffer_call(oracle_mod):
 @pytest.mark.parametrize("N", [16, 32, 64, 128, 512])
 def test_small_job_sizing_cuts_long_rows_finer_and_sums_them_in_the_kernel(oracle_mod, N):
     """A small matrix (a latency-bound job) with a few rows of thousands of nonzeros among short ones: with the sizes
-    left to the library the long rows are cut into about sqrt(length) pieces, rows from 64 nonzeros on are cut too,
-    and one launch computes everything -- the pieces of a row are added in the kernel by whoever finishes last.
+    left to the library the long rows are cut into pieces of about sqrt(length / 2) nonzeros, rows of more than 128
+    nonzeros are cut too, and one launch computes everything -- the pieces of a row are added in the kernel by whoever finishes last.
     Repeated launches must give the same bits (the arrival counters return to zero; the sum order is fixed)."""
     rng = np.random.default_rng(5)
     M, K = 3001, 2500
     lens = rng.integers(0, 9, M)
-    lens[[7, 1500, 2999]] = [2400, 700, 90]   # 49 / 27 / 3 pieces
-    lens[100:140] = 70                        # just over the cut length
+    lens[[7, 1500, 2999]] = [2400, 700, 128]  # 69 / 22 pieces; 128 stays whole
+    lens[100:140] = 140                       # just over the cut length: 5 pieces each
     rp = np.zeros(M + 1, np.int64); np.cumsum(lens, out=rp[1:])
     cols = np.concatenate([np.sort(rng.choice(K, int(l), replace=False)) for l in lens]).astype(np.int32)
     vals = rng.standard_normal(cols.size).astype(np.float32)
     p = cs.Plan(M, K, rp, cols, vals, path=cs.PATH_ROWS)
     info = p.info()
-    assert info["num_long_rows"] == 43 and info["num_chunks"] > 43 + 49 + 27
+    assert info["num_long_rows"] == 42 and info["num_chunks"] == 69 + 22 + 40 * 5
     assert p.launch_count(N) == 1
     B = g.dense_operand(K, N, 77).numpy()
     ref = oracle_mod.spmm_csr(rp, cols, vals, B, M, K)
