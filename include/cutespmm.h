@@ -81,8 +81,11 @@ typedef enum {
 typedef struct {
     uint32_t struct_size; /* sizeof(cutespmm_options_t), for forward compatibility */
     uint32_t path;        /* cutespmm_path_t */
-    uint32_t split_nnz;   /* rows longer than this are cut into chunks of this many nonzeros (0 = default 256, at most 384) */
-    uint32_t tile_nnz;    /* nonzeros a thread block takes per scheduling tile (0 = default) */
+    uint32_t split_nnz;   /* rows longer than this are cut into chunks of this many nonzeros (at most 384) */
+    uint32_t tile_nnz;    /* cost (nonzeros + 4 per row) a thread block takes per scheduling tile */
+                          /* Both 0 (the default): 256 / 512 for large jobs; a job below about 2 M nonzeros gets tiles for
+                             one resident wave, rows cut from max(128, cost/8192) nonzeros on and cut rows in pieces of
+                             sqrt(length/2).  One of them 0: that one takes its large-job default. */
     float brick_density;  /* AUTO: panels whose 16x8 bricks are at least this full go to the brick kernel (0 = default) */
     uint32_t flags;       /* CUTESPMM_FLAG_* */
     uint32_t reorder;     /* cutespmm_reorder_t */

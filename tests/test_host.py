@@ -82,6 +82,35 @@ def test_long_rows_become_chunks():
     assert info["num_chunks"] == int(np.ceil(lens[lens > 8] / 8).sum())
 
 
+def _plan_of_row_lengths(lens, **kw):
+    lens = np.asarray(lens, np.int64)
+    rp = np.zeros(lens.size + 1, np.uint64)
+    np.cumsum(lens, out=rp[1:])
+    cols = np.concatenate([np.arange(l, dtype=np.uint32) for l in lens]) if lens.sum() else np.zeros(0, np.uint32)
+    return cs.Plan(lens.size, int(max(lens.max(), 1)), rp, cols, np.ones(cols.size, np.float32), host_only=True, path=cs.PATH_ROWS, **kw)
+
+
+def test_sizes_left_to_the_library_follow_the_job():
+    """split_nnz = tile_nnz = 0: a small job gets tiles for one resident wave, rows are cut from 128 nonzeros on and
+    a cut row into pieces of ceil(sqrt(length / 2)) (at least 32) nonzeros; a large job keeps 256 / 512; given values
+    are taken as given."""
+    chunks = lambda lens, **kw: (lambda i: (i["num_long_rows"], i["num_chunks"]))(_plan_of_row_lengths(lens, **kw).info())
+    assert chunks([128]) == (0, 0)                       # not longer than the cut length
+    assert chunks([130]) == (1, 5)                       # pieces of 32
+    assert chunks([2400]) == (1, 69)                     # pieces of ceil(sqrt(1200)) = 35
+    assert chunks([2400], split_nnz=256) == (1, 10)      # as given
+    assert chunks([2400], tile_nnz=512) == (1, 10)       # one of the two given: the other takes its large-job default
+    # 4000 rows of 4 nonzeros: cost 32 000 -> tiles of the smallest cost (96 = 12 rows); with the default cost 512, 64 rows each
+    small = [4] * 4000
+    assert _plan_of_row_lengths(small).info()["num_tiles"] == -(-4000 // 12)
+    assert _plan_of_row_lengths(small, tile_nnz=512, split_nnz=256).info()["num_tiles"] == -(-4000 // 64)
+    # a large job (cost above 2.1 M): 256-nonzero chunks, tiles of cost 512
+    big = [8] * 200_000 + [3000]
+    info = _plan_of_row_lengths(big).info()
+    assert (info["num_long_rows"], info["num_chunks"]) == (1, 12)
+    assert info["num_tiles"] == -(-200_000 // 43)        # 43 rows x (8 + 4) reach cost 512
+
+
 def test_bad_input_is_rejected_not_fatal():
     rp = np.array([0, 2, 1], np.uint64)
     with pytest.raises(cs.CuteSpmmError) as e:

@@ -72,6 +72,25 @@ def test_slab_path_on_a_small_power_law_graph_and_rounding_modes(oracle_mod):
     assert e.value.status == -4
 
 
+def test_same_sign_operands_keep_the_stated_bound_on_the_tensor_core_paths(oracle_mod):
+    """All-positive A and B: the truncation of B to TF32 on the brick and slab paths is one-sided (every product comes
+    out low, by up to 2^-10 of its value and 2^-11.5 on average over mantissas), so the errors of a row do not cancel.
+    The stated bound (relative Frobenius 1e-3) must hold there too; rounding B to nearest removes the bias."""
+    A0 = g.WORKLOADS["elasticity40"]["make"]()
+    vals = A0.vals.abs() + 0.25
+    B = (g.dense_operand(A0.K, 128, 52).abs() + 0.25).numpy()
+    ref = oracle_mod.spmm_csr(A0.row_ptr, A0.cols, vals, B, A0.M, A0.K)
+    rp, cols = A0.row_ptr.numpy(), A0.cols.numpy()
+    errs = {}
+    for name, kw in (("brick", dict(path=cs.PATH_BRICK)), ("slab", dict(path=cs.PATH_SLAB)),
+                     ("brick_nearest", dict(path=cs.PATH_BRICK, round_b_nearest=True))):
+        errs[name] = oracle_mod.rel_fro(ref, run(cs.Plan(A0.M, A0.K, rp, cols, vals.numpy(), **kw), B))
+    print("same-sign operands, relative Frobenius error:", errs)
+    assert errs["brick"] <= REL_FRO_TOL and errs["slab"] <= REL_FRO_TOL
+    assert 2e-4 <= errs["brick"] <= 6e-4          # the bias itself: about 2^-11.5 = 3.5e-4
+    assert errs["brick_nearest"] <= 0.5 * errs["brick"]
+
+
 def test_strided_and_misaligned_operands(oracle_mod):
     A = g.uniform_random(300, 200, 5, seed=41)  # M not a multiple of 16
     p = cs.Plan.from_csr(A, path=cs.PATH_ROWS)
