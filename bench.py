@@ -410,7 +410,7 @@ def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak, refer
     balg = bytes_model(A.nnz, A.M, N, A.K)
     ach = balg / (ms * 1e-3) / 1e9
     info = plan.info()
-    out = {"workload": workload, "N": N, "nnz": A.nnz, "path": "brick" if info["num_bricks"] else "rows", "ms_per_step": round(ms, 5),
+    out = {"workload": workload, "N": N, "nnz": A.nnz, "path": plan.kernels(N), "ms_per_step": round(ms, 5),
            "ms_min": round(mn, 5), "gflops": round(2.0 * A.nnz * N / (ms * 1e-3) / 1e9, 1),
            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
                         "traffic": dram_traffic_for(workload, N, path_name, 1)},
@@ -629,7 +629,7 @@ def run_ours(args):
         "metric": "spmm_gflops", "value": round(gflops, 2), "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "K": K, "nnz": nnz, "N": N, "path": args.path, "reorder": args.reorder,
+        "config": {"workload": args.workload, "M": M, "K": K, "nnz": nnz, "N": N, "path": args.path, "kernels": plan.kernels(N), "reorder": args.reorder,
                    "matrix": name, "rows_per_rank": [int(bounds[i + 1] - bounds[i]) for i in range(world)],
                    "l2": "not flushed" if args.no_flush else "flushed between steps (256 MiB write)",
                    "operands_bytes": bytes_alg, "parallelism": f"row panels over {world} GPU(s), B resident in every GPU, C row-sharded"},
@@ -721,7 +721,7 @@ def run_matrices(args):
             gf = 2.0 * A.nnz * N / (ms * 1e-3) / 1e9
             ref = ref_blocks.get((f.stem, N)) or ref_blocks.get(None) or {"unavailable": "not reached"}
             ref_gf = ref.get("gflops_l2_flushed")
-            kind = "brick+rows" if info["num_bricks"] and info["num_tiles"] else ("brick" if info["num_bricks"] else "rows")
+            kind = plan.kernels(N)
             row = {"matrix": f.stem, "rows": A.M, "nnz": A.nnz, "N": N, "path": kind, "gflops": round(gf, 1), "rel_fro": err,
                    "reference_gpu_gflops": ref_gf, "ratio": None if not ref_gf else round(gf / ref_gf, 2),
                    "reference_note": ref.get("unavailable")}

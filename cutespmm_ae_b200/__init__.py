@@ -77,6 +77,7 @@ def _load() -> C.CDLL:
         "cutespmm_spmm": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, vp]),
         "cutespmm_spmm_host": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, vp, f32p]),
         "cutespmm_spmm_launch_count": (C.c_int, [vp, C.c_uint32]),
+        "cutespmm_spmm_kernels": (C.c_int, [vp, C.c_uint32]),
         "cutespmm_spmm_csr_noalloc": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, vp, vp, vp, vp, C.c_uint64, vp,
                                                 C.c_uint64, C.c_uint32, vp]),
         "cutespmm_plan_device_status": (C.c_int, [vp, u32p]),
@@ -213,6 +214,11 @@ class Plan:
 
     def launch_count(self, N: int) -> int:
         return lib.cutespmm_spmm_launch_count(self._h, N)
+
+    def kernels(self, N: int) -> str:
+        """The kernels a product of N columns runs: "rows", "brick", "slab" or a "+"-joined combination."""
+        mask = lib.cutespmm_spmm_kernels(self._h, N)
+        return "+".join(n for b, n in ((2, "brick"), (4, "slab"), (1, "rows")) if mask & b) or "none"
 
     def device_status(self) -> int:
         s = C.c_uint32()

@@ -554,9 +554,37 @@ static SlabArgs slab_args(const cutespmm_plan *p, const float *B, uint64_t ldb, 
 
 // Whether a window of N columns at these addresses runs the brick kernel for the brick panels; if
 // not, the row kernel executes every row from its all-rows work list.
+// Path auto leaves products narrower than 64 columns to the row kernel even where the plan has brick panels: with a
+// group of N/4 lanes per row it is the faster of the two there (stencil512 at N = 32: 0.035 against 0.041 ms,
+// elasticity40: 0.045 against 0.047 ms; at N = 64 the brick kernel wins, 0.048 / 0.053 against 0.057 / 0.070 ms).
+// A plan created with path brick runs its bricks at every width the brick kernel takes.
+static bool brick_wanted(const HostPlan &h, uint32_t N)
+{
+    return h.num_bricks && (N >= 64 || h.opts.path == CUTESPMM_PATH_BRICK);
+}
 static bool use_brick(const cutespmm_plan *p, const float *B, uint64_t ldb, const float *C, uint64_t ldc, uint32_t N)
 {
-    return p->host.num_bricks && brick_supports(N, ldb, ldc, B, C);
+    return brick_wanted(p->host, N) && brick_supports(N, ldb, ldc, B, C);
+}
+
+// Kernels of one column window of width nw (bit 0 row kernel, bit 1 brick kernel, bit 2 slab kernel).  The alignment of
+// the caller's pointers is unknown here: the aligned case is assumed.
+static int window_kernels(const HostPlan &h, uint32_t nw)
+{
+    const bool brick = brick_wanted(h, nw) && nw % 32 == 0;
+    const bool slab = h.slab_panels && nw % 128 == 0;
+    const bool all_rows = (!brick && h.num_bricks) || (!slab && h.slab_panels);
+    int mask = (brick ? 2 : 0) | (slab ? 4 : 0);
+    if (all_rows ? (!h.tiles_all.empty() || !h.chunks_all.empty()) : (!h.tiles.empty() || !h.chunks.empty())) mask |= 1;
+    return mask;
+}
+
+int cutespmm_spmm_kernels(const cutespmm_plan_t *p, uint32_t N)
+{
+    if (!p || N == 0 || p->host.M == 0) return 0;
+    int mask = 0;
+    for (uint32_t n0 = 0; n0 < N; n0 += kScratchCols) mask |= window_kernels(p->host, N - n0 < kScratchCols ? N - n0 : kScratchCols);
+    return mask;
 }
 
 int cutespmm_spmm_launch_count(const cutespmm_plan_t *p, uint32_t N)
@@ -564,15 +592,8 @@ int cutespmm_spmm_launch_count(const cutespmm_plan_t *p, uint32_t N)
     if (!p || N == 0 || p->host.M == 0) return 0;
     int total = 0;
     for (uint32_t n0 = 0; n0 < N; n0 += kScratchCols) {
-        const uint32_t nw = N - n0 < kScratchCols ? N - n0 : kScratchCols;
-        // alignment of the caller's pointers is unknown here: assume the aligned case
-        const HostPlan &h = p->host;
-        const bool brick = h.num_bricks && nw % 32 == 0;
-        const bool slab = h.slab_panels && nw % 128 == 0;
-        const bool all_rows = (!brick && h.num_bricks) || (!slab && h.slab_panels);
-        if (brick) total += 1;
-        if (slab) total += 1;
-        if (all_rows ? (!h.tiles_all.empty() || !h.chunks_all.empty()) : (!h.tiles.empty() || !h.chunks.empty())) total += 1;
+        const int mask = window_kernels(p->host, N - n0 < kScratchCols ? N - n0 : kScratchCols);
+        total += (mask & 1) + ((mask >> 1) & 1) + ((mask >> 2) & 1);
     }
     return total;
 }

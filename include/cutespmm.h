@@ -55,7 +55,10 @@ typedef enum {
  * kernel.cu:28-29).  By default the elements of B reach the tensor core as fp32 bit patterns whose low
  * 13 mantissa bits it ignores (truncation; measured relative Frobenius error about 4.5e-4 against the
  * fp32 CPU product).  With this flag B is rounded to nearest as well (kernel.cu:35; about 2.5e-4) at
- * the cost of one conversion per element of every gathered row.  Not available on CUTESPMM_PATH_SLAB, where
+ * the cost of one conversion per element of every gathered row.  Truncation is one-sided: on operands of
+ * one sign the errors of a row do not cancel and the result comes out low by the mean truncation loss,
+ * measured 3.6e-4 relative (brick and slab path alike; 8.5e-5 with this flag) -- still inside the 1e-3
+ * the tensor-core paths state, with less margin than zero-mean data suggests.  Not available on CUTESPMM_PATH_SLAB, where
  * the copy engine places B in the tensor core's operand layout and no thread touches it. */
 #define CUTESPMM_FLAG_ROUND_B_NEAREST 1u
 
@@ -222,6 +225,11 @@ int cutespmm_spmm_csr_noalloc(uint32_t M, uint32_t K, uint32_t nnz, const uint32
 
 /* Number of kernels one cutespmm_spmm call launches for this plan and N. */
 int cutespmm_spmm_launch_count(const cutespmm_plan_t *plan, uint32_t N);
+
+/* Which kernels those are: bit 0 the CUDA-core row kernel, bit 1 the tensor-core brick kernel, bit 2 the tcgen05 slab
+ * kernel (16-byte aligned operands assumed).  A plan made with path auto runs products narrower than 64 columns on the
+ * row kernel alone, whatever its panels look like: there a row kernel with several rows of A per warp is the faster. */
+int cutespmm_spmm_kernels(const cutespmm_plan_t *plan, uint32_t N);
 
 /* Status word the kernels of this plan write on a failed bounded wait (0 = none; 1 row kernel, 2 brick
  * kernel, 3 slab kernel).  Orders nothing: call after the stream has been synchronised.  A non-zero

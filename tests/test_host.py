@@ -271,6 +271,19 @@ def test_similar_rows_grouping_shrinks_the_panels_column_sets():
         assert grouped["nnz"] == plain["nnz"]
 
 
+def test_kernels_of_a_product_by_width():
+    """Path auto runs the brick kernel from 64 columns on and the row kernel alone below; path brick runs bricks at every
+    width the brick kernel takes (multiples of 32); widths it does not take fall to the row kernel's all-rows list."""
+    gd = load_golden("stencil_16x16")
+    mk = lambda **kw: cs.Plan(int(gd["M"]), int(gd["K"]), gd["row_ptr"], gd["cols"], gd["vals"], host_only=True, **kw)
+    auto, brick, rows = mk(path=cs.PATH_AUTO, min_brick_panels=1), mk(path=cs.PATH_BRICK), mk(path=cs.PATH_ROWS)
+    assert auto.info()["num_bricks"] > 0
+    assert [auto.kernels(n) for n in (16, 32, 48, 64, 128, 100, 512, 576)] == ["rows", "rows", "rows", "brick", "brick", "rows", "brick", "brick"]
+    assert [brick.kernels(n) for n in (32, 64, 48)] == ["brick", "brick", "rows"]
+    assert [rows.kernels(n) for n in (32, 128)] == ["rows", "rows"]
+    assert auto.launch_count(32) == 1 and auto.launch_count(128) == 1 and auto.launch_count(1024) == 2
+
+
 def test_auto_keeps_small_matrices_on_the_row_kernel():
     """The default of path auto: dense panels go to the tensor-core kernel only when there are enough of them to fill
     its grid (4440); a small stencil stays on the row kernel, the 512 x 512 one does not."""
