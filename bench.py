@@ -72,6 +72,7 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-per-config", action="store_true", help="skip the per_config block (1 GPU)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--sddmm", action="store_true", help="1 GPU: also time cutespmm_sddmm over the workload's plan (block \"sddmm\")")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = chosen by operand size)")
     ap.add_argument("--matrices", default="", help="a folder of MatrixMarket files: print the per-matrix table instead of the benchmark line")
     ap.add_argument("--no-reference-gpu", action="store_true", help="--matrices: skip the reference's own kernel")
@@ -416,6 +417,9 @@ def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak, refer
                         "traffic": dram_traffic_for(workload, N, path_name, 1)},
            "e2e_ms_per_step": round(e2e_ms, 3), "e2e_gflops": round(2.0 * A.nnz * N / (e2e_ms * 1e-3) / 1e9, 1),
            "plan_create_ms": round(plan_ms, 1), "plan_builder": how, "rel_fro_sample": err, "rows_checked": rows}
+    if (workload, N) in (("stencil512", 128), ("rmat20", 128)):  # the operator next to the product in a graph layer
+        del Bh, Ch
+        out["sddmm"] = measure_sddmm(plan, A, B, steps, dev, flush, peak)
     plan.close()
     # the reference's own kernel on the same GPU, for context (its preprocessing cannot hold the two R-MAT configurations)
     if reference_gpu and workload in ("uniform4096", "stencil512", "elasticity40"):
@@ -423,6 +427,37 @@ def measure_config(cs, g, workload, N, path_name, steps, dev, flush, peak, refer
         torch.cuda.empty_cache()
         out["reference_gpu"] = reference_gpu_block(workload, N)
     return out
+
+
+def measure_sddmm(plan, A, Y, steps, dev, flush, peak, n_random=1 << 11, seed=11):
+    """cutespmm_sddmm over the same plan and dense operand (Y = B, X = a second dense matrix): device time per call, the
+    algorithmic bytes it stands for (A as CSR once, X once, the rows of Y the pattern names once, one float out per
+    nonzero) and a sample of rows checked against the CPU oracle."""
+    import oracle
+    from cutespmm_ae_b200 import generators as g
+
+    N = Y.shape[1]
+    X = g.dense_operand(A.M, N, 9099, "normal", device=dev)
+    out = torch.empty(A.nnz, dtype=torch.float32, device=dev)
+    ms, _, mn = time_steps(lambda: plan.sddmm(X, Y, out, scale_by_values=True), steps, 3, flush, None, dev)
+    gen = torch.Generator().manual_seed(seed)
+    which = torch.unique(torch.randint(0, A.M, (min(n_random, A.M),), generator=gen).to(dev))
+    deg = A.row_ptr[1:] - A.row_ptr[:-1]
+    lo, lens = A.row_ptr[which], deg[which]
+    rp = torch.zeros(which.numel() + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(lens, 0, out=rp[1:])
+    total = int(rp[-1])
+    idx = torch.repeat_interleave(lo - rp[:-1], lens, output_size=total) + torch.arange(total, device=dev)
+    uniq, inv = torch.unique(A.cols[idx].long(), return_inverse=True)
+    want = oracle.sddmm_csr(rp.cpu().numpy().astype(np.uint64), inv.cpu().numpy().astype(np.uint32), A.vals[idx].cpu().numpy(),
+                            X[which].cpu().numpy(), Y[uniq].cpu().numpy())
+    got = out[idx].cpu().numpy()
+    err = float(np.linalg.norm(want.astype(np.float64) - got) / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
+    balg = 8 * A.nnz + 4 * (A.M + 1) + 4 * N * A.M + 4 * N * min(A.K, A.nnz) + 4 * A.nnz
+    ach = balg / (ms * 1e-3) / 1e9
+    return {"ms_per_step": round(ms, 5), "ms_min": round(mn, 5), "gflops": round(2.0 * A.nnz * N / (ms * 1e-3) / 1e9, 1),
+            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4), "traffic": None},
+            "rel_err_sample": err, "nonzeros_checked": total, "gpu_launches_per_call": 1}
 
 
 def reference_gpu_blocks(workload, Ns, mtx_files=None, timeout=600):
@@ -498,6 +533,7 @@ def run_ours(args):
     C = torch.empty((mine.M, N), dtype=torch.float32, device=dev)
     flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
+    peak, peak_src = measured_hbm_peak()
     sampler = ClockSampler(local).start() if rank == 0 else None
     wall0 = time.perf_counter()
     ms_per_step, med_ms, min_ms = time_steps(lambda: plan.spmm(B, C), args.steps, args.warmup, flush, dist, dev)
@@ -506,6 +542,7 @@ def run_ours(args):
     status = plan.device_status()
     if status != 0:
         raise SystemExit(f"device status word is {status}: a bounded wait ran out")
+    sddmm_block = measure_sddmm(plan, mine, B, min(args.steps, 20), dev, flush, peak) if (args.sddmm and world == 1) else None
     # the same steps back to back without the flush (whatever the previous step left in L2 stays): reported beside the
     # flushed figure, never instead of it
     warm_ms = None
@@ -622,7 +659,6 @@ def run_ours(args):
     # only the rows of B its columns name
     distinct_cols = int(torch.unique(mine.cols).numel()) if world > 1 else K
     bytes_alg = bytes_model(mine.nnz, mine.M, N, min(K, distinct_cols))
-    peak, peak_src = measured_hbm_peak()
     achieved = bytes_alg / (ms_per_step * 1e-3) / 1e9
     gather_bytes = 8 * mine.nnz + 4 * (mine.M + 1) + 4 * N * mine.nnz + 4 * mine.M * N
     line = {
@@ -661,6 +697,8 @@ def run_ours(args):
             line["cpu_baseline"]["sample"] += f"; rows of rank 0's shard ({mine.M} rows)"
     if dist:
         dist.barrier()
+    if sddmm_block is not None:
+        line["sddmm"] = sddmm_block
     if world == 1 and not args.no_per_config:
         del C, Bh_full
         plan.close()

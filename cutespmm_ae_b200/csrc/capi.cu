@@ -678,6 +678,7 @@ int cutespmm_sddmm(const cutespmm_plan_t *p, const float *X, uint64_t ldx, const
     a.num_chunks = (uint32_t)(all ? h.chunks_all.size() : h.chunks.size());
     a.X = X; a.Y = Y; a.ldx = ldx; a.ldy = ldy; a.out = out; a.N = N;
     a.scale = scale_by_values ? 1u : 0u;
+    a.status = p->d_status;
     a.vec4 = !((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) & 15) && !((ldx | ldy) & 3) ? 1u : 0u;
     cudaError_t e = launch_sddmm(a, p->sm_count, s);
     return e == cudaSuccess ? CUTESPMM_OK : fail_cuda(e, "SDDMM kernel launch");

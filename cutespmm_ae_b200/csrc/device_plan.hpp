@@ -57,6 +57,7 @@ struct SddmmArgs {
     uint32_t N;
     uint32_t scale;                      // 1: multiply by the stored value of A
     uint32_t vec4;                       // 1: X, Y and their leading dimensions allow 16-byte loads
+    uint32_t *status;                    // device status word: set to 1 when a bounded wait gives up
 };
 cudaError_t launch_sddmm(const SddmmArgs &a, int sm_count, cudaStream_t s);
 

@@ -19,6 +19,7 @@
 #include "device_plan.hpp"
 #include "plan.hpp"
 #include "ptx.cuh"
+#include "tile_stage.cuh"
 
 namespace cutespmm {
 
@@ -33,17 +34,7 @@ template <bool DEEP> struct Tuning {
     static constexpr int kUnroll = DEEP ? 8 : 4;
     static constexpr int kMinBlocks = DEEP ? 4 : 6;
 };
-constexpr int kWarps = 8;
-constexpr int kStages = 3;  // tiles in flight per block (TMA bulk copies into shared memory)
-
-// One staged tile: its descriptor, the slice of row pointers and the slice of (column, value) pairs,
-// each fetched by one bulk copy that starts on a 16-byte boundary at or before the first needed
-// element (hence the slack of 3 words / 1 pair in front and behind).
-struct __align__(16) TileStage {
-    uint4 desc;                               // row_begin, row_end, pair_begin, pair_end
-    uint32_t row_ptr[kMaxTileRows + 8];
-    uint2 pairs[kMaxTilePairs + 2];
-};
+constexpr int kWarps = kTileWarps;
 constexpr unsigned kFull = 0xffffffffu;
 
 template <int VEC> struct Vec;
@@ -330,36 +321,10 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
     const uint32_t ldb32 = (uint32_t)a.ldb;  // < 2^32 (checked by the caller): one 32x32->64 multiply per address
     const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
 
-    // ---- tiles: descriptor, row pointers and pairs arrive in shared memory by TMA, kStages deep ----
-    __shared__ TileStage stage[kStages];
-    __shared__ __align__(8) uint64_t full_bar[kStages];
-    __shared__ uint32_t next_row[kStages];  // rows of the staged tile already claimed by a warp
-    __shared__ uint32_t warps_done[kStages];
-
-    const uint4 *tiles = reinterpret_cast<const uint4 *>(a.tiles);
-    auto issue = [&](uint32_t t, int s) {  // one thread: fetch tile t into stage s
-        const uint4 d = __ldg(tiles + t);
-        const uint32_t rb = d.x & ~3u, re = (d.y + 1 + 3) & ~3u;  // row pointers [rb, re) cover d.x .. d.y
-        const uint32_t jb = d.z & ~1u, je = (d.w + 1) & ~1u;      // pairs [jb, je) cover d.z .. d.w-1
-        const uint32_t bytes = 16u + (re - rb) * 4u + (je - jb) * 8u;
-        ptx::mbar_expect_tx(&full_bar[s], bytes);
-        ptx::bulk_g2s(&stage[s].desc, tiles + t, 16u, &full_bar[s]);
-        ptx::bulk_g2s(stage[s].row_ptr, a.row_ptr + rb, (re - rb) * 4u, &full_bar[s]);
-        if (je > jb) ptx::bulk_g2s(stage[s].pairs, pairs + jb, (je - jb) * 8u, &full_bar[s]);
-    };
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            ptx::mbar_init(&full_bar[s], 1);
-            next_row[s] = 0;
-            warps_done[s] = 0;
-        }
-        ptx::fence_mbar_init();
-        for (int s = 0; s < kStages; ++s) {
-            const uint64_t t = blockIdx.x + (uint64_t)s * gridDim.x;
-            if (t < a.num_tiles) issue((uint32_t)t, s);
-        }
-    }
-    __syncthreads();
+    // ---- tiles: descriptor, row pointers and pairs arrive in shared memory by TMA, kTileStages deep ----
+    __shared__ TileRing ring;
+    const TileSource src{reinterpret_cast<const uint4 *>(a.tiles), a.row_ptr, pairs, a.num_tiles};
+    tile_ring_start(ring, src);
 
     // Chunks of long rows first (the first tiles are on their way meanwhile): they are the largest single work items.
     if (a.num_chunks)
@@ -370,32 +335,31 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
     for (uint32_t i = 0;; ++i) {
         const uint64_t t = blockIdx.x + (uint64_t)i * gridDim.x;
         if (t >= a.num_tiles) break;
-        const int s = i % kStages;
-        if (!ptx::mbar_wait(&full_bar[s], (i / kStages) & 1u)) {
+        const int s = i % kTileStages;
+        if (!tile_wait(ring, i)) {
             if (lane == 0) atomicExch(a.status, 1u);  // the copy never landed: report, do not hang
             break;
         }
-        const uint4 d = stage[s].desc;
+        const TileStage &st = ring.stage[s];
+        const uint4 d = st.desc;
         const uint32_t rb = d.x & ~3u, jb = d.z & ~1u;
         for (;;) {
-            uint32_t r = 0;
-            if (lane == 0) r = atomicAdd(&next_row[s], (uint32_t)G);
-            r = __shfl_sync(kFull, r, 0) + d.x;
+            uint32_t r = tile_claim_rows(ring, s, (uint32_t)G, lane) + d.x;
             if (r >= d.y) break;
             r += grp;  // the group's own row
             if (G == 1 || r < d.y) {
-                const uint32_t j0 = stage[s].row_ptr[r - rb], j1 = stage[s].row_ptr[r - rb + 1];
+                const uint32_t j0 = st.row_ptr[r - rb], j1 = st.row_ptr[r - rb + 1];
                 V acc[CH];
 #pragma unroll
                 for (int ch = 0; ch < CH; ++ch) zero_vec(acc[ch]);
                 constexpr int U = (CH == 1) ? Tuning<DEEP>::kUnroll : Tuning<DEEP>::kUnroll / 2;  // rows of B in flight per group and step
                 uint32_t j = j0 - jb, jend = j1 - jb;  // positions in the staged pair slice
-                for (; j + U <= jend; j += U) row_group<VEC, CH, FULL, U, false>(acc, stage[s].pairs + j, U, bl, ldb32, ok);
+                for (; j + U <= jend; j += U) row_group<VEC, CH, FULL, U, false>(acc, st.pairs + j, U, bl, ldb32, ok);
                 // what is left of the row (fewer than U nonzeros) goes as one more group, so that its loads are in flight
                 // together instead of one after the other: positions past the end repeat the row's last pair and are not added
                 if (const uint32_t rem = jend - j) {
-                    if (rem > U / 2) row_group<VEC, CH, FULL, U, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
-                    else row_group<VEC, CH, FULL, U / 2, true>(acc, stage[s].pairs + j, rem, bl, ldb32, ok);
+                    if (rem > U / 2) row_group<VEC, CH, FULL, U, true>(acc, st.pairs + j, rem, bl, ldb32, ok);
+                    else row_group<VEC, CH, FULL, U / 2, true>(acc, st.pairs + j, rem, bl, ldb32, ok);
                 }
                 const uint32_t r_out = a.row_map ? __ldg(a.row_map + r) : r;  // a reordered plan writes the row to its place in the caller's C
                 float *out = a.C + (uint64_t)r_out * a.ldc + col0;
@@ -405,21 +369,7 @@ __global__ void __launch_bounds__(kWarps * 32, Tuning<DEEP>::kMinBlocks) spmm_ro
             }
             if constexpr (G > 1) __syncwarp();
         }
-        // this warp is finished with stage s; the last warp to say so refills it
-        __syncwarp();
-        if (lane == 0) {
-            __threadfence_block();
-            if (atomicAdd(&warps_done[s], 1u) == kWarps - 1) {
-                __threadfence_block();
-                warps_done[s] = 0;
-                next_row[s] = 0;
-                const uint64_t t2 = t + (uint64_t)kStages * gridDim.x;
-                if (t2 < a.num_tiles) {
-                    ptx::fence_async_smem();
-                    issue((uint32_t)t2, s);
-                }
-            }
-        }
+        tile_release(ring, src, i, t, lane);  // the last warp to leave the stage refills it
     }
 }
 

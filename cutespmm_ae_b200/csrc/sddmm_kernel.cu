@@ -5,101 +5,150 @@
 // the "edge feature" operator that accompanies SpMM in a graph layer (the reference tree carries it as
 // TC-GNN's forward_ef, TC-GNN_ATC23/TCGNN_conv/TCGNN.cpp:265, and its own kernels do not have it), and
 // the gradient of SpMM with respect to the values of A (dA = SDDMM(dC, B)).  Like the row kernel it is
-// bound by gathering one row of Y per nonzero: a warp owns a row of A, keeps its 128-column slice of
-// X[r] in registers, and handles four nonzeros at a time, eight lanes per nonzero, so that a row of Y
-// is four 128-byte requests and a dot product needs three shuffles.  Long rows are taken chunk by
-// chunk from the plan's work list (no partial sums are needed: every nonzero has its own output).
+// bound by gathering one row of Y per nonzero, and it is built on the same skeleton: the block's tiles
+// arrive in shared memory by TMA, warps claim rows as they go, chunks of long rows are dealt over the
+// blocks first.  A warp keeps the 128-column span of X[r] in registers and handles eight nonzeros per
+// step -- eight lanes per nonzero, so a row of Y is four 128-byte requests and a dot product needs
+// three shuffles; two such groups of four are in flight.  Every nonzero has its own output, so nothing
+// is summed across work items.
 #include <cuda_runtime.h>
 
 #include <cstdint>
 
 #include "device_plan.hpp"
 #include "plan.hpp"
+#include "tile_stage.cuh"
 
 namespace cutespmm {
 
 namespace {
 
-constexpr int kWarps = 8;
 constexpr unsigned kFull = 0xffffffffu;
+constexpr int kSteps = 2;  // groups of four nonzeros in flight per warp
 
-// One pass over columns [c0, c0 + 128) of X and Y for the nonzeros [j0, j1) of `row`.
-// first: this is the first pass (write the result); otherwise add to what the earlier passes wrote.
-__device__ __forceinline__ void sddmm_span(const SddmmArgs &a, uint32_t row, uint32_t j0, uint32_t j1, uint32_t c0, bool first, int lane)
+// The lane's part of the 128-column span that starts at column c0 of a row: float4 number sub, sub+8, sub+16, sub+24.
+template <bool FAST>
+__device__ __forceinline__ void load_span(float4 (&v)[4], const float *row, uint32_t c0, uint32_t N, bool vec4, int sub)
 {
-    const int sub = lane & 7, grp = lane >> 3;  // eight lanes per nonzero, four nonzeros per step
-    const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
-    float4 x[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t c = c0 + (uint32_t)(sub + 8 * i) * 4;
-        x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < a.N) {
-            const float *px = a.X + (uint64_t)row * a.ldx + c;
-            if (a.vec4 && c + 4 <= a.N) x[i] = __ldg(reinterpret_cast<const float4 *>(px));
-            else {
-                x[i].x = __ldg(px);
-                if (c + 1 < a.N) x[i].y = __ldg(px + 1);
-                if (c + 2 < a.N) x[i].z = __ldg(px + 2);
-                if (c + 3 < a.N) x[i].w = __ldg(px + 3);
-            }
-        }
-    }
-    for (uint32_t j = j0; j < j1; j += 4) {
-        const uint32_t mine = j + grp;
-        const bool act = mine < j1;
-        uint2 pr = make_uint2(0u, 0u);
-        if (act) pr = __ldg(pairs + mine);  // the eight lanes of a group read one address
-        float s = 0.f;
-        if (act) {
-            const float *py = a.Y + (uint64_t)pr.x * a.ldy + c0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t c = (uint32_t)(sub + 8 * i) * 4;
-                if (c0 + c < a.N) {
-                    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (a.vec4 && c0 + c + 4 <= a.N) y = __ldg(reinterpret_cast<const float4 *>(py + c));
-                    else {
-                        y.x = __ldg(py + c);
-                        if (c0 + c + 1 < a.N) y.y = __ldg(py + c + 1);
-                        if (c0 + c + 2 < a.N) y.z = __ldg(py + c + 2);
-                        if (c0 + c + 3 < a.N) y.w = __ldg(py + c + 3);
-                    }
-                    s = fmaf(x[i].x, y.x, s);
-                    s = fmaf(x[i].y, y.y, s);
-                    s = fmaf(x[i].z, y.z, s);
-                    s = fmaf(x[i].w, y.w, s);
+        if (FAST) {
+            v[i] = __ldg(reinterpret_cast<const float4 *>(row + c));
+        } else {
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < N) {
+                if (vec4 && c + 4 <= N) v[i] = __ldg(reinterpret_cast<const float4 *>(row + c));
+                else {
+                    v[i].x = __ldg(row + c);
+                    if (c + 1 < N) v[i].y = __ldg(row + c + 1);
+                    if (c + 2 < N) v[i].z = __ldg(row + c + 2);
+                    if (c + 3 < N) v[i].w = __ldg(row + c + 3);
                 }
             }
-        }
-        s += __shfl_xor_sync(kFull, s, 4);
-        s += __shfl_xor_sync(kFull, s, 2);
-        s += __shfl_xor_sync(kFull, s, 1);
-        if (act && sub == 0) {
-            if (a.scale) s *= __uint_as_float(pr.y);
-            a.out[mine] = first ? s : a.out[mine] + s;
         }
     }
 }
 
-__global__ void __launch_bounds__(kWarps * 32) sddmm_kernel(SddmmArgs a)
+__device__ __forceinline__ float dot_span(const float4 (&x)[4], const float4 (&y)[4])
 {
-    const int lane = threadIdx.x & 31;
-    const uint32_t gw = blockIdx.x * kWarps + (threadIdx.x >> 5), nw = gridDim.x * kWarps;
-    for (uint32_t c0 = 0; c0 < a.N; c0 += 128) {
-        // chunks of long rows (row, j0, j1, slot): the largest items first
-        for (uint32_t c = gw; c < a.num_chunks; c += nw) {
-            const uint4 ck = __ldg(reinterpret_cast<const uint4 *>(a.chunks) + c);
-            sddmm_span(a, ck.x, ck.y, ck.z, c0, c0 == 0, lane);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        s = fmaf(x[i].x, y[i].x, s);
+        s = fmaf(x[i].y, y[i].y, s);
+        s = fmaf(x[i].z, y[i].z, s);
+        s = fmaf(x[i].w, y[i].w, s);
+    }
+    return s;
+}
+
+// Nonzeros [0, cnt) of one row (or chunk) whose pairs are pair_at(k) and whose outputs are out[k]: the span c0 of
+// X[row] against the same span of the rows of Y they name.  first: write; otherwise add to the earlier spans' sums.
+template <bool FAST, class PairAt>
+__device__ __forceinline__ void sddmm_items(const SddmmArgs &a, const float4 (&x)[4], PairAt pair_at, uint32_t cnt, float *out,
+                                            uint32_t c0, bool first, int lane)
+{
+    const int sub = lane & 7, grp = lane >> 3;
+    for (uint32_t k = 0; k < cnt; k += 4 * kSteps) {
+        uint2 pr[kSteps];
+        float4 y[kSteps][4];
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) {
+            const uint32_t mine = k + u * 4 + grp;
+            pr[u] = pair_at(min(mine, cnt - 1));  // positions past the end repeat the last pair (a cache hit) and are not stored
+            load_span<FAST>(y[u], a.Y + (uint64_t)pr[u].x * a.ldy, c0, a.N, a.vec4 != 0, sub);
         }
-        // every other row: a warp takes the rows of the tiles in turn
-        for (uint32_t t = blockIdx.x; t < a.num_tiles; t += gridDim.x) {
-            const uint4 d = __ldg(reinterpret_cast<const uint4 *>(a.tiles) + t);  // row_begin, row_end, pair_begin, pair_end
-            for (uint32_t r = d.x + (threadIdx.x >> 5); r < d.y; r += kWarps) {
-                const uint32_t j0 = __ldg(a.row_ptr + r), j1 = __ldg(a.row_ptr + r + 1);
-                if (j1 > j0) sddmm_span(a, r, j0, j1, c0, c0 == 0, lane);
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) {
+            float s = dot_span(x, y[u]);
+            s += __shfl_xor_sync(kFull, s, 4);
+            s += __shfl_xor_sync(kFull, s, 2);
+            s += __shfl_xor_sync(kFull, s, 1);
+            const uint32_t mine = k + u * 4 + grp;
+            if (mine < cnt && sub == 0) {
+                if (a.scale) s *= __uint_as_float(pr[u].y);
+                out[mine] = first ? s : out[mine] + s;
             }
         }
+    }
+}
+
+template <bool FAST>
+__global__ void __launch_bounds__(kTileWarps * 32, 3) sddmm_kernel(SddmmArgs a)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7;
+    const uint2 *pairs = reinterpret_cast<const uint2 *>(a.pairs);
+    __shared__ TileRing ring;
+    const TileSource src{reinterpret_cast<const uint4 *>(a.tiles), a.row_ptr, pairs, a.num_tiles};
+    tile_ring_start(ring, src);
+
+    // chunks of long rows first (the tiles are on their way): chunk c goes to block c mod gridDim.x.  The pairs of a
+    // chunk come 32 at a time with one coalesced load, the next 32 while these are in use.
+    {
+        const uint4 *chunks = reinterpret_cast<const uint4 *>(a.chunks);
+        for (uint32_t c = warp * gridDim.x + blockIdx.x; c < a.num_chunks; c += gridDim.x * kTileWarps) {
+            const uint4 ck = __ldg(chunks + c);  // row, j0, j1, slot
+            for (uint32_t c0 = 0; c0 < a.N; c0 += 128) {
+                float4 x[4];
+                load_span<FAST>(x, a.X + (uint64_t)ck.x * a.ldx, c0, a.N, a.vec4 != 0, sub);
+                uint2 nxt = make_uint2(0u, 0u);
+                if (ck.y + lane < ck.z) nxt = __ldg(pairs + ck.y + lane);
+                for (uint32_t j = ck.y; j < ck.z; j += 32) {
+                    const uint2 cur = nxt;
+                    if (j + 32 + lane < ck.z) nxt = __ldg(pairs + j + 32 + lane);
+                    auto pair_at = [&](uint32_t k) { return make_uint2(__shfl_sync(kFull, cur.x, (int)k), __shfl_sync(kFull, cur.y, (int)k)); };
+                    sddmm_items<FAST>(a, x, pair_at, min(32u, ck.z - j), a.out + j, c0, c0 == 0, lane);
+                }
+            }
+        }
+    }
+
+    for (uint32_t i = 0;; ++i) {
+        const uint64_t t = blockIdx.x + (uint64_t)i * gridDim.x;
+        if (t >= a.num_tiles) break;
+        const int s = i % kTileStages;
+        if (!tile_wait(ring, i)) {
+            if (lane == 0) atomicExch(a.status, 1u);  // the copy never landed: report, do not hang
+            break;
+        }
+        const TileStage &st = ring.stage[s];
+        const uint4 d = st.desc;
+        const uint32_t rb = d.x & ~3u, jb = d.z & ~1u;
+        for (;;) {
+            const uint32_t r = tile_claim_rows(ring, s, 1u, lane) + d.x;
+            if (r >= d.y) break;
+            const uint32_t j0 = st.row_ptr[r - rb], j1 = st.row_ptr[r - rb + 1];
+            if (j1 == j0) continue;
+            const uint2 *row_pairs = st.pairs + (j0 - jb);
+            auto pair_at = [&](uint32_t k) { return row_pairs[k]; };  // the lanes of a group read one address
+            for (uint32_t c0 = 0; c0 < a.N; c0 += 128) {
+                float4 x[4];
+                load_span<FAST>(x, a.X + (uint64_t)r * a.ldx, c0, a.N, a.vec4 != 0, sub);
+                sddmm_items<FAST>(a, x, pair_at, j1 - j0, a.out + j0, c0, c0 == 0, lane);
+            }
+        }
+        tile_release(ring, src, i, t, lane);
     }
 }
 
@@ -108,10 +157,12 @@ __global__ void __launch_bounds__(kWarps * 32) sddmm_kernel(SddmmArgs a)
 cudaError_t launch_sddmm(const SddmmArgs &a, int sm_count, cudaStream_t s)
 {
     if (a.num_tiles == 0 && a.num_chunks == 0) return cudaSuccess;
-    uint32_t blocks = a.num_tiles > (a.num_chunks + kWarps - 1) / kWarps ? a.num_tiles : (a.num_chunks + kWarps - 1) / kWarps;
-    const uint32_t cap = (uint32_t)sm_count * 8;
+    const uint32_t chunk_blocks = (a.num_chunks + kTileWarps - 1) / kTileWarps;
+    uint32_t blocks = a.num_tiles > chunk_blocks ? a.num_tiles : chunk_blocks;
+    const uint32_t cap = (uint32_t)sm_count * 3;  // one resident wave
     if (blocks > cap) blocks = cap;
-    sddmm_kernel<<<blocks, kWarps * 32, 0, s>>>(a);
+    if (a.vec4 && a.N % 128 == 0) sddmm_kernel<true><<<blocks, kTileWarps * 32, 0, s>>>(a);
+    else sddmm_kernel<false><<<blocks, kTileWarps * 32, 0, s>>>(a);
     return cudaGetLastError();
 }
 
