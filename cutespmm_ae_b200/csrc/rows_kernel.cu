@@ -6,12 +6,14 @@
 // bricks included; its tile splitter (inc/splitter.hpp:34-124) that would send light tiles to CUDA
 // cores is never called.  Here a warp owns one row at a time: the lanes span the columns of B
 // (one float4 each at N = 128, so a row of B is one coalesced 512-byte request), the row's
-// (column, value) pairs are fetched 32 at a time with one coalesced 8-byte load per lane and handed
-// round with shuffles, and the products are accumulated in fp32 registers in storage order.  The
-// eight warps of a block take interleaved rows of one scheduling tile, so rows that share columns
-// (stencils, block structure) meet in L1.  C rows are written once with streaming stores; nothing
-// is read-modify-written: a long row is cut into chunks whose partial sums go to a scratch matrix and
-// are added, in slot order, by whichever warp finishes the row's last chunk (one counter per long row).
+// (column, value) pairs are read from the block's staged tile in shared memory (tile_stage.cuh; one
+// broadcast read per nonzero), and the products are accumulated in fp32 registers in storage order.
+// For narrow products (N <= 64) a warp splits into groups of N/4 lanes and owns that many rows at
+// once.  The eight warps of a block claim the rows of one scheduling tile as they go, so rows that
+// share columns (stencils, block structure) meet in L1.  C rows are written once with streaming
+// stores; nothing is read-modify-written: a long row is cut into chunks whose partial sums go to a
+// scratch matrix and are added, in slot order, by whichever warp finishes the row's last chunk (one
+// counter per long row), in the same launch.
 #include <cuda_runtime.h>
 
 #include <cstdint>
