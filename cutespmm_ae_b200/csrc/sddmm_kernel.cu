@@ -63,35 +63,44 @@ __device__ __forceinline__ float dot_span(const float4 (&x)[4], const float4 (&y
     return s;
 }
 
-// Nonzeros [0, cnt) of one row (or chunk) whose pairs are pair_at(k) and whose outputs are out[k]: the span c0 of
-// X[row] against the same span of the rows of Y they name.  first: write; otherwise add to the earlier spans' sums.
+// STEPS groups of four nonzeros, starting at nonzero k of the item: the span c0 of X[row] (in x) against the same span
+// of the rows of Y they name.  first: write; otherwise add to the earlier spans' sums.
+template <bool FAST, int STEPS, class PairAt>
+__device__ __forceinline__ void sddmm_step(const SddmmArgs &a, const float4 (&x)[4], PairAt pair_at, uint32_t k, uint32_t cnt, float *out,
+                                           uint32_t c0, bool first, int lane)
+{
+    const int sub = lane & 7, grp = lane >> 3;
+    uint2 pr[STEPS];
+    float4 y[STEPS][4];
+#pragma unroll
+    for (int u = 0; u < STEPS; ++u) {
+        const uint32_t mine = k + u * 4 + grp;
+        pr[u] = pair_at(min(mine, cnt - 1));  // positions past the end repeat the last pair (a cache hit) and are not stored
+        load_span<FAST>(y[u], a.Y + (uint64_t)pr[u].x * a.ldy, c0, a.N, a.vec4 != 0, sub);
+    }
+#pragma unroll
+    for (int u = 0; u < STEPS; ++u) {
+        float s = dot_span(x, y[u]);
+        s += __shfl_xor_sync(kFull, s, 4);
+        s += __shfl_xor_sync(kFull, s, 2);
+        s += __shfl_xor_sync(kFull, s, 1);
+        const uint32_t mine = k + u * 4 + grp;
+        if (mine < cnt && sub == 0) {
+            if (a.scale) s *= __uint_as_float(pr[u].y);
+            out[mine] = first ? s : out[mine] + s;
+        }
+    }
+}
+
+// Nonzeros [0, cnt) of one row (or chunk) whose pairs are pair_at(k) and whose outputs are out[k]: kSteps groups of four
+// in flight while more than four nonzeros are left, one group for a tail of one to four.
 template <bool FAST, class PairAt>
 __device__ __forceinline__ void sddmm_items(const SddmmArgs &a, const float4 (&x)[4], PairAt pair_at, uint32_t cnt, float *out,
                                             uint32_t c0, bool first, int lane)
 {
-    const int sub = lane & 7, grp = lane >> 3;
-    for (uint32_t k = 0; k < cnt; k += 4 * kSteps) {
-        uint2 pr[kSteps];
-        float4 y[kSteps][4];
-#pragma unroll
-        for (int u = 0; u < kSteps; ++u) {
-            const uint32_t mine = k + u * 4 + grp;
-            pr[u] = pair_at(min(mine, cnt - 1));  // positions past the end repeat the last pair (a cache hit) and are not stored
-            load_span<FAST>(y[u], a.Y + (uint64_t)pr[u].x * a.ldy, c0, a.N, a.vec4 != 0, sub);
-        }
-#pragma unroll
-        for (int u = 0; u < kSteps; ++u) {
-            float s = dot_span(x, y[u]);
-            s += __shfl_xor_sync(kFull, s, 4);
-            s += __shfl_xor_sync(kFull, s, 2);
-            s += __shfl_xor_sync(kFull, s, 1);
-            const uint32_t mine = k + u * 4 + grp;
-            if (mine < cnt && sub == 0) {
-                if (a.scale) s *= __uint_as_float(pr[u].y);
-                out[mine] = first ? s : out[mine] + s;
-            }
-        }
-    }
+    uint32_t k = 0;
+    for (; k + 4 < cnt; k += 4 * kSteps) sddmm_step<FAST, kSteps>(a, x, pair_at, k, cnt, out, c0, first, lane);
+    if (k < cnt) sddmm_step<FAST, 1>(a, x, pair_at, k, cnt, out, c0, first, lane);
 }
 
 template <bool FAST>
