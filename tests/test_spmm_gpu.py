@@ -91,6 +91,38 @@ def test_same_sign_operands_keep_the_stated_bound_on_the_tensor_core_paths(oracl
     assert errs["brick_nearest"] <= 0.5 * errs["brick"]
 
 
+@pytest.mark.parametrize("kind", ["rows_with_long_rows", "brick"])
+def test_product_captured_in_a_cuda_graph_and_replayed(oracle_mod, kind):
+    """cutespmm_spmm allocates nothing and synchronises nothing, so an iterative caller can capture it in a CUDA graph:
+    the replays must give the product of whatever B holds at replay time (the long rows' arrival counters are back at
+    zero after every launch)."""
+    if kind == "brick":
+        A = g.stencil9(64, 64)
+        plan = cs.Plan.from_csr(A, path=cs.PATH_BRICK)
+        tol = REL_FRO_TOL
+    else:
+        A = g.rmat(11, 8, seed=71, values="uniform")
+        plan = cs.Plan.from_csr(A, path=cs.PATH_ROWS)
+        assert plan.info()["num_long_rows"] > 0
+        tol = REL_FRO_TOL_FP32
+    N = 128
+    B = g.dense_operand(A.K, N, 72).cuda()
+    C = torch.full((A.M, N), float("nan"), device="cuda")
+    plan.spmm(B, C)  # first launch outside the capture (kernel attributes, module load)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        plan.spmm(B, C)
+    for seed in (73, 74, 75):
+        B.copy_(g.dense_operand(A.K, N, seed).cuda())
+        C.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = oracle_mod.spmm_csr(A.row_ptr, A.cols, A.vals, B.cpu().numpy(), A.M, A.K)
+        assert oracle_mod.rel_fro(ref, C.cpu().numpy()) <= tol
+    assert plan.device_status() == 0
+
+
 def test_strided_and_misaligned_operands(oracle_mod):
     A = g.uniform_random(300, 200, 5, seed=41)  # M not a multiple of 16
     p = cs.Plan.from_csr(A, path=cs.PATH_ROWS)
@@ -297,8 +329,8 @@ def test_largest_configuration_at_its_own_size(oracle_mod):
 @pytest.mark.parametrize("path", [cs.PATH_ROWS, cs.PATH_BRICK, cs.PATH_AUTO], ids=["rows", "brick", "auto"])
 def test_row_clustering_keeps_the_callers_row_order(oracle_mod, path, how):
     """A plan with CUTESPMM_REORDER_CLUSTER_ROWS processes the rows in another order but writes every row of C to its
-    own place: the product of a row-shuffled stencil and of a power-law graph (hub rows cut into chunks: the fix-up
-    kernel writes mapped rows too) must equal the oracle's on the caller's matrix."""
+    own place: the product of a row-shuffled stencil and of a power-law graph (hub rows cut into chunks: the in-launch sum
+    writes mapped rows too) must equal the oracle's on the caller's matrix."""
     from test_host import _shuffle_rows
 
     S, _ = _shuffle_rows(g.stencil9(160))
