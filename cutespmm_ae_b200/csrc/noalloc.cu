@@ -22,6 +22,7 @@
 // No counterpart in the reference project.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <mutex>
 #include <string>
@@ -41,6 +42,7 @@ constexpr int kSlab = 128;                                        // columns one
 constexpr unsigned kFull = 0xffffffffu;
 
 static __device__ __align__(256) float g_scratch[kScratchFloats];
+static __device__ uint32_t g_next_row[CUTESPMM_NOALLOC_MAX_N / kSlab];  // row counters of the rows kernel, one per column slab
 
 // Slot of the chunk that starts at nonzero position `start`.  Chunks of one row start kSplit apart
 // and two long rows start more than kSplit apart, so a window of kSplit positions holds at most one
@@ -70,6 +72,7 @@ __device__ __forceinline__ void accumulate(float (&acc)[4], const uint32_t *__re
                                            const float *__restrict__ B, uint64_t ldb, uint32_t n0, uint32_t N, uint32_t K,
                                            int lane)
 {
+    constexpr int U = 4;  // nonzeros whose rows of B are in flight together
     for (uint32_t j = j0; j < j1; j += 32) {
         const uint32_t n = min(32u, j1 - j);
         uint32_t c = 0;
@@ -78,38 +81,57 @@ __device__ __forceinline__ void accumulate(float (&acc)[4], const uint32_t *__re
             c = __ldg(cols + j + lane);
             v = __ldg(vals + j + lane);
         }
-        for (uint32_t k = 0; k < n; ++k) {
-            const uint32_t ck = __shfl_sync(kFull, c, k);
-            const float vk = __shfl_sync(kFull, v, k);
-            if (ck >= K) continue;  // uniform across the warp
-            const float *row = B + (uint64_t)ck * ldb + n0 + lane;
+        for (uint32_t k = 0; k < n; k += U) {
+            float vk[U], b[U][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                if (n0 + lane + 32 * i < N) acc[i] = fmaf(vk, __ldg(row + 32 * i), acc[i]);
+            for (int u = 0; u < U; ++u) {
+                const int src = (int)min(k + u, n - 1);  // positions past the end repeat the last one and add nothing
+                const uint32_t ck = __shfl_sync(kFull, c, src);
+                vk[u] = __shfl_sync(kFull, v, src);
+                const bool use = k + u < n && ck < K;    // uniform across the warp
+                if (!use) vk[u] = 0.f;
+                const float *row = B + (uint64_t)ck * ldb + n0 + lane;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) b[u][i] = (use && n0 + lane + 32 * i < N) ? __ldg(row + 32 * i) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i] = fmaf(vk[u], b[u][i], acc[i]);
         }
     }
 }
 
-// Rows of at most kSplit nonzeros: one warp per row, result straight to C.
+// Rows of at most kSplit nonzeros: one warp per row, result straight to C.  Warps claim kClaim consecutive rows at a
+// time from a counter per column slab (next_row, zeroed by the host before the launch): a fixed stride would hand the
+// rows r, r + stride, ... of a power-law graph -- whose long rows sit at indices with few one-bits -- to the same few warps.
+constexpr uint32_t kClaim = 4;
 __global__ void __launch_bounds__(kWarps * 32) noalloc_rows_kernel(const uint32_t *__restrict__ rowPtr,
                                                                    const uint32_t *__restrict__ cols,
                                                                    const float *__restrict__ vals, uint32_t M,
                                                                    uint32_t K, uint32_t nnz,
                                                                    const float *__restrict__ B, uint64_t ldb,
-                                                                   float *__restrict__ C, uint64_t ldc, uint32_t N)
+                                                                   float *__restrict__ C, uint64_t ldc, uint32_t N,
+                                                                   uint32_t *__restrict__ next_row)
 {
     const int lane = threadIdx.x & 31;
     const uint32_t n0 = blockIdx.y * kSlab;
-    const uint64_t nw = (uint64_t)gridDim.x * kWarps;
-    for (uint64_t r = (uint64_t)blockIdx.x * kWarps + (threadIdx.x >> 5); r < M; r += nw) {
-        const Range rg = row_range(rowPtr, r, nnz);
-        const uint32_t j0 = rg.j0, j1 = rg.j1;
-        if (j1 - j0 > kSplit) continue;  // written by the fix-up kernel
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        accumulate(acc, cols, vals, j0, j1, B, ldb, n0, N, K, lane);
+    for (;;) {
+        uint32_t first = 0;
+        if (lane == 0) first = atomicAdd(next_row + blockIdx.y, kClaim);
+        first = __shfl_sync(kFull, first, 0);
+        if (first >= M) break;  // also ends the loop should the counter ever wrap: M < 2^32 - kClaim * warps is not assumed
+        const uint32_t last = min(M, first + kClaim);
+        for (uint64_t r = first; r < last; ++r) {
+            const Range rg = row_range(rowPtr, r, nnz);
+            const uint32_t j0 = rg.j0, j1 = rg.j1;
+            if (j1 - j0 > kSplit) continue;  // written by the fix-up kernel
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            accumulate(acc, cols, vals, j0, j1, B, ldb, n0, N, K, lane);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            if (n0 + lane + 32 * i < N) C[r * ldc + n0 + lane + 32 * i] = acc[i];
+            for (int i = 0; i < 4; ++i)
+                if (n0 + lane + 32 * i < N) C[r * ldc + n0 + lane + 32 * i] = acc[i];
+        }
     }
 }
 
@@ -183,7 +205,10 @@ __global__ void __launch_bounds__(kWarps * 32) noalloc_fixup_kernel(const uint32
 // Device address of g_scratch and the SM count, looked up once per device.
 struct DeviceSetup {
     float *scratch = nullptr;
+    uint32_t *next_row = nullptr;
     int sm_count = 0;
+    int rows_blocks_per_sm = 0;  // resident blocks of the rows kernel: its grid is one resident wave
+    int chunks_blocks_per_sm = 0;  // the same for the chunks kernel
 };
 constexpr int kMaxDevices = 64;
 DeviceSetup g_setup[kMaxDevices];
@@ -231,7 +256,20 @@ extern "C" int cutespmm_spmm_csr_noalloc(uint32_t M, uint32_t K, uint32_t nnz, c
             e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
             if (e != cudaSuccess || sms <= 0)
                 return fail(CUTESPMM_ECUDA, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+            uint32_t *ctr = nullptr;
+            e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ctr), g_next_row);
+            if (e != cudaSuccess || !ctr)
+                return fail(CUTESPMM_ECUDA, std::string("cudaGetSymbolAddress(row counters): ") + cudaGetErrorString(e));
+            int per_sm = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, noalloc_rows_kernel, kWarps * 32, 0);
+            if (e != cudaSuccess) return fail(CUTESPMM_ECUDA, std::string("cudaOccupancyMaxActiveBlocksPerMultiprocessor: ") + cudaGetErrorString(e));
+            int per_sm_chunks = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_chunks, noalloc_chunks_kernel, kWarps * 32, 0);
+            if (e != cudaSuccess) return fail(CUTESPMM_ECUDA, std::string("cudaOccupancyMaxActiveBlocksPerMultiprocessor: ") + cudaGetErrorString(e));
             g_setup[dev].sm_count = sms;
+            g_setup[dev].rows_blocks_per_sm = per_sm > 0 ? per_sm : 1;
+            g_setup[dev].chunks_blocks_per_sm = per_sm_chunks > 0 ? per_sm_chunks : 1;
+            g_setup[dev].next_row = ctr;
             g_setup[dev].scratch = ptr;
         }
         setup = g_setup[dev];
@@ -243,10 +281,18 @@ extern "C" int cutespmm_spmm_csr_noalloc(uint32_t M, uint32_t K, uint32_t nnz, c
         const uint64_t b = (items + kWarps - 1) / kWarps;
         return (uint32_t)(b < 1 ? 1 : (b > max_blocks ? max_blocks : b));
     };
-    noalloc_rows_kernel<<<dim3(blocks_for(M), slabs), kWarps * 32, 0, s>>>(rowPtr_dev, cols_dev, vals_dev, M, K, nnz, B_dev,
-                                                                           ldb, C_dev, ldc, N);
+    // the rows kernel: one resident wave of blocks whose warps claim rows from a counter per slab, zeroed here on the stream
+    e = cudaMemsetAsync(setup.next_row, 0, sizeof(uint32_t) * (CUTESPMM_NOALLOC_MAX_N / kSlab), s);
+    if (e != cudaSuccess) return fail(CUTESPMM_ECUDA, std::string("cutespmm_spmm_csr_noalloc: clearing the row counters: ") + cudaGetErrorString(e));
+    {
+        const uint64_t want = ((uint64_t)M + kClaim * kWarps - 1) / (kClaim * kWarps);
+        const uint64_t wave = (uint64_t)setup.sm_count * setup.rows_blocks_per_sm;
+        noalloc_rows_kernel<<<dim3((uint32_t)(want < wave ? (want ? want : 1) : wave), slabs), kWarps * 32, 0, s>>>(
+            rowPtr_dev, cols_dev, vals_dev, M, K, nnz, B_dev, ldb, C_dev, ldc, N, setup.next_row);
+    }
     if (nnz > kSplit) {  // a long row needs more than kSplit nonzeros
-        noalloc_chunks_kernel<<<dim3(blocks_for((nnz + kSplit - 1) / kSplit), slabs), kWarps * 32, 0, s>>>(
+        const uint32_t chunk_wave = (uint32_t)setup.sm_count * (uint32_t)setup.chunks_blocks_per_sm;
+        noalloc_chunks_kernel<<<dim3(std::min(blocks_for((nnz + kSplit - 1) / kSplit), chunk_wave), slabs), kWarps * 32, 0, s>>>(
             rowPtr_dev, cols_dev, vals_dev, M, K, nnz, B_dev, ldb, setup.scratch, lds, N);
         noalloc_fixup_kernel<<<dim3(blocks_for(M), slabs), kWarps * 32, 0, s>>>(rowPtr_dev, M, nnz, setup.scratch, lds,
                                                                                 C_dev, ldc, N);
