@@ -208,14 +208,15 @@ int cutespmm_sddmm(const cutespmm_plan_t *plan, const float *X_dev, uint64_t ldx
  * row, rows longer than CUTESPMM_NOALLOC_SPLIT_NNZ cut into chunks whose partial sums are added in a
  * fixed order).  The partial sums live in a CUTESPMM_NOALLOC_SCRATCH_BYTES array that is part of the
  * library image: every GPU that loads the library holds it until the process exits.  The call makes no
- * cudaMalloc/cudaFree and calls no allocating routine.
+ * cudaMalloc/cudaFree and calls no allocating or synchronising routine: on the caller's stream it queues one
+ * 16-byte cudaMemsetAsync (the counters its warps claim rows from, also part of the image) and up to three kernels.
  * Limits, checked before anything is launched (CUTESPMM_EUNSUPPORTED with a message otherwise):
  *   N <= CUTESPMM_NOALLOC_MAX_N   and   (2*ceil(nnz/SPLIT_NNZ) + 2) * roundup(N, 4) * 4 <= SCRATCH_BYTES
  *   (16.7 M nonzeros at N = 128).
  * All calls on a device share the scratch, which keeps the previous call's contents; nothing in it
  * needs clearing, but calls that overlap on the same GPU race on it -- keep them on one stream or
- * order them with events.  The first call on each device looks up the scratch's device address
- * (cudaGetSymbolAddress); make that first call outside any stream capture. */
+ * order them with events.  The first call on each device looks up the device addresses of the scratch and the
+ * counters (cudaGetSymbolAddress) and the kernels' occupancy; make that first call outside any stream capture. */
 #define CUTESPMM_NOALLOC_SCRATCH_BYTES (16u << 20)
 #define CUTESPMM_NOALLOC_SPLIT_NNZ 1024u
 #define CUTESPMM_NOALLOC_MAX_N 512u
