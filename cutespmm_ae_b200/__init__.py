@@ -78,6 +78,7 @@ def _load() -> C.CDLL:
         "cutespmm_spmm_host": (C.c_int, [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_uint32, vp, f32p]),
         "cutespmm_spmm_launch_count": (C.c_int, [vp, C.c_uint32]),
         "cutespmm_spmm_kernels": (C.c_int, [vp, C.c_uint32]),
+        "cutespmm_plan_set_values": (C.c_int, [vp, vp, vp]),
         "cutespmm_spmm_csr_noalloc": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, vp, vp, vp, vp, C.c_uint64, vp,
                                                 C.c_uint64, C.c_uint32, vp]),
         "cutespmm_plan_device_status": (C.c_int, [vp, u32p]),
@@ -281,6 +282,16 @@ class Plan:
         _check(lib.cutespmm_sddmm(self._h, X.data_ptr(), X.stride(0) if self.M > 1 else max(N, 1), Y.data_ptr(),
                                   Y.stride(0) if self.K > 1 else max(N, 1), N, 1 if scale_by_values else 0, out.data_ptr(), st))
         return out
+
+    def set_values(self, vals, stream=None):
+        """New values for the same pattern (cutespmm_plan_set_values): vals is a CUDA fp32 tensor with one element per
+        nonzero in the plan's storage order, e.g. normalised output of `sddmm`."""
+        import torch
+
+        if not vals.is_cuda or vals.dtype != torch.float32 or vals.numel() != self.nnz or not vals.is_contiguous():
+            raise ValueError("vals must be a contiguous CUDA fp32 tensor with one element per nonzero")
+        st = (stream or torch.cuda.current_stream(vals.device)).cuda_stream
+        _check(lib.cutespmm_plan_set_values(self._h, vals.data_ptr(), st))
 
     def spmm_sharded(self, comm: "Comm", B, Cout=None, *, b_mode: int = B_RESIDENT, root: int = 0, b_bounds=None, stream=None):
         """This rank's rows of A @ B through cutespmm_spmm_sharded: B (K x N, contiguous, on this rank's GPU) is

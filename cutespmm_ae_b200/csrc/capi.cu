@@ -457,7 +457,7 @@ int cutespmm_plan_active_cols(const cutespmm_plan_t *p, uint32_t *out)
 int cutespmm_plan_decode_csr(const cutespmm_plan_t *p, uint64_t *rowPtr, uint32_t *cols, float *vals)
 {
     if (!p || !rowPtr || (p->host.nnz && (!cols || !vals))) return fail(CUTESPMM_EINVAL, "null argument");
-    if (p->host.device_built && p->on_device) {  // the pairs live on the device only, in CSR order
+    if ((p->host.device_built || p->host.values_on_device) && p->on_device) {  // the current pairs live on the device, in CSR order
         const HostPlan &h = p->host;
         for (uint64_t r = 0; r <= h.M; ++r) rowPtr[r] = h.row_ptr[r];
         std::vector<Pair> pr(h.nnz);
@@ -682,6 +682,26 @@ int cutespmm_sddmm(const cutespmm_plan_t *p, const float *X, uint64_t ldx, const
     a.vec4 = !((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) & 15) && !((ldx | ldy) & 3) ? 1u : 0u;
     cudaError_t e = launch_sddmm(a, p->sm_count, s);
     return e == cudaSuccess ? CUTESPMM_OK : fail_cuda(e, "SDDMM kernel launch");
+}
+
+int cutespmm_plan_set_values(cutespmm_plan_t *p, const float *vals_dev, void *stream)
+{
+    if (!p) return fail(CUTESPMM_EINVAL, "plan is NULL");
+    if (!p->on_device) return fail(CUTESPMM_EUNSUPPORTED, "host-only plan has no device arrays");
+    const HostPlan &h = p->host;
+    if (h.num_bricks || h.slab_panels)
+        return fail(CUTESPMM_EUNSUPPORTED, "values can be replaced in a plan whose rows all run on the row kernel (path rows, or auto without dense panels)");
+    if (!h.row_map.empty()) return fail(CUTESPMM_EUNSUPPORTED, "values cannot be replaced in a plan with row reordering");
+    if (h.nnz == 0) return CUTESPMM_OK;
+    if (!vals_dev) return fail(CUTESPMM_EINVAL, "vals is NULL");
+    if (reinterpret_cast<uintptr_t>(vals_dev) & 3) return fail(CUTESPMM_EINVAL, "vals must be 4-byte aligned");
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != p->device)
+        return fail(CUTESPMM_EINVAL, "the current CUDA device is not the one the plan was created on");
+    const cudaError_t e = launch_set_values(p->d_pairs, vals_dev, h.nnz, p->sm_count, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(e, "replacing the values");
+    p->host.values_on_device = true;
+    return CUTESPMM_OK;
 }
 
 int cutespmm_plan_device_status(const cutespmm_plan_t *p, uint32_t *status)

@@ -161,7 +161,23 @@ __global__ void __launch_bounds__(256) pack_pairs_kernel(const uint32_t *__restr
     if (__any_sync(0xffffffffu, out_of_range) && (threadIdx.x & 31) == 0) atomicOr(bad, 1u);
 }
 
+// pairs[j].value = vals[j]: new values for an unchanged pattern.
+__global__ void __launch_bounds__(256) set_values_kernel(uint2 *__restrict__ pairs, const float *__restrict__ vals, uint64_t nnz)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < nnz; j += stride) pairs[j].y = __float_as_uint(__ldcs(vals + j));
+}
+
 }  // namespace
+
+cudaError_t launch_set_values(void *pairs, const float *vals, uint64_t nnz, int sm_count, cudaStream_t s)
+{
+    if (nnz == 0) return cudaSuccess;
+    const uint64_t want = (nnz + 255) / 256;
+    const uint32_t blocks = (uint32_t)(want < (uint64_t)sm_count * 8 ? want : (uint64_t)sm_count * 8);
+    set_values_kernel<<<blocks, 256, 0, s>>>(static_cast<uint2 *>(pairs), vals, nnz);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_pack_pairs(const uint32_t *cols, const float *vals, void *pairs, uint64_t nnz, uint32_t K, uint32_t *bad, int sm_count,
                               cudaStream_t s)

@@ -108,6 +108,7 @@ cudaError_t launch_pack_pairs(const uint32_t *cols, const float *vals, void *pai
 // shared-memory sort takes (32 KB of column indices); 16 rows of at most kMaxSplitNnz nonzeros fit, so every panel
 // left out holds a long row and runs on the row kernel whatever its density.
 constexpr uint32_t kDevPanelMax = 8192;
+cudaError_t launch_set_values(void *pairs, const float *vals, uint64_t nnz, int sm_count, cudaStream_t s);
 cudaError_t launch_panel_columns(const uint32_t *row_ptr, const void *pairs, uint32_t M, uint32_t num_panels, uint32_t *ncols,
                                  uint32_t *acols, int sm_count, cudaStream_t s);
 cudaError_t launch_panel_max_col(const uint32_t *row_ptr, const void *pairs, uint32_t M, uint32_t num_panels, uint32_t *maxcol, int sm_count,

@@ -82,6 +82,7 @@ struct HostPlan {
     uint64_t M = 0, K = 0, nnz = 0;
     cutespmm_options_t opts{};
     bool device_built = false;  // the nonzeros were packed on the device; the host holds row pointers and work lists only
+    bool values_on_device = false;  // cutespmm_plan_set_values replaced the values on the device: the host copy in `pairs` is stale
     bool adaptive_tiling = false;  // the caller left split_nnz and tile_nnz at 0: small jobs get smaller tiles and chunks
 
     // ---- row reordering (CUTESPMM_REORDER_CLUSTER_ROWS): row r of everything below is row row_map[r] of the caller's

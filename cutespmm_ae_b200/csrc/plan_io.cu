@@ -83,7 +83,7 @@ int cutespmm_plan_save(const cutespmm_plan_t *plan, const char *path)
     HostPlan h;  // a copy: a device-built plan gets its device-only arrays filled in below
     try {
         h = plan->host;
-        if (plan->host.device_built && plan->on_device) {
+        if ((plan->host.device_built || plan->host.values_on_device) && plan->on_device) {
             int cur = -1;
             cudaGetDevice(&cur);
             if (cur != plan->device) cudaSetDevice(plan->device);

@@ -67,6 +67,14 @@ class SparseOperator:
     def sddmm(self, X: torch.Tensor, Y: torch.Tensor, scale_by_values: bool = False) -> torch.Tensor:
         return torch.ops.cutespmm.sddmm(self.id, X, Y, scale_by_values)
 
+    def set_values(self, vals: torch.Tensor) -> None:
+        """New values for the same pattern (Plan.set_values), e.g. normalised `sddmm` scores as attention weights.  The
+        plan of A^T, if a backward pass has built one, is dropped and rebuilt from the new values on next use."""
+        self.plan.set_values(vals)
+        if self._transposed is not None:
+            self._transposed.close()
+            self._transposed = None
+
     def close(self) -> None:
         _plans.pop(self.id, None)
         for p in (self.plan, self._transposed):

@@ -199,6 +199,15 @@ int cutespmm_spmm_host(cutespmm_plan_t *plan, const float *B_host, uint64_t ldb,
 int cutespmm_sddmm(const cutespmm_plan_t *plan, const float *X_dev, uint64_t ldx, const float *Y_dev, uint64_t ldy, uint32_t N,
                    int scale_by_values, float *out_dev, void *stream);
 
+/* New values for an unchanged pattern: vals_dev[j] becomes the value of nonzero j in the plan's storage order -- the
+ * order cutespmm_sddmm writes its output in and cutespmm_plan_decode_csr returns -- so edge scores computed by
+ * cutespmm_sddmm (and normalised by the caller) become the weights of the next product: the weighted / attention
+ * aggregation of a graph layer (the reference tree carries it as the TC-GNN baseline's forward_AGNN,
+ * TC-GNN_ATC23/TCGNN_conv/TCGNN.cpp:260-264).  One pass over the nonzeros on `stream`; products queued on the stream
+ * afterwards see the new values.  For plans whose rows all run on the row kernel (path rows, or auto without dense
+ * panels) and without row reordering; CUTESPMM_EUNSUPPORTED otherwise. */
+int cutespmm_plan_set_values(cutespmm_plan_t *plan, const float *vals_dev, void *stream);
+
 /* ---- product without any allocation ------------------------------------------------------------
  * No counterpart in the reference.  For callers that must not allocate device memory when they
  * call (all of HBM already belongs to the host framework's pool, a real-time loop that may not make

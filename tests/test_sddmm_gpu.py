@@ -82,3 +82,48 @@ def test_sddmm_refusals_and_empty_cases():
         cs.Plan.from_csr(A).sddmm(X, torch.zeros(A.K, 9, device="cuda"))
     empty = cs.Plan(32, 16, np.zeros(33, np.uint64), np.zeros(0, np.uint32), np.zeros(0, np.float32))
     assert empty.sddmm(torch.zeros(32, 8, device="cuda"), torch.zeros(16, 8, device="cuda")).numel() == 0
+
+
+@pytest.mark.parametrize("builder", ["host", "device"])
+def test_set_values_makes_edge_scores_the_weights_of_the_next_product(oracle_mod, builder, tmp_path):
+    """The attention step of a graph layer: scores = sddmm(X, Y), any elementwise normalisation, set_values(scores), then
+    the product aggregates with those weights.  The pattern and the work lists stay; decode and save see the new values."""
+    A = g.rmat(11, 8, seed=81, values="uniform")  # hub rows: chunks whose pieces are summed in the launch
+    if builder == "host":
+        p = cs.Plan.from_csr(A, path=cs.PATH_ROWS)
+    else:
+        p = cs.Plan.from_device_csr(A.M, A.K, A.row_ptr.to(torch.int32).cuda(), A.cols.to(torch.int32).cuda(), A.vals.cuda(), path=cs.PATH_ROWS)
+    assert p.info()["num_long_rows"] > 0
+    X, Y = g.dense_operand(A.M, 64, 82, device="cuda"), g.dense_operand(A.K, 64, 83, device="cuda")
+    w = torch.tanh(p.sddmm(X, Y) / 8.0)
+    p.set_values(w)
+    rp, cc, vv = p.decode_csr()  # the plan's storage order, with the new values
+    assert np.array_equal(vv, w.cpu().numpy())
+    B = g.dense_operand(A.K, 128, 84)
+    C = torch.full((A.M, 128), float("nan"), device="cuda")
+    p.spmm(B.cuda(), C)
+    torch.cuda.synchronize()
+    ref = oracle_mod.spmm_csr(rp, cc, vv, B.numpy(), A.M, A.K)
+    assert oracle_mod.rel_fro(ref, C.cpu().numpy()) <= TOL
+    # a second replacement, and the saved plan carries what the device holds
+    p.set_values(-w)
+    f = tmp_path / "weighted.plan"
+    p.save(f)
+    q = cs.Plan.load(f)
+    C2 = torch.empty_like(C)
+    q.spmm(B.cuda(), C2)
+    torch.cuda.synchronize()
+    assert oracle_mod.rel_fro(-ref, C2.cpu().numpy()) <= TOL
+    assert np.array_equal(q.decode_csr()[2], -vv)
+
+
+def test_set_values_is_refused_where_the_values_live_in_tensor_core_records_or_rows_are_reordered():
+    S = g.stencil9(64)
+    for kw in (dict(path=cs.PATH_BRICK), dict(path=cs.PATH_ROWS, reorder="cluster")):
+        p = cs.Plan.from_csr(S, **kw)
+        with pytest.raises(cs.CuteSpmmError) as e:
+            p.set_values(torch.ones(S.nnz, device="cuda"))
+        assert e.value.status == -4
+    p = cs.Plan.from_csr(S, path=cs.PATH_ROWS)
+    with pytest.raises(ValueError):
+        p.set_values(torch.ones(S.nnz + 1, device="cuda"))

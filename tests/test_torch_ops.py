@@ -58,3 +58,25 @@ def test_forward_backward_and_opcheck(oracle_mod):
     torch.library.opcheck(torch.ops.cutespmm.spmm.default, (op.id, B.detach().clone().requires_grad_(True)),
                           test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
     op.close()
+
+
+@pytest.mark.gpu
+def test_attention_weights_flow_through_forward_and_backward(oracle_mod):
+    """scores = sddmm -> weights -> set_values: the forward product and the gradient with respect to B (through the plan
+    of A^T, rebuilt after the values changed) both use the new weights."""
+    A = g.rmat(10, 8, seed=19, values="uniform")
+    op = torch_ops.SparseOperator(cs.Plan.from_csr(A, path=cs.PATH_ROWS), plan_kwargs=dict(path=cs.PATH_ROWS))
+    B = g.dense_operand(A.K, 64, 20, device="cuda").requires_grad_(True)
+    G = g.dense_operand(A.M, 64, 21, device="cuda")
+    (op(B) * G).sum().backward()  # builds the plan of A^T from the old values
+    B.grad = None
+    w = torch.sigmoid(op.sddmm(G, B.detach()))
+    op.set_values(w)
+    rp, cc, vv = op.plan.decode_csr()
+    C = op(B)
+    assert oracle_mod.rel_fro(oracle_mod.spmm_csr(rp, cc, vv, B.detach().cpu().numpy(), A.M, A.K), C.detach().cpu().numpy()) <= 2e-6
+    (C * G).sum().backward()
+    t_rp, t_cols, t_vals = torch_ops.transpose_csr(A.M, A.K, rp, cc, vv)
+    want = oracle_mod.spmm_csr(t_rp, t_cols, t_vals, G.cpu().numpy(), A.K, A.M)
+    assert oracle_mod.rel_fro(want, B.grad.cpu().numpy()) <= 2e-6
+    op.close()
