@@ -9,10 +9,14 @@ any stream:
     op = SparseOperator(plan)          # registers the plan, gives it an integer id
     C = op(B)                          # C = A @ B, differentiable with respect to B
     scores = op.sddmm(X, Y)            # one dot product per stored nonzero
+    C = op.weighted(w, B)              # C = (pattern of A with values w) @ B, differentiable with respect to w and B
 
 The gradient of C = A @ B with respect to B is A^T @ dC: the transposed plan is built on first use
-(from the plan's own decoded CSR) and cached.  A is constant data of the plan, so no gradient flows to
-its values; `op.sddmm(dC, B)` is that gradient for a caller who wants it.
+(from the plan's own decoded CSR) and cached.  In `op(B)` A is constant data of the plan, so no gradient flows
+to its values.  `op.weighted(w, B)` is the attention form (TCGNN.cpp:260-264, forward_AGNN): w -- one weight per
+stored nonzero in the plan's storage order, typically normalised `op.sddmm` scores -- replaces the plan's values
+(Plan.set_values) before the product; its gradients are dB = A_w^T @ dC (the transposed plan receives w through a
+permutation computed once) and dw = sddmm(dC, B).
 """
 from __future__ import annotations
 
@@ -50,6 +54,7 @@ class SparseOperator:
         self.M, self.K, self.nnz = plan.M, plan.K, plan.nnz
         self._plan_kwargs = plan_kwargs or {}
         self._transposed: Plan | None = None
+        self._t_perm: torch.Tensor | None = None  # storage position in A of every stored position of A^T
         self.id = next(_ids)
         _plans[self.id] = self
         weakref.finalize(self, _plans.pop, self.id, None)
@@ -66,6 +71,18 @@ class SparseOperator:
 
     def sddmm(self, X: torch.Tensor, Y: torch.Tensor, scale_by_values: bool = False) -> torch.Tensor:
         return torch.ops.cutespmm.sddmm(self.id, X, Y, scale_by_values)
+
+    def weighted(self, w: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+        return torch.ops.cutespmm.spmm_weighted(self.id, w, B)
+
+    def _transposed_with(self, w: torch.Tensor) -> Plan:
+        """The plan of A^T carrying the weights w (given in this plan's storage order)."""
+        if self._t_perm is None:
+            rp, cols, _ = self.plan.decode_csr()
+            self._t_perm = torch.from_numpy(np.argsort(np.asarray(cols, dtype=np.int64), kind="stable")).to(w.device)
+        t = self.transposed()
+        t.set_values(w.detach().contiguous()[self._t_perm])
+        return t
 
     def set_values(self, vals: torch.Tensor) -> None:
         """New values for the same pattern (Plan.set_values), e.g. normalised `sddmm` scores as attention weights.  The
@@ -139,6 +156,46 @@ def _spmm_setup(ctx, inputs, output):
 
 _spmm.register_autograd(_spmm_backward, setup_context=_spmm_setup)
 _spmm_t.register_autograd(lambda ctx, g: (None, torch.ops.cutespmm.spmm(ctx.plan_id, g)), setup_context=_spmm_setup)
+
+
+@torch.library.custom_op("cutespmm::spmm_weighted", mutates_args=())
+def _spmm_w(plan_id: int, w: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    op = _get(plan_id)
+    op.plan.set_values(w.detach().contiguous())
+    Bc = B if B.stride(-1) == 1 else B.contiguous()
+    return op.plan.spmm(Bc)
+
+
+@_spmm_w.register_fake
+def _(plan_id: int, w: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    return B.new_empty((_get(plan_id).M, B.shape[1]))
+
+
+@torch.library.custom_op("cutespmm::spmm_weighted_transposed", mutates_args=())
+def _spmm_wt(plan_id: int, w: torch.Tensor, G: torch.Tensor) -> torch.Tensor:
+    op = _get(plan_id)
+    Gc = G if G.stride(-1) == 1 else G.contiguous()
+    return op._transposed_with(w).spmm(Gc)
+
+
+@_spmm_wt.register_fake
+def _(plan_id: int, w: torch.Tensor, G: torch.Tensor) -> torch.Tensor:
+    return G.new_empty((_get(plan_id).K, G.shape[1]))
+
+
+def _spmm_w_setup(ctx, inputs, output):
+    ctx.plan_id = inputs[0]
+    ctx.save_for_backward(inputs[1], inputs[2])
+
+
+def _spmm_w_backward(ctx, grad_C):
+    w, B = ctx.saved_tensors
+    grad_w = torch.ops.cutespmm.sddmm(ctx.plan_id, grad_C, B, False) if ctx.needs_input_grad[1] else None
+    grad_B = torch.ops.cutespmm.spmm_weighted_transposed(ctx.plan_id, w, grad_C) if ctx.needs_input_grad[2] else None
+    return None, grad_w, grad_B
+
+
+_spmm_w.register_autograd(_spmm_w_backward, setup_context=_spmm_w_setup)
 
 
 @torch.library.custom_op("cutespmm::sddmm", mutates_args=())

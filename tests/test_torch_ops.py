@@ -80,3 +80,31 @@ def test_attention_weights_flow_through_forward_and_backward(oracle_mod):
     want = oracle_mod.spmm_csr(t_rp, t_cols, t_vals, G.cpu().numpy(), A.K, A.M)
     assert oracle_mod.rel_fro(want, B.grad.cpu().numpy()) <= 2e-6
     op.close()
+
+
+@pytest.mark.gpu
+def test_weighted_product_is_differentiable_in_the_weights_and_in_b():
+    """op.weighted(w, B) against a dense torch product built from the same pattern: forward, dC/dw (SDDMM) and dC/dB
+    (the transposed plan with permuted weights), twice with different weights (the plans are reused)."""
+    A = g.uniform_random(300, 200, 7, seed=31)
+    op = torch_ops.SparseOperator(cs.Plan.from_csr(A, path=cs.PATH_ROWS), plan_kwargs=dict(path=cs.PATH_ROWS))
+    rp, cc, _ = op.plan.decode_csr()
+    rows = torch.from_numpy(np.repeat(np.arange(A.M), np.diff(rp.astype(np.int64)))).cuda()
+    cols = torch.from_numpy(cc.astype(np.int64)).cuda()
+    for seed in (32, 33):
+        w = g.dense_operand(A.nnz, 1, seed, device="cuda").flatten().requires_grad_(True)
+        B = g.dense_operand(A.K, 48, seed + 10, device="cuda").requires_grad_(True)
+        G = g.dense_operand(A.M, 48, seed + 20, device="cuda")
+        (op.weighted(w, B) * G).sum().backward()
+        w2, B2 = w.detach().clone().requires_grad_(True), B.detach().clone().requires_grad_(True)
+        dense = torch.zeros(A.M, A.K, device="cuda").index_put((rows, cols), w2)
+        C_ref = dense @ B2
+        (C_ref * G).sum().backward()
+        C = op.weighted(w.detach(), B.detach())
+        assert torch.allclose(C, C_ref.detach(), rtol=1e-4, atol=1e-4)
+        assert torch.allclose(w.grad, w2.grad, rtol=1e-4, atol=1e-4)
+        assert torch.allclose(B.grad, B2.grad, rtol=1e-4, atol=1e-4)
+    torch.library.opcheck(torch.ops.cutespmm.spmm_weighted.default,
+                          (op.id, w.detach().clone().requires_grad_(True), B.detach().clone().requires_grad_(True)),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+    op.close()
