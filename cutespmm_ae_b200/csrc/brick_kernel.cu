@@ -71,7 +71,10 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
     const uint32_t W = gridDim.x * kBrickWarps;
     uint32_t ord = warp * gridDim.x + blockIdx.x;  // this warp's current panel (ordinal among brick panels)
     if (ord >= a.num_panels) return;  // warps never synchronise with each other, so leaving early is safe
-    const uint32_t n0 = blockIdx.y * L::kSlab;
+    // A product wider than one slab of L::kSlab columns walks every panel once per slab, slab after slab, before it moves
+    // to its next panel: the panel's records and column lists are then found in L2 by the second walk, and one grid of
+    // persistent blocks covers all slabs.
+    const uint32_t slabs = a.N / L::kSlab;
 
     unsigned char *mine = smem_raw + (size_t)warp * L::kWarpBytes;
     uint64_t *full = reinterpret_cast<uint64_t *>(mine + kStages * L::kStageBytes);
@@ -100,6 +103,8 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
     };
     uint32_t pk, pk_end;  // producer cursor: next slot to issue, end of its panel
     load_range(ord, pk, pk_end);
+    uint32_t p_k0 = pk;   // first slot of the producer's panel (walked again for the next slab)
+    uint32_t p_slab = 0, c_slab = 0;  // column slab of the producer cursor / of the brick being consumed
     uint32_t G = pk >> 2;
     uint4 mc_cur = load_cols(G), mc_nxt = load_cols(G + 1);
     uint32_t n_k0, n_k1, nn_k0, nn_k1;  // slot ranges of the next panel and the one after (k0 == k1: none)
@@ -129,13 +134,21 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
             ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)k * kRecWords, kRecWords * 4u, &full[s]);
         }
         if ((uint32_t)(lane >> 1) == j)
-            ptx::tma_gather4(reinterpret_cast<unsigned char *>(stage_b(s)) + (lane & 1) * L::kHalfBytes, &tmap_b, (int)n0, (int)mc_cur.x,
+            ptx::tma_gather4(reinterpret_cast<unsigned char *>(stage_b(s)) + (lane & 1) * L::kHalfBytes, &tmap_b, (int)(p_slab * L::kSlab), (int)mc_cur.x,
                              (int)mc_cur.y, (int)mc_cur.z, (int)mc_cur.w, &full[s]);
         ++issued;
-        if (++pk == pk_end) {  // panel finished: move the cursor to the warp's next panel
+        if (++pk == pk_end && p_slab + 1 < slabs) {  // panel finished for this slab: the same panel again, next slab
+            ++p_slab;
+            pk = p_k0;
+            G = pk >> 2;
+            mc_cur = load_cols(G);
+            mc_nxt = load_cols(G + 1);
+        } else if (pk == pk_end) {  // panel finished: move the cursor to the warp's next panel
+            p_slab = 0;
             p_ord += W;
             pk = n_k0;
             pk_end = n_k1;
+            p_k0 = pk;
             G = pk >> 2;
             mc_cur = n_mc;
             n_k0 = nn_k0;
@@ -190,6 +203,8 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
             const uint64_t r_lo = (uint64_t)info.y * kPanelRows + g, r_hi = r_lo + 8;
             // a reordered plan writes every row to its place in the caller's C
             const uint64_t o_lo = a.row_map && r_lo < a.M ? __ldg(a.row_map + r_lo) : r_lo, o_hi = a.row_map && r_hi < a.M ? __ldg(a.row_map + r_hi) : r_hi;
+            const uint32_t n0 = c_slab * L::kSlab;
+            c_slab = c_slab + 1 == slabs ? 0 : c_slab + 1;
             float *c_lo = a.C + o_lo * a.ldc + n0 + 2 * t, *c_hi = a.C + o_hi * a.ldc + n0 + 2 * t;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
@@ -209,14 +224,13 @@ template <int NT, bool ROUND_B> cudaError_t launch_brick_t(const BrickArgs &a, i
     constexpr int smem = kBrickWarps * L::kWarpBytes;
     cudaError_t e = allow_dynamic_smem<spmm_brick_kernel<NT, ROUND_B>>(smem);
     if (e != cudaSuccess) return e;
-    const uint32_t slabs = a.N / L::kSlab;
     uint32_t blocks = (a.num_panels + kBrickWarps - 1) / kBrickWarps;
     if (blocks > (uint32_t)sm_count) blocks = (uint32_t)sm_count;  // one resident block per SM, persistent
     // B as a 2-D tensor; the box is the slab plus the 8 columns of padding that give the shared-memory stride
     CUtensorMap tmap;
     e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, L::kStride, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (e != cudaSuccess) return e;
-    spmm_brick_kernel<NT, ROUND_B><<<dim3(blocks, slabs), kBrickWarps * 32, smem, s>>>(tmap, a);
+    spmm_brick_kernel<NT, ROUND_B><<<blocks, kBrickWarps * 32, smem, s>>>(tmap, a);
     return cudaGetLastError();
 }
 
