@@ -55,7 +55,8 @@ template <int NT> struct StageLayout {
 
 // ROUND_B: round the elements of B to tf32 to nearest (cvt.rna, what the reference does,
 // kernel.cu:35) instead of letting the tensor core drop the low 13 mantissa bits.
-template <int NT, bool ROUND_B>
+// MULTI: the product is wider than one slab of columns (the single-slab kernel carries none of the slab bookkeeping).
+template <int NT, bool ROUND_B, bool MULTI>
 __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const __grid_constant__ CUtensorMap tmap_b, BrickArgs a)
 {
     using L = StageLayout<NT>;
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
     // A product wider than one slab of L::kSlab columns walks every panel once per slab, slab after slab, before it moves
     // to its next panel: the panel's records and column lists are then found in L2 by the second walk, and one grid of
     // persistent blocks covers all slabs.
-    const uint32_t slabs = a.N / L::kSlab;
+    const uint32_t slabs = MULTI ? a.N / L::kSlab : 1u;
 
     unsigned char *mine = smem_raw + (size_t)warp * L::kWarpBytes;
     uint64_t *full = reinterpret_cast<uint64_t *>(mine + kStages * L::kStageBytes);
@@ -134,16 +135,16 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
             ptx::bulk_g2s(stage_rec(s), a.recs + (size_t)k * kRecWords, kRecWords * 4u, &full[s]);
         }
         if ((uint32_t)(lane >> 1) == j)
-            ptx::tma_gather4(reinterpret_cast<unsigned char *>(stage_b(s)) + (lane & 1) * L::kHalfBytes, &tmap_b, (int)(p_slab * L::kSlab), (int)mc_cur.x,
+            ptx::tma_gather4(reinterpret_cast<unsigned char *>(stage_b(s)) + (lane & 1) * L::kHalfBytes, &tmap_b, (int)(MULTI ? p_slab * L::kSlab : 0u), (int)mc_cur.x,
                              (int)mc_cur.y, (int)mc_cur.z, (int)mc_cur.w, &full[s]);
         ++issued;
-        if (++pk == pk_end && p_slab + 1 < slabs) {  // panel finished for this slab: the same panel again, next slab
+        if (MULTI && pk + 1 == pk_end && p_slab + 1 < slabs) {  // panel finished for this slab: the same panel again, next slab
             ++p_slab;
             pk = p_k0;
             G = pk >> 2;
             mc_cur = load_cols(G);
             mc_nxt = load_cols(G + 1);
-        } else if (pk == pk_end) {  // panel finished: move the cursor to the warp's next panel
+        } else if (++pk == pk_end) {  // panel finished: move the cursor to the warp's next panel
             p_slab = 0;
             p_ord += W;
             pk = n_k0;
@@ -203,8 +204,8 @@ __global__ void __launch_bounds__(kBrickWarps * 32, 1) spmm_brick_kernel(const _
             const uint64_t r_lo = (uint64_t)info.y * kPanelRows + g, r_hi = r_lo + 8;
             // a reordered plan writes every row to its place in the caller's C
             const uint64_t o_lo = a.row_map && r_lo < a.M ? __ldg(a.row_map + r_lo) : r_lo, o_hi = a.row_map && r_hi < a.M ? __ldg(a.row_map + r_hi) : r_hi;
-            const uint32_t n0 = c_slab * L::kSlab;
-            c_slab = c_slab + 1 == slabs ? 0 : c_slab + 1;
+            const uint32_t n0 = MULTI ? c_slab * L::kSlab : 0u;
+            if (MULTI) c_slab = c_slab + 1 == slabs ? 0 : c_slab + 1;
             float *c_lo = a.C + o_lo * a.ldc + n0 + 2 * t, *c_hi = a.C + o_hi * a.ldc + n0 + 2 * t;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
@@ -222,7 +223,8 @@ template <int NT, bool ROUND_B> cudaError_t launch_brick_t(const BrickArgs &a, i
 {
     using L = StageLayout<NT>;
     constexpr int smem = kBrickWarps * L::kWarpBytes;
-    cudaError_t e = allow_dynamic_smem<spmm_brick_kernel<NT, ROUND_B>>(smem);
+    const bool multi = a.N > (uint32_t)L::kSlab;
+    cudaError_t e = multi ? allow_dynamic_smem<spmm_brick_kernel<NT, ROUND_B, true>>(smem) : allow_dynamic_smem<spmm_brick_kernel<NT, ROUND_B, false>>(smem);
     if (e != cudaSuccess) return e;
     uint32_t blocks = (a.num_panels + kBrickWarps - 1) / kBrickWarps;
     if (blocks > (uint32_t)sm_count) blocks = (uint32_t)sm_count;  // one resident block per SM, persistent
@@ -230,7 +232,8 @@ template <int NT, bool ROUND_B> cudaError_t launch_brick_t(const BrickArgs &a, i
     CUtensorMap tmap;
     e = make_b_tensor_map(&tmap, a.B, a.N, a.K, a.ldb, L::kStride, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (e != cudaSuccess) return e;
-    spmm_brick_kernel<NT, ROUND_B><<<blocks, kBrickWarps * 32, smem, s>>>(tmap, a);
+    if (multi) spmm_brick_kernel<NT, ROUND_B, true><<<blocks, kBrickWarps * 32, smem, s>>>(tmap, a);
+    else spmm_brick_kernel<NT, ROUND_B, false><<<blocks, kBrickWarps * 32, smem, s>>>(tmap, a);
     return cudaGetLastError();
 }
 
